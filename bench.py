@@ -1,0 +1,516 @@
+#!/usr/bin/env python
+"""bench.py -- throughput of the GEMM hot path on B200, one JSON line on stdout.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Default workload: the NVFP4 block-scaled GEMM M=8192, N=28672, K=8192 (bf16 output), the
+configuration the sharded numbers are quoted on.  At N > 1 the weight matrix is split by output
+columns across the ranks (strong scaling: total work fixed); A is replicated; no data-path
+collective is inside the timed step (the NCCL all-gather of the bf16 output is timed beside it).
+
+A step is one GEMM launch over inputs already resident in HBM.  L2 is flushed (a 256 MiB write)
+between timed steps, each step is timed with CUDA events on the launching stream, the step times
+are summed, and the maximum over ranks is reported.  `e2e` repeats the measurement through the
+C ABI with HOST buffers: pinned activations copied in, the output copied back, every step.
+
+`--impl reference` times Blaze's own host GEMM (tests/test_gemm_naive.cu:38-48, compiled into
+oracle/_ref when the reference tree was present, otherwise the oracle's port of that loop) on the
+box's host cores over a bounded row-slice of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (kind, M, N, K) -- BASELINE.json configs
+    "nvfp4_8192x28672x8192": ("nvfp4", 8192, 28672, 8192),
+    "fp8_4096": ("fp8", 4096, 4096, 4096),
+    "w4a16_4096x22016x4096": ("w4a16_bf16", 4096, 22016, 4096),
+    "fp16_256": ("f16", 256, 256, 256),
+    "nvfp4_4096x12288x4096": ("nvfp4", 4096, 12288, 4096),
+    "nvfp4_4096x22016x4096": ("nvfp4", 4096, 22016, 4096),
+    "bf16_8192": ("bf16", 8192, 8192, 8192),
+}
+DECODE_SHAPES = [(16, 12288, 4096), (16, 4096, 4096), (16, 22016, 4096), (16, 4096, 11008)]
+NOMINAL_TFLOPS = {"nvfp4": 9000.0, "fp8": 4500.0, "f16": 2250.0, "bf16": 2250.0, "w4a16_bf16": 2250.0, "w4a16_f16": 2250.0}
+PEAK_MULT_OVER_BF16 = {"nvfp4": 4.0, "fp8": 2.0, "f16": 1.0, "bf16": 1.0, "w4a16_bf16": 1.0, "w4a16_f16": 1.0}
+
+
+def measured_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ----------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.004):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._h = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._h = None
+
+    def _loop(self):
+        nv = self._nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        getter = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                mask = int(getter(self._h))
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self._h is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        s = sorted(self.samples)
+        med = s[len(s) // 2] if s else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# ------------------------------------------------------------------------- GPU workloads
+
+class L2Flusher:
+    def __init__(self, device):
+        import torch
+        self.buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+
+    def flush(self):
+        self.buf.fill_(1)
+
+
+def make_operands(kind, M, N, K, device, seed_b=123):
+    """Synthetic operands on the device: N(0,1) activations (seed 42), N(0,1) weights (seed 123; N(0,0.02)
+    for W4A16), quantised by the library's own kernels.  Returns kwargs for GemmPlan and the byte count."""
+    import torch
+    from blaze_b200 import quantize_fp8, quantize_nvfp4
+    ga = torch.Generator(device=device).manual_seed(42)
+    gb = torch.Generator(device=device).manual_seed(seed_b)
+    if kind == "nvfp4":
+        xa = torch.randn((M, K), generator=ga, device=device)
+        ad, asf, gA = quantize_nvfp4(xa, tiled=True); del xa
+        xb = torch.randn((N, K), generator=gb, device=device)
+        bd, bsf, gB = quantize_nvfp4(xb, tiled=True); del xb
+        kw = dict(A=ad, B=bd, A_sf=asf, B_sf=bsf, a_scale=float(gA.item()), b_scale=float(gB.item()), a_sf_layout="tiled", b_sf_layout="tiled")
+        nbytes = M * K // 2 + M * K // 16 + N * K // 2 + N * K // 16
+    elif kind == "fp8":
+        xa = torch.rand((M, K), generator=ga, device=device) * 2 - 1
+        xb = torch.rand((N, K), generator=gb, device=device) * 2 - 1
+        qa, sa = quantize_fp8(xa); qb, sb = quantize_fp8(xb)
+        kw = dict(A=qa, B=qb, a_scale=float(sa[1].item()), b_scale=float(sb[1].item()))
+        nbytes = M * K + N * K
+    elif kind.startswith("w4a16"):
+        dt = torch.bfloat16 if kind.endswith("bf16") else torch.float16
+        A = torch.randn((M, K), generator=ga, device=device).to(dt)
+        W = torch.randn((N, K), generator=gb, device=device) * 0.02
+        bd, bsf, gB = quantize_nvfp4(W, tiled=True); del W
+        kw = dict(A=A, B=bd, B_sf=bsf, b_scale=float(gB.item()), b_sf_layout="tiled")
+        nbytes = M * K * 2 + N * K // 2 + N * K // 16
+    else:
+        dt = torch.bfloat16 if kind == "bf16" else torch.float16
+        A = torch.randn((M, K), generator=ga, device=device).to(dt)
+        B = torch.randn((N, K), generator=gb, device=device).to(dt)
+        kw = dict(A=A, B=B)
+        nbytes = (M * K + N * K) * 2
+    torch.cuda.synchronize()
+    return kw, nbytes
+
+
+def time_steps(fn, steps, warmup, flusher, barrier=None):
+    """W warm-ups, then K steps each bracketed by CUDA events with an L2 flush before it."""
+    import torch
+    for _ in range(warmup):
+        flusher.flush(); fn()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        flusher.flush()
+        starts[i].record()
+        fn()
+        ends[i].record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    times = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    return sum(times) / steps, times
+
+
+def run_gemm_workload(kind, M, N, K, device, steps, warmup, flusher, out_dtype="bf16", barrier=None, variant="auto", seed_b=123):
+    import torch
+    from blaze_b200 import GemmPlan
+    kw, op_bytes = make_operands(kind, M, N, K, device, seed_b)
+    A, B = kw.pop("A"), kw.pop("B")
+    dt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[out_dtype]
+    C = torch.empty((M, N), dtype=dt, device=device)
+    plan = GemmPlan(kind, M, N, K, A, B, out_dtype=out_dtype, variant=variant, **kw)
+    ms, times = time_steps(lambda: plan.execute(C), steps, warmup, flusher, barrier)
+    plan.check()
+    info = plan.info()
+    return dict(plan=plan, C=C, A=A, B=B, kw=kw, ms=ms, times=times, info=info, op_bytes=op_bytes,
+                flops=2.0 * M * N * K, out_bytes=M * N * C.element_size())
+
+
+def run_decode(device, steps, warmup, peaks):
+    """BASELINE config 3: NVFP4 M=16 decode projections.  Enough distinct weight copies to exceed twice
+    the L2 are cycled inside one CUDA graph so that every launch streams its weights from HBM."""
+    import torch
+    from blaze_b200 import GemmPlan
+    out = []
+    for (M, N, K) in DECODE_SHAPES:
+        kw, _ = make_operands("nvfp4", M, N, K, device)
+        A, B = kw.pop("A"), kw.pop("B")
+        w_bytes = N * K // 2 + N * K // 16
+        algo = w_bytes + M * K // 2 + M * K // 16 + 2 * M * N
+        copies = max(2, -(-2 * 126 * 1024 * 1024 // w_bytes))
+        Bs = [B] + [B.clone() for _ in range(copies - 1)]
+        SFs = [kw["B_sf"]] + [kw["B_sf"].clone() for _ in range(copies - 1)]
+        C = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+        plans = []
+        for b, sf in zip(Bs, SFs):
+            k2 = dict(kw); k2["B_sf"] = sf
+            plans.append(GemmPlan("nvfp4", M, N, K, A, b, out_dtype="bf16", **k2))
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            for p in plans:
+                p.execute(C)
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for p in plans:
+                    p.execute(C)
+        for _ in range(max(3, warmup)):
+            graph.replay()
+        torch.cuda.synchronize()
+        reps = max(3, steps)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(reps):
+            graph.replay()
+        e.record()
+        torch.cuda.synchronize()
+        us = s.elapsed_time(e) * 1000.0 / (reps * copies)
+        plans[0].check()
+        info = plans[0].info()
+        gbs = algo / (us * 1e-6) / 1e9
+        out.append({"M": M, "N": N, "K": K, "us_per_gemm": round(us, 3), "hbm_gbs": round(gbs, 1), "algorithmic_bytes": algo,
+                    "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4), "weight_copies_cycled": copies,
+                    "split_k": info["split_k"], "grid": info["grid"], "launches": reps * copies})
+        for p in plans:
+            p.destroy()
+        del Bs, SFs, plans, graph
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_e2e(res, steps, device):
+    """Same GEMM through the public call with host buffers: pinned A (and its scale factors) copied to
+    the device, the GEMM, the whole output copied back to pinned host memory, every step."""
+    import torch
+    plan, C, A, kw = res["plan"], res["C"], res["A"], res["kw"]
+    hA = torch.empty(A.shape, dtype=A.dtype, pin_memory=True); hA.copy_(A)
+    sf = kw.get("A_sf")
+    hS = None
+    if sf is not None:
+        hS = torch.empty(sf.shape, dtype=sf.dtype, pin_memory=True); hS.copy_(sf)
+    hC = torch.empty(C.shape, dtype=C.dtype, pin_memory=True)
+    h2d = A.numel() * A.element_size() + (sf.numel() if sf is not None else 0)
+    d2h = C.numel() * C.element_size()
+
+    def step():
+        A.copy_(hA, non_blocking=True)
+        if hS is not None:
+            sf.copy_(hS, non_blocking=True)
+        plan.execute(C)
+        hC.copy_(C, non_blocking=True)
+
+    step(); torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(steps):
+        step()
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / steps
+    checksum = float(hC.view(-1)[:1024].float().abs().sum())       # the host copy is read
+    return ms, h2d, d2h, checksum
+
+
+# ------------------------------------------------------------------------- CPU reference arm
+
+def cpu_reference_gemm(kind, M, N, K, target_seconds, threads=None):
+    """Times the host reference GEMM on a row-slice of the workload.  NVFP4 / FP8 operands are
+    dequantised first (exactly representable in fp16), so Blaze's own gemm_cpu_fp16 applies as is."""
+    import numpy as np
+    from oracle import build_oracle
+    build_oracle.build_oracle()
+    from oracle import oracle as O
+    threads = threads or (os.cpu_count() or 1)
+    use_ref = O.ref_available()
+    rng = np.random.default_rng(123)
+    # operands of the slice: quantise on the host with the oracle (a few rows of A, all of B is too
+    # much for the reference's [K, N] fp16 layout at the large configs, so N is sliced as well)
+    n_slice = min(N, 2048)
+    xb = rng.standard_normal((n_slice, K)).astype(np.float32)
+    xa_row = np.random.default_rng(42).standard_normal((1, K)).astype(np.float32)
+    if kind == "nvfp4":
+        bd, bsf, _ = O.quantize_nvfp4(xb); Bt = O.dequant_nvfp4_noglobal(bd, bsf)
+        deq_a = lambda x: O.dequant_nvfp4_noglobal(*O.quantize_nvfp4(x)[:2])
+    elif kind == "fp8":
+        Bt = O.e4m3_to_f32(O.quantize_fp8(xb)[0]); deq_a = lambda x: O.e4m3_to_f32(O.quantize_fp8(x)[0])
+    else:
+        Bt = O.f16_to_f32(O.f32_to_f16(xb)); deq_a = lambda x: O.f16_to_f32(O.f32_to_f16(x))
+    B16_kn = np.ascontiguousarray(O.f32_to_f16(Bt).T)                   # Blaze's [K, N] fp16 layout
+
+    def run(rows):
+        A32 = deq_a(np.repeat(xa_row, rows, axis=0) * np.linspace(0.5, 1.5, rows, dtype=np.float32)[:, None])
+        A16 = O.f32_to_f16(A32)
+        t0 = time.perf_counter()
+        if use_ref:
+            chunks = np.array_split(np.arange(rows), min(threads, rows))
+            outs = [None] * len(chunks)
+
+            def work(i):
+                outs[i] = O.ref_gemm_cpu_fp16(A16[chunks[i]], B16_kn)
+            ths = [threading.Thread(target=work, args=(i,)) for i in range(len(chunks))]
+            [t.start() for t in ths]; [t.join() for t in ths]
+        else:
+            O.gemm_f32(A32, Bt, nthreads=threads)
+        return time.perf_counter() - t0
+
+    t1 = run(threads)                                                   # calibration: one row per thread
+    rows = max(threads, int(threads * max(1.0, target_seconds / max(t1, 1e-3))))
+    rows = min(rows, M)
+    return dict(run=run, rows=rows, n_slice=n_slice, threads=threads, kind="reference" if use_ref else "port", calib_s=t1)
+
+
+def reference_arm(args, kind, M, N, K, workload_name):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    total = args.steps + args.warmup
+    per_step = max(0.5, min(8.0, 150.0 / max(total, 1)))
+    ref = cpu_reference_gemm(kind, M, N, K, per_step)
+    rows, n_slice = ref["rows"], ref["n_slice"]
+    for _ in range(args.warmup):
+        ref["run"](rows)
+    t = [ref["run"](rows) for _ in range(args.steps)]
+    sec = sum(t) / len(t)
+    flops = 2.0 * rows * n_slice * K
+    value = flops / sec / 1e12
+    sample = "%d rows x %d columns x K=%d slice of the workload per step, %s" % (
+        rows, n_slice, K, "Blaze gemm_cpu_fp16 (oracle/_ref) on row chunks, one thread each" if ref["kind"] == "reference" else "oracle port of gemm_cpu_fp16")
+    line = {"impl": "reference", "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": kind, "data": "synthetic",
+            "config": {"workload": workload_name, "M": M, "N": N, "K": K, "sample": sample},
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": ref["threads"], "kind": ref["kind"], "sample": sample},
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+    return 0
+
+
+# ---------------------------------------------------------------------------------- main
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="nvfp4_8192x28672x8192", choices=list(WORKLOADS) + ["decode"])
+    ap.add_argument("--variant", default="auto")
+    ap.add_argument("--no-others", action="store_true", help="skip the secondary workloads reported under 'others'")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    name = args.workload
+    if name == "decode":
+        kind, M, N, K = "nvfp4", 16, 22016, 4096
+    else:
+        kind, M, N, K = WORKLOADS[name]
+    if args.impl == "reference":
+        return reference_arm(args, kind, M, N, K, name)
+
+    import torch
+    import torch.distributed as dist
+    from blaze_b200 import _native
+    _native.lib()                                                        # fails loudly when the CUDA library is missing
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    barrier = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        barrier = lambda: dist.barrier(device_ids=[local])
+    peaks = measured_peaks()
+    flusher = L2Flusher(device)
+
+    if name == "decode":
+        with ClockSampler(local) as clk:
+            dec = run_decode(device, args.steps, args.warmup, peaks)
+        worst = min(dec, key=lambda d: d["hbm_gbs"])
+        best = max(dec, key=lambda d: d["hbm_gbs"])
+        line = {"metric": "nvfp4_decode_hbm_gbs", "value": best["hbm_gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": best["us_per_gemm"] / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4",
+                "data": "synthetic", "config": {"workload": "nvfp4 decode M=16, Llama-7B projections (BASELINE configs[2])", "l2": "weight copies > 2x L2 cycled in one CUDA graph"},
+                "roofline": {"bound": "hbm", "achieved": best["hbm_gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": best["hbm_gbs"] / peaks["hbm_gbs"],
+                             "traffic": None, "peak_source": peaks["source"]},
+                "shapes": dec, "worst": worst, "clocks": clk.summary(), "gpu_launches": sum(d["launches"] for d in dec)}
+        print(json.dumps(line))
+        return 0
+
+    # ---- main workload; at world > 1 every rank owns N/world output columns (rows of the K-major weights)
+    assert N % world == 0
+    n_local = N // world
+    with ClockSampler(local) as clk:
+        res = run_gemm_workload(kind, M, n_local, K, device, args.steps, args.warmup, flusher, barrier=barrier, variant=args.variant,
+                                seed_b=123 + 1000 * rank)
+    ms_local = res["ms"]
+    ms = ms_local
+    gather = None
+    if world > 1:
+        t = torch.tensor([ms_local], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        # optional exchange step, timed beside the GEMM: NCCL all-gather of the bf16 output,
+        # result layout [world][M][N/world]
+        full = torch.empty((world, M, n_local), dtype=res["C"].dtype, device=device)
+
+        def step_gather():
+            res["plan"].execute(res["C"])
+            dist.all_gather_into_tensor(full, res["C"])
+        g_ms, _ = time_steps(step_gather, max(5, args.steps // 3), 3, flusher, barrier)
+        t = torch.tensor([g_ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        g_ms = float(t.item())
+        gather = {"ms_per_step_gemm_plus_allgather": g_ms, "tflops": 2.0 * M * N * K / (g_ms * 1e-3) / 1e12,
+                  "allgather_bytes_received_per_rank": (world - 1) * M * n_local * 2, "layout": "[world][M][N/world] bf16"}
+    flops_total = 2.0 * M * N * K
+    value = flops_total / (ms * 1e-3) / 1e12
+
+    # roofline of the dominant (only) kernel, per launch on this rank
+    flops_launch = 2.0 * M * n_local * K
+    achieved = flops_launch / (ms_local * 1e-3) / 1e12
+    peak = peaks["bf16_tflops"] * PEAK_MULT_OVER_BF16[kind]
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                "peak_source": "%s dense bf16 burst (%.1f TFLOP/s) x %g, the nominal %s : bf16 ratio" % (peaks["source"], peaks["bf16_tflops"], PEAK_MULT_OVER_BF16[kind], kind),
+                "frac_of_nominal_peak": achieved / NOMINAL_TFLOPS[kind], "nominal_peak": NOMINAL_TFLOPS[kind],
+                "algorithmic_flops_per_launch": flops_launch,
+                "algorithmic_bytes_per_launch": res["op_bytes"] + res["out_bytes"],
+                "hbm_gbs_at_this_rate": (res["op_bytes"] + res["out_bytes"]) / (ms_local * 1e-3) / 1e9}
+
+    e2e_ms, h2d, d2h, _ = run_e2e(res, max(3, min(args.steps, 10)), device)
+    if world > 1:
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e = {"value": flops_total / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "ms_per_step": e2e_ms, "note": "pinned host activations in, whole bf16 output back to pinned host memory, every step; weights resident"}
+
+    launches = args.steps * res["info"]["launches"]
+    line = {"metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": kind, "data": "synthetic",
+            "config": {"workload": name, "kind": kind, "M": M, "N": N, "K": K, "out": "bf16", "accumulate": "fp32",
+                       "sharding": "weights split by output columns, %d per rank; activations replicated" % n_local,
+                       "l2": "256 MiB write between timed steps", "timing": "CUDA events per step on the launching stream, max over ranks",
+                       "kernel": res["info"]},
+            "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clk.summary()}
+    if gather:
+        line["gather"] = gather
+
+    if rank == 0 and world == 1 and not args.no_others:
+        others = {}
+        for w in ("fp8_4096", "w4a16_4096x22016x4096", "nvfp4_4096x12288x4096", "bf16_8192", "fp16_256"):
+            k2, m2, n2, kk2 = WORKLOADS[w]
+            try:
+                r2 = run_gemm_workload(k2, m2, n2, kk2, device, min(args.steps, 20), 3, flusher, out_dtype="f32" if w == "fp16_256" else "bf16")
+                tf = r2["flops"] / (r2["ms"] * 1e-3) / 1e12
+                others[w] = {"ms": r2["ms"], "tflops": tf, "frac_of_nominal_peak": tf / NOMINAL_TFLOPS[k2],
+                             "frac_of_measured_bf16_scaled": tf / (peaks["bf16_tflops"] * PEAK_MULT_OVER_BF16[k2]), "kernel": r2["info"]}
+                launches += min(args.steps, 20) * r2["info"]["launches"]
+                r2["plan"].destroy()
+                del r2
+                torch.cuda.empty_cache()
+            except Exception as ex:   # a secondary workload must not lose the headline line
+                others[w] = {"error": str(ex)[:200]}
+        try:
+            others["nvfp4_decode_M16"] = run_decode(device, 5, 3, peaks)
+        except Exception as ex:
+            others["nvfp4_decode_M16"] = {"error": str(ex)[:200]}
+        line["others"] = others
+
+    if rank == 0 and world == 1 and not args.no_cpu:
+        ref = cpu_reference_gemm(kind, M, N, K, 12.0)
+        sec = ref["run"](ref["rows"])
+        cpu_tf = 2.0 * ref["rows"] * ref["n_slice"] * K / sec / 1e12
+        line["cpu_baseline"] = {"value": cpu_tf, "unit": "TFLOP/s", "cores": ref["threads"], "kind": ref["kind"],
+                                "sample": "%d rows x %d columns x K=%d slice, %.1f s" % (ref["rows"], ref["n_slice"], K, sec)}
+    elif rank == 0:
+        line["cpu_baseline"] = None
+
+    res["plan"].destroy()
+    if world > 1:
+        dist.barrier(device_ids=[local])
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

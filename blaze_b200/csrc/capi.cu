@@ -1,0 +1,604 @@
+// capi.cu -- implementation of the C ABI declared in include/blaze_b200.h: plan construction
+// (operand repacking, tensor maps, kernel choice), launches, and the operand-preparation calls.
+//
+// Counterpart of the host halves of Blaze's src/kernels/gemm_*_sm100.cu (launch_* and
+// create_/execute_/destroy_ plans, e.g. gemm_fp8_sm100.cu:268-430,
+// gemm_fp4_blkscaled_sm100.cu:708-951,1083-1230).  Unlike those, nothing here exits the process:
+// every failure is a status code, and the device-side error word is read by blz_gemm_plan_check.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <type_traits>
+
+#include "../../include/blaze_b200.h"
+#include "decode_kernel.cuh"
+#include "gemm_kernel.cuh"
+#include "prep_kernels.cuh"
+
+using namespace blz;
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+thread_local char g_last_cuda_error_text[256] = "";
+
+bool cuda_ok(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return true;
+    g_last_cuda_error = static_cast<int>(e);
+    snprintf(g_last_cuda_error_text, sizeof(g_last_cuda_error_text), "%s: %s", what, cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return false;
+}
+#define BLZ_CUDA(call)                                             \
+    do {                                                           \
+        if (!cuda_ok((call), #call)) return BLZ_ERR_CUDA;          \
+    } while (0)
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up at run time so the library has no link-time dependency on
+// libcuda and can be loaded (not run) on a machine without a GPU driver.
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+    return fn;
+}
+
+// 2-D byte-typed tensor map over a row-major matrix: `inner_bytes` contiguous bytes per row,
+// `rows` rows, `pitch_bytes` apart; box = box_inner bytes x box_rows rows.
+blz_status encode_map(CUtensorMap* m, const void* base, uint64_t inner_bytes, uint64_t rows, uint64_t pitch_bytes,
+                      uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swizzle) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) {
+        snprintf(g_last_cuda_error_text, sizeof(g_last_cuda_error_text), "cuTensorMapEncodeTiled entry point not found");
+        return BLZ_ERR_CUDA;
+    }
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (pitch_bytes & 15u) != 0) return BLZ_ERR_INVALID_ARGUMENT;
+    cuuint64_t dims[2] = {inner_bytes, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_inner, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda_error = static_cast<int>(r);
+        snprintf(g_last_cuda_error_text, sizeof(g_last_cuda_error_text), "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+        return BLZ_ERR_CUDA;
+    }
+    return BLZ_OK;
+}
+
+int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
+
+int64_t sf_katoms(int64_t K) { return round_up(ceil_div(K, 64), 4); }
+int64_t sf_row_blocks(int64_t rows) { return round_up(ceil_div(rows, 128), 2); }
+
+int elem_bytes_out(int dt) { return dt == BLZ_F32 ? 4 : 2; }
+
+int grid_for(int64_t work_items, int threads) {
+    int64_t g = ceil_div(work_items, threads);
+    if (g < 1) g = 1;
+    if (g > 148 * 16) g = 148 * 16;
+    return static_cast<int>(g);
+}
+
+using GemmKernelFn = void (*)(const CUtensorMap, const CUtensorMap, const GemmKernelParams);
+
+struct KernelChoice {
+    const void* fn;
+    int bn, stages, acc_bufs, smem, tmem_cols;
+};
+
+template <int KIND, int BN, int STAGES, int ACC>
+KernelChoice choice() {
+    using Cfg = GemmTileConfig<KIND, BN, STAGES, ACC>;
+    return KernelChoice{reinterpret_cast<const void*>(&gemm_tc_kernel<KIND, BN, STAGES, ACC>), BN, STAGES, ACC,
+                        static_cast<int>(Cfg::SMEM_BYTES), static_cast<int>(Cfg::TMEM_COLS)};
+}
+
+KernelChoice pick_kernel(int mma_kind, int bn) {
+    switch (mma_kind) {
+        case MMA_F16: return bn == 256 ? choice<MMA_F16, 256, 4, 2>() : choice<MMA_F16, 128, 6, 2>();
+        case MMA_F8: return bn == 256 ? choice<MMA_F8, 256, 4, 2>() : choice<MMA_F8, 128, 6, 2>();
+        default: return bn == 256 ? choice<MMA_NVF4, 256, 4, 1>() : choice<MMA_NVF4, 128, 5, 2>();
+    }
+}
+
+}  // namespace
+
+struct blz_gemm_plan {
+    blz_gemm_desc desc;
+    int device = 0, num_sms = 0;
+    int mma_kind = 0;
+    int variant = 0;
+    // operands as the kernels consume them (K-major, tiled scales)
+    const void* a_used = nullptr;
+    const void* b_used = nullptr;
+    const uint8_t* sfa_used = nullptr;
+    const uint8_t* sfb_used = nullptr;
+    int a_elem_bits = 16;
+    // device memory the plan owns
+    void* own_b = nullptr;
+    void* own_sfa = nullptr;
+    void* own_sfb = nullptr;
+    void* own_w16 = nullptr;      // W4A16: weights expanded to 16 bit, refreshed by every execute
+    void* own_split = nullptr;    // decode: fp32 partial sums
+    int* own_counters = nullptr;  // decode: per-tile arrival counters
+    int* status = nullptr;
+    int64_t owned_bytes = 0;
+    // tiled-kernel launch
+    KernelChoice kc{};
+    CUtensorMap tm_a{}, tm_b{};
+    GemmKernelParams kp{};
+    int grid = 0;
+    // decode-kernel launch
+    DecodeKernelParams dp{};
+    int decode_smem = 0, decode_stages = 0, decode_split = 1, decode_mma_n = 0, decode_tmem = 0;
+    const void* decode_fn = nullptr;
+    int launches = 1;
+};
+
+namespace {
+
+blz_status dev_alloc(blz_gemm_plan* p, void** out, int64_t bytes, bool zero) {
+    if (!cuda_ok(cudaMalloc(out, static_cast<size_t>(bytes)), "cudaMalloc")) return BLZ_ERR_OUT_OF_MEMORY;
+    p->owned_bytes += bytes;
+    if (zero) BLZ_CUDA(cudaMemset(*out, 0, static_cast<size_t>(bytes)));
+    return BLZ_OK;
+}
+
+blz_status validate(const blz_gemm_desc* d) {
+    if (!d) return BLZ_ERR_INVALID_ARGUMENT;
+    if (d->M <= 0 || d->N <= 0 || d->K <= 0) return BLZ_ERR_INVALID_ARGUMENT;
+    if (!d->A || !d->B) return BLZ_ERR_INVALID_ARGUMENT;
+    if (d->kind < BLZ_GEMM_F16 || d->kind > BLZ_GEMM_W4A16_BF16) return BLZ_ERR_INVALID_ARGUMENT;
+    if (d->out_dtype < BLZ_F16 || d->out_dtype > BLZ_F32) return BLZ_ERR_INVALID_ARGUMENT;
+    if (d->epilogue < BLZ_EPI_NONE || d->epilogue > BLZ_EPI_RESIDUAL_ADD) return BLZ_ERR_INVALID_ARGUMENT;
+    if (d->ldc != 0 && d->ldc < d->N) return BLZ_ERR_INVALID_ARGUMENT;
+    const bool fp4_a = d->kind == BLZ_GEMM_NVFP4;
+    const bool fp4_b = d->kind == BLZ_GEMM_NVFP4 || d->kind == BLZ_GEMM_W4A16_F16 || d->kind == BLZ_GEMM_W4A16_BF16;
+    if (fp4_a && !d->A_sf) return BLZ_ERR_INVALID_ARGUMENT;
+    if (fp4_b && !d->B_sf) return BLZ_ERR_INVALID_ARGUMENT;
+    // row pitches must be multiples of 16 bytes for the tensor maps
+    if (d->kind == BLZ_GEMM_F16 || d->kind == BLZ_GEMM_BF16) { if (d->K % 8) return BLZ_ERR_INVALID_ARGUMENT; }
+    else if (d->kind == BLZ_GEMM_FP8) { if (d->K % 16) return BLZ_ERR_INVALID_ARGUMENT; }
+    else { if (d->K % 32) return BLZ_ERR_INVALID_ARGUMENT; }
+    if (d->b_layout == BLZ_B_NMAJOR && fp4_b && (d->N % 2)) return BLZ_ERR_INVALID_ARGUMENT;
+    if ((d->epilogue == BLZ_EPI_BIAS || d->epilogue == BLZ_EPI_BIAS_SILU) && !d->bias) return BLZ_ERR_INVALID_ARGUMENT;
+    if (d->epilogue == BLZ_EPI_RESIDUAL_ADD && !d->residual) return BLZ_ERR_INVALID_ARGUMENT;
+    return BLZ_OK;
+}
+
+// B in Blaze's [K, N] convention -> plan-owned K-major copy (and tiled scales).
+blz_status prepare_b(blz_gemm_plan* p) {
+    const blz_gemm_desc& d = p->desc;
+    const bool fp4_b = d.kind == BLZ_GEMM_NVFP4 || d.kind == BLZ_GEMM_W4A16_F16 || d.kind == BLZ_GEMM_W4A16_BF16;
+    const int64_t N = d.N, K = d.K;
+    p->b_used = d.B;
+    if (d.b_layout == BLZ_B_NMAJOR) {
+        if (fp4_b) {
+            blz_status s = dev_alloc(p, &p->own_b, N * K / 2, false);
+            if (s) return s;
+            repack_fp4_kn_to_nk_kernel<<<grid_for((N / 2) * (K / 2), 256), 256>>>(static_cast<const uint8_t*>(d.B), static_cast<uint8_t*>(p->own_b),
+                                                                                   static_cast<int>(K), static_cast<int>(N));
+        } else {
+            const int eb = d.kind == BLZ_GEMM_FP8 ? 1 : 2;
+            blz_status s = dev_alloc(p, &p->own_b, N * K * eb, false);
+            if (s) return s;
+            dim3 grid(static_cast<unsigned>(ceil_div(N, 32)), static_cast<unsigned>(ceil_div(K, 32))), block(32, 8);
+            if (eb == 1) transpose_kn_to_nk_kernel<uint8_t><<<grid, block>>>(static_cast<const uint8_t*>(d.B), static_cast<uint8_t*>(p->own_b), static_cast<int>(K), static_cast<int>(N));
+            else transpose_kn_to_nk_kernel<uint16_t><<<grid, block>>>(static_cast<const uint16_t*>(d.B), static_cast<uint16_t*>(p->own_b), static_cast<int>(K), static_cast<int>(N));
+        }
+        BLZ_CUDA(cudaGetLastError());
+        p->b_used = p->own_b;
+    }
+    if (fp4_b) {
+        if (d.b_sf_layout == BLZ_SF_TILED && d.b_layout == BLZ_B_KMAJOR) {
+            p->sfb_used = static_cast<const uint8_t*>(d.B_sf);
+        } else {
+            const int64_t bytes = blz_tiled_scales_bytes(N, K);
+            blz_status s = dev_alloc(p, &p->own_sfb, bytes, true);
+            if (s) return s;
+            const int64_t kb = K / 16;
+            const int64_t row_stride = d.b_layout == BLZ_B_NMAJOR ? 1 : kb;
+            const int64_t blk_stride = d.b_layout == BLZ_B_NMAJOR ? N : 1;
+            tile_scales_kernel<<<grid_for(N * kb, 256), 256>>>(static_cast<const uint8_t*>(d.B_sf), N, kb, row_stride, blk_stride, sf_katoms(K),
+                                                                 static_cast<uint8_t*>(p->own_sfb));
+            BLZ_CUDA(cudaGetLastError());
+            p->sfb_used = static_cast<const uint8_t*>(p->own_sfb);
+        }
+    }
+    return BLZ_OK;
+}
+
+blz_status prepare_a_scales(blz_gemm_plan* p) {
+    const blz_gemm_desc& d = p->desc;
+    if (d.kind != BLZ_GEMM_NVFP4) return BLZ_OK;
+    if (d.a_sf_layout == BLZ_SF_TILED) { p->sfa_used = static_cast<const uint8_t*>(d.A_sf); return BLZ_OK; }
+    const int64_t bytes = blz_tiled_scales_bytes(d.M, d.K);
+    blz_status s = dev_alloc(p, &p->own_sfa, bytes, true);
+    if (s) return s;
+    const int64_t kb = d.K / 16;
+    tile_scales_kernel<<<grid_for(static_cast<int64_t>(d.M) * kb, 256), 256>>>(static_cast<const uint8_t*>(d.A_sf), d.M, kb, kb, 1, sf_katoms(d.K),
+                                                                                static_cast<uint8_t*>(p->own_sfa));
+    BLZ_CUDA(cudaGetLastError());
+    p->sfa_used = static_cast<const uint8_t*>(p->own_sfa);
+    return BLZ_OK;
+}
+
+// bytes of one operand row as the tensor core reads it
+int64_t row_bytes(int mma_kind, int64_t K) { return mma_kind == MMA_F16 ? K * 2 : mma_kind == MMA_F8 ? K : K / 2; }
+
+blz_status setup_tiled(blz_gemm_plan* p) {
+    const blz_gemm_desc& d = p->desc;
+    const int64_t rb = row_bytes(p->mma_kind, d.K);
+    const int m_tiles = static_cast<int>(ceil_div(d.M, 128));
+    int bn;
+    if (p->variant == BLZ_VARIANT_TILE_128x256) bn = 256;
+    else if (p->variant == BLZ_VARIANT_TILE_128x128) bn = 128;
+    else bn = (d.N >= 256 && m_tiles * ceil_div(d.N, 256) >= p->num_sms) ? 256 : 128;
+    p->variant = bn == 256 ? BLZ_VARIANT_TILE_128x256 : BLZ_VARIANT_TILE_128x128;
+    p->kc = pick_kernel(p->mma_kind, bn);
+    BLZ_CUDA(cudaFuncSetAttribute(p->kc.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, p->kc.smem));
+
+    blz_status s = encode_map(&p->tm_a, p->a_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.M), static_cast<uint64_t>(rb), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (s) return s;
+    s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rb), 128, static_cast<uint32_t>(bn), CU_TENSOR_MAP_SWIZZLE_128B);
+    if (s) return s;
+
+    GemmKernelParams& kp = p->kp;
+    kp.M = d.M; kp.N = d.N;
+    kp.m_tiles = m_tiles;
+    kp.n_tiles = static_cast<int>(ceil_div(d.N, bn));
+    kp.k_stages = static_cast<int>(ceil_div(rb, 128));
+    const uint32_t fmt = d.kind == BLZ_GEMM_BF16 || d.kind == BLZ_GEMM_W4A16_BF16 ? 1u : 0u;
+    kp.idesc = p->mma_kind == MMA_NVF4 ? make_idesc_nvf4(128, bn) : p->mma_kind == MMA_F8 ? make_idesc(0, 0, 128, bn) : make_idesc(fmt, fmt, 128, bn);
+    kp.sfa = p->sfa_used; kp.sfb = p->sfb_used;
+    kp.sf_katoms = static_cast<int>(sf_katoms(d.K));
+    kp.status = p->status;
+    const int64_t tiles = static_cast<int64_t>(kp.m_tiles) * kp.n_tiles;
+    p->grid = static_cast<int>(tiles < p->num_sms ? tiles : p->num_sms);
+    return BLZ_OK;
+}
+
+void fill_epilogue(const blz_gemm_plan* p, void* C, EpilogueParams& e) {
+    const blz_gemm_desc& d = p->desc;
+    e.C = C;
+    e.bias = d.bias; e.residual = d.residual;
+    e.ldc = d.ldc ? d.ldc : d.N; e.ldr = e.ldc;
+    e.alpha = d.a_scale * d.b_scale;
+    e.mode = d.epilogue;
+    e.out_type = d.out_dtype;
+    const int eb = elem_bytes_out(d.out_dtype);
+    bool vec = (reinterpret_cast<uintptr_t>(C) & 15u) == 0 && ((e.ldc * eb) & 15) == 0;
+    if (d.residual) vec = vec && (reinterpret_cast<uintptr_t>(d.residual) & 15u) == 0;
+    e.vec_ok = vec ? 1 : 0;
+}
+
+// ---- decode variant (NVFP4, M <= 64)
+
+struct DecodeChoice { const void* fn; int mma_n, stages, smem; };
+
+template <int MMA_N, int STAGES>
+DecodeChoice decode_choice() {
+    return DecodeChoice{reinterpret_cast<const void*>(&decode_nvf4_kernel<MMA_N, STAGES>), MMA_N, STAGES,
+                        static_cast<int>(DecodeConfig<MMA_N, STAGES>::SMEM_BYTES)};
+}
+
+int env_int(const char* name, int fallback) {
+    const char* v = getenv(name);
+    if (!v || !*v) return fallback;
+    return atoi(v);
+}
+
+blz_status decode_encode_x(blz_gemm_plan* p) {
+    const blz_gemm_desc& d = p->desc;
+    const int64_t rb = d.K / 2;
+    return encode_map(&p->tm_a, p->a_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.M), static_cast<uint64_t>(rb), 128,
+                      static_cast<uint32_t>(p->decode_mma_n), CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+blz_status decode_setup(blz_gemm_plan* p) {
+    const blz_gemm_desc& d = p->desc;
+    const DecodeChoice dc = d.M <= 16 ? decode_choice<16, 5>() : d.M <= 32 ? decode_choice<32, 4>() : decode_choice<64, 3>();
+    p->decode_fn = dc.fn; p->decode_mma_n = dc.mma_n; p->decode_stages = dc.stages; p->decode_smem = dc.smem;
+    p->decode_tmem = 128;
+    BLZ_CUDA(cudaFuncSetAttribute(dc.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, dc.smem));
+    const int64_t rb = d.K / 2;
+    blz_status s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rb), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (s) return s;
+    if ((s = decode_encode_x(p))) return s;
+
+    DecodeKernelParams& dp = p->dp;
+    dp.M = d.M; dp.N = d.N;
+    dp.n_tiles = static_cast<int>(ceil_div(d.N, 128));
+    dp.k_stages_total = static_cast<int>(ceil_div(rb, 128));
+    // Split K until every SM has a CTA, keeping at least two pipeline stages per split.
+    int want = env_int("BLZ_DECODE_SPLIT", 0);
+    if (want <= 0) want = static_cast<int>(ceil_div(p->num_sms, dp.n_tiles));
+    int max_split = dp.k_stages_total / 2 > 0 ? dp.k_stages_total / 2 : 1;
+    if (want > max_split) want = max_split;
+    if (want < 1) want = 1;
+    dp.stages_per_split = static_cast<int>(ceil_div(dp.k_stages_total, want));
+    dp.split = static_cast<int>(ceil_div(dp.k_stages_total, dp.stages_per_split));
+    dp.idesc = make_idesc_nvf4(128, static_cast<uint32_t>(dc.mma_n));
+    dp.sfw = p->sfb_used; dp.sfx = p->sfa_used;
+    dp.sf_katoms = static_cast<int>(sf_katoms(d.K));
+    dp.status = p->status;
+    p->decode_split = dp.split;
+    if (dp.split > 1) {
+        const int64_t bytes = static_cast<int64_t>(dp.split) * dc.mma_n * dp.n_tiles * 128 * sizeof(float);
+        if ((s = dev_alloc(p, &p->own_split, bytes, false))) return s;
+        void* c = nullptr;
+        if ((s = dev_alloc(p, &c, static_cast<int64_t>(dp.n_tiles) * sizeof(int), true))) return s;
+        p->own_counters = static_cast<int*>(c);
+    }
+    dp.partial = static_cast<float*>(p->own_split);
+    dp.counters = p->own_counters;
+    p->grid = dp.n_tiles * dp.split;
+    return BLZ_OK;
+}
+
+blz_status decode_rebind_a(blz_gemm_plan* p) {
+    p->dp.sfx = p->sfa_used;
+    return decode_encode_x(p);
+}
+
+blz_status decode_launch(blz_gemm_plan* p, void* C, cudaStream_t stream) {
+    DecodeKernelParams dp = p->dp;
+    fill_epilogue(p, C, dp.epi);
+    // tm_b maps the weights (the 128-row operand), tm_a the activations
+    void* args[3] = {&p->tm_b, &p->tm_a, &dp};
+    BLZ_CUDA(cudaLaunchKernel(p->decode_fn, dim3(p->grid), dim3(256), args, static_cast<size_t>(p->decode_smem), stream));
+    return BLZ_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int blz_version(void) { return 1; }
+
+const char* blz_status_string(blz_status s) {
+    switch (s) {
+        case BLZ_OK: return "ok";
+        case BLZ_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case BLZ_ERR_UNSUPPORTED: return "unsupported combination";
+        case BLZ_ERR_CUDA: return "CUDA call failed";
+        case BLZ_ERR_DEVICE_TIMEOUT: return "device-side wait ran out";
+        case BLZ_ERR_NO_DEVICE: return "no sm_100 device";
+        case BLZ_ERR_TOO_LARGE: return "size exceeds the stated maximum";
+        case BLZ_ERR_OUT_OF_MEMORY: return "out of device memory";
+    }
+    return "unknown status";
+}
+
+int blz_last_cuda_error(void) { return g_last_cuda_error; }
+const char* blz_last_cuda_error_string(void) { return g_last_cuda_error_text; }
+
+int64_t blz_tiled_scales_bytes(int64_t rows, int64_t K) {
+    if (rows <= 0 || K <= 0) return 0;
+    return sf_row_blocks(rows) * sf_katoms(K) * 512;
+}
+
+blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_plan) {
+    if (!out_plan) return BLZ_ERR_INVALID_ARGUMENT;
+    *out_plan = nullptr;
+    blz_status s = validate(desc);
+    if (s) return s;
+    int dev = 0;
+    if (!cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return BLZ_ERR_NO_DEVICE;
+    cudaDeviceProp prop;
+    if (!cuda_ok(cudaGetDeviceProperties(&prop, dev), "cudaGetDeviceProperties")) return BLZ_ERR_NO_DEVICE;
+    if (prop.major != 10) return BLZ_ERR_NO_DEVICE;
+
+    blz_gemm_plan* p = new (std::nothrow) blz_gemm_plan();
+    if (!p) return BLZ_ERR_OUT_OF_MEMORY;
+    p->desc = *desc;
+    if (p->desc.a_scale == 0.0f) p->desc.a_scale = 1.0f;
+    if (p->desc.b_scale == 0.0f) p->desc.b_scale = 1.0f;
+    p->device = dev;
+    p->num_sms = prop.multiProcessorCount;
+    p->variant = desc->variant;
+    switch (desc->kind) {
+        case BLZ_GEMM_F16: case BLZ_GEMM_BF16: case BLZ_GEMM_W4A16_F16: case BLZ_GEMM_W4A16_BF16: p->mma_kind = MMA_F16; break;
+        case BLZ_GEMM_FP8: p->mma_kind = MMA_F8; break;
+        default: p->mma_kind = MMA_NVF4; break;
+    }
+    const bool w4a16 = desc->kind == BLZ_GEMM_W4A16_F16 || desc->kind == BLZ_GEMM_W4A16_BF16;
+
+    auto fail = [&](blz_status st) { blz_gemm_plan_destroy(p); return st; };
+
+    void* st_mem = nullptr;
+    if ((s = dev_alloc(p, &st_mem, sizeof(int), true))) return fail(s);
+    p->status = static_cast<int*>(st_mem);
+    p->a_used = desc->A;
+    if ((s = prepare_b(p))) return fail(s);
+    if ((s = prepare_a_scales(p))) return fail(s);
+
+    if (w4a16) {
+        // The tensor core consumes 16-bit weights: every execute expands the packed weights into
+        // this buffer (q * block scale, exact in 16 bits); the fp32 tensor scale goes into alpha.
+        if ((s = dev_alloc(p, &p->own_w16, static_cast<int64_t>(desc->N) * desc->K * 2, false))) return fail(s);
+        p->launches = 2;
+    }
+
+    const bool want_decode = desc->variant == BLZ_VARIANT_DECODE ||
+                             (desc->variant == BLZ_VARIANT_AUTO && desc->kind == BLZ_GEMM_NVFP4 && desc->M <= 64);
+    if (want_decode) {
+        if (desc->kind != BLZ_GEMM_NVFP4 || desc->M > 64) return fail(BLZ_ERR_UNSUPPORTED);
+        p->variant = BLZ_VARIANT_DECODE;
+        if ((s = decode_setup(p))) return fail(s);
+    } else {
+        const void* b_tc = w4a16 ? p->own_w16 : p->b_used;
+        const void* keep = p->b_used;
+        p->b_used = b_tc;
+        s = setup_tiled(p);
+        p->b_used = keep;
+        if (s) return fail(s);
+    }
+    if (!cuda_ok(cudaDeviceSynchronize(), "cudaDeviceSynchronize")) return fail(BLZ_ERR_CUDA);
+    *out_plan = p;
+    return BLZ_OK;
+}
+
+blz_status blz_gemm_execute(blz_gemm_plan* p, void* C, void* stream_v) {
+    if (!p || !C) return BLZ_ERR_INVALID_ARGUMENT;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const blz_gemm_desc& d = p->desc;
+    if (p->variant == BLZ_VARIANT_DECODE) return decode_launch(p, C, stream);
+
+    if (p->own_w16) {
+        const int64_t blocks16 = static_cast<int64_t>(d.N) * (d.K / 16);
+        if (d.kind == BLZ_GEMM_W4A16_F16)
+            dequant_nvfp4_kernel<__half><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<__half*>(p->own_w16));
+        else
+            dequant_nvfp4_kernel<__nv_bfloat16><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<__nv_bfloat16*>(p->own_w16));
+        BLZ_CUDA(cudaGetLastError());
+    }
+    GemmKernelParams kp = p->kp;
+    fill_epilogue(p, C, kp.epi);
+    void* args[3] = {&p->tm_a, &p->tm_b, &kp};
+    BLZ_CUDA(cudaLaunchKernel(p->kc.fn, dim3(p->grid), dim3(256), args, static_cast<size_t>(p->kc.smem), stream));
+    return BLZ_OK;
+}
+
+blz_status blz_gemm_plan_set_a(blz_gemm_plan* p, const void* A, const void* A_sf, float a_scale) {
+    if (!p || !A) return BLZ_ERR_INVALID_ARGUMENT;
+    blz_gemm_desc& d = p->desc;
+    if (d.kind == BLZ_GEMM_NVFP4) {
+        if (!A_sf || d.a_sf_layout != BLZ_SF_TILED) return BLZ_ERR_INVALID_ARGUMENT;
+        d.A_sf = A_sf;
+        p->sfa_used = static_cast<const uint8_t*>(A_sf);
+    }
+    d.A = A;
+    p->a_used = A;
+    if (a_scale != 0.0f) d.a_scale = a_scale;
+    if (p->variant == BLZ_VARIANT_DECODE) return decode_rebind_a(p);
+    const int64_t rb = row_bytes(p->mma_kind, d.K);
+    blz_status s = encode_map(&p->tm_a, A, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.M), static_cast<uint64_t>(rb), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (s) return s;
+    p->kp.sfa = p->sfa_used;
+    return BLZ_OK;
+}
+
+blz_status blz_gemm_plan_check(blz_gemm_plan* p, void* stream_v) {
+    if (!p) return BLZ_ERR_INVALID_ARGUMENT;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    BLZ_CUDA(cudaStreamSynchronize(stream));
+    int word = 0;
+    BLZ_CUDA(cudaMemcpy(&word, p->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (word != 0) {
+        g_last_cuda_error = word;
+        snprintf(g_last_cuda_error_text, sizeof(g_last_cuda_error_text), "device error word 0x%x", word);
+        BLZ_CUDA(cudaMemset(p->status, 0, sizeof(int)));
+        return BLZ_ERR_DEVICE_TIMEOUT;
+    }
+    return BLZ_OK;
+}
+
+blz_status blz_gemm_plan_info(const blz_gemm_plan* p, blz_plan_info* info) {
+    if (!p || !info) return BLZ_ERR_INVALID_ARGUMENT;
+    memset(info, 0, sizeof(*info));
+    info->variant = p->variant;
+    if (p->variant == BLZ_VARIANT_DECODE) {
+        info->tile_m = p->decode_mma_n; info->tile_n = 128;
+        info->stages = p->decode_stages; info->split_k = p->decode_split;
+        info->grid = p->grid; info->smem_bytes = p->decode_smem; info->tmem_cols = p->decode_tmem;
+    } else {
+        info->tile_m = 128; info->tile_n = p->kc.bn;
+        info->stages = p->kc.stages; info->split_k = 1;
+        info->grid = p->grid; info->smem_bytes = p->kc.smem; info->tmem_cols = p->kc.tmem_cols;
+    }
+    info->launches = p->launches;
+    info->workspace_bytes = p->owned_bytes;
+    return BLZ_OK;
+}
+
+blz_status blz_gemm_plan_destroy(blz_gemm_plan* p) {
+    if (!p) return BLZ_OK;
+    cudaFree(p->own_b); cudaFree(p->own_sfa); cudaFree(p->own_sfb); cudaFree(p->own_w16);
+    cudaFree(p->own_split); cudaFree(p->own_counters); cudaFree(p->status);
+    (void)cudaGetLastError();
+    delete p;
+    return BLZ_OK;
+}
+
+blz_status blz_gemm_launch(const blz_gemm_desc* desc, void* C, void* stream) {
+    blz_gemm_plan* p = nullptr;
+    blz_status s = blz_gemm_plan_create(desc, &p);
+    if (s) return s;
+    s = blz_gemm_execute(p, C, stream);
+    if (s == BLZ_OK) s = blz_gemm_plan_check(p, stream);
+    blz_gemm_plan_destroy(p);
+    return s;
+}
+
+// ------------------------------------------------------------ preparation
+
+blz_status blz_amax(const void* x, int32_t x_dtype, int64_t n, float* d_amax, void* stream_v) {
+    if (!x || !d_amax || n <= 0) return BLZ_ERR_INVALID_ARGUMENT;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const int g = grid_for(n, 256 * 8);
+    if (x_dtype == BLZ_F32) amax_kernel<float><<<g, 256, 0, stream>>>(static_cast<const float*>(x), n, d_amax);
+    else if (x_dtype == BLZ_F16) amax_kernel<__half><<<g, 256, 0, stream>>>(static_cast<const __half*>(x), n, d_amax);
+    else if (x_dtype == BLZ_BF16) amax_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), n, d_amax);
+    else return BLZ_ERR_INVALID_ARGUMENT;
+    BLZ_CUDA(cudaGetLastError());
+    return BLZ_OK;
+}
+
+blz_status blz_quantize_fp8(const void* x, int32_t x_dtype, int64_t n, const float* d_amax, uint8_t* q, float* d_scales, void* stream_v) {
+    if (!x || !d_amax || !q || n <= 0) return BLZ_ERR_INVALID_ARGUMENT;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const int g = grid_for(n, 256 * 4);
+    if (x_dtype == BLZ_F32) quantize_fp8_kernel<float><<<g, 256, 0, stream>>>(static_cast<const float*>(x), n, d_amax, q, d_scales);
+    else if (x_dtype == BLZ_F16) quantize_fp8_kernel<__half><<<g, 256, 0, stream>>>(static_cast<const __half*>(x), n, d_amax, q, d_scales);
+    else if (x_dtype == BLZ_BF16) quantize_fp8_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), n, d_amax, q, d_scales);
+    else return BLZ_ERR_INVALID_ARGUMENT;
+    BLZ_CUDA(cudaGetLastError());
+    return BLZ_OK;
+}
+
+blz_status blz_quantize_nvfp4(const void* x, int32_t x_dtype, int64_t rows, int64_t K, const float* d_amax, uint8_t* data, uint8_t* sf,
+                              int32_t sf_layout, float* d_global, void* stream_v) {
+    if (!x || !d_amax || !data || !sf || rows <= 0 || K <= 0 || (K % 16) != 0) return BLZ_ERR_INVALID_ARGUMENT;
+    if ((reinterpret_cast<uintptr_t>(data) & 7u) != 0) return BLZ_ERR_INVALID_ARGUMENT;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const int tiled = sf_layout == BLZ_SF_TILED ? 1 : 0;
+    if (tiled) BLZ_CUDA(cudaMemsetAsync(sf, 0, static_cast<size_t>(blz_tiled_scales_bytes(rows, K)), stream));
+    const int g = grid_for(rows * (K / 16), 256);
+    const long long ka = sf_katoms(K);
+    if (x_dtype == BLZ_F32) quantize_nvfp4_kernel<float><<<g, 256, 0, stream>>>(static_cast<const float*>(x), rows, K, d_amax, data, sf, tiled, ka, d_global);
+    else if (x_dtype == BLZ_F16) quantize_nvfp4_kernel<__half><<<g, 256, 0, stream>>>(static_cast<const __half*>(x), rows, K, d_amax, data, sf, tiled, ka, d_global);
+    else if (x_dtype == BLZ_BF16) quantize_nvfp4_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, K, d_amax, data, sf, tiled, ka, d_global);
+    else return BLZ_ERR_INVALID_ARGUMENT;
+    BLZ_CUDA(cudaGetLastError());
+    return BLZ_OK;
+}
+
+blz_status blz_tile_scales(const uint8_t* sf, int64_t rows, int64_t K, int64_t row_stride, int64_t blk_stride, uint8_t* tiled, void* stream_v) {
+    if (!sf || !tiled || rows <= 0 || K <= 0 || (K % 16) != 0) return BLZ_ERR_INVALID_ARGUMENT;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    BLZ_CUDA(cudaMemsetAsync(tiled, 0, static_cast<size_t>(blz_tiled_scales_bytes(rows, K)), stream));
+    const int64_t kb = K / 16;
+    tile_scales_kernel<<<grid_for(rows * kb, 256), 256, 0, stream>>>(sf, rows, kb, row_stride, blk_stride, sf_katoms(K), tiled);
+    BLZ_CUDA(cudaGetLastError());
+    return BLZ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,177 @@
+// prep_kernels.cuh -- operand preparation around the GEMM: scale-factor tiling, layout
+// repacking for operands given in Blaze's [K, N] convention, quantisers and the NVFP4 -> 16-bit
+// dequantiser.  All HBM-bound byte work: one pass, coalesced, grid sized by the problem.
+//
+// Counterparts in Blaze: interleave_scales_kernel / interleave_scales_transposed_kernel
+// (src/kernels/gemm_fp4_blkscaled_sm100.cu:59-104) and fp16_to_e4m3_kernel
+// (src/kernels/gemm_mixed_sm100.cu:312-321).  Blaze has no quantiser; the arithmetic here is
+// the definition the CPU oracle states, operation for operation, so results are bit-identical.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+namespace blz {
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+__device__ __forceinline__ uint8_t f32_to_e4m3_bits(float v) {
+    return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+__device__ __forceinline__ float e4m3_bits_to_f32(uint8_t b) {
+    __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(b), __NV_E4M3);
+    return __half2float(__half(h));
+}
+__device__ __forceinline__ uint8_t f32_to_e2m1_bits(float v) {
+    return static_cast<uint8_t>(__nv_cvt_float_to_fp4(v, __NV_E2M1, cudaRoundNearest)) & 0xF;
+}
+// magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6 with the sign in bit 3
+__device__ __forceinline__ float e2m1_bits_to_f32(uint32_t n) {
+    const uint32_t e = (n >> 1) & 3u, m = n & 1u;
+    float v = (e == 0) ? 0.5f * static_cast<float>(m) : __uint_as_float(((e + 126u) << 23) | (m << 22));
+    return (n & 8u) ? -v : v;
+}
+
+// byte offset of the scale of (row r, 16-value K block b) in the tiled layout
+__host__ __device__ __forceinline__ long long tiled_sf_offset(long long r, long long b, long long katoms) {
+    return ((r / 128) * katoms + b / 4) * 512 + (r % 32) * 16 + ((r % 128) / 32) * 4 + (b % 4);
+}
+
+// ---- scale tiling: in(r, b) = sf[r*row_stride + b*blk_stride]; `tiled` was zeroed beforehand.
+__global__ void tile_scales_kernel(const uint8_t* __restrict__ sf, long long rows, long long kblocks,
+                                   long long row_stride, long long blk_stride, long long katoms,
+                                   uint8_t* __restrict__ tiled) {
+    const long long total = rows * kblocks;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        long long r, b;
+        if (blk_stride == 1) { r = i / kblocks; b = i % kblocks; }   // consecutive threads walk the contiguous dimension
+        else { b = i / rows; r = i % rows; }
+        tiled[tiled_sf_offset(r, b, katoms)] = sf[r * row_stride + b * blk_stride];
+    }
+}
+
+// ---- [K, N] -> [N, K] for 1- or 2-byte elements (shared-memory tile transpose)
+template <typename T>
+__global__ void transpose_kn_to_nk_kernel(const T* __restrict__ in, T* __restrict__ out, int K, int N) {
+    __shared__ T tile[32][33];
+    const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        const int k = k0 + j, n = n0 + threadIdx.x;
+        if (k < K && n < N) tile[j][threadIdx.x] = in[static_cast<long long>(k) * N + n];
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        const int n = n0 + j, k = k0 + threadIdx.x;
+        if (n < N && k < K) out[static_cast<long long>(n) * K + k] = tile[threadIdx.x][j];
+    }
+}
+
+// ---- packed E2M1 [K, N/2] (two N-neighbours per byte, even N in the low nibble)
+//      -> [N, K/2] (two K-neighbours per byte, even K in the low nibble)
+__global__ void repack_fp4_kn_to_nk_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int K, int N) {
+    // one thread per output byte pair: handles n = 2*np, 2*np+1 and k = 2*kp, 2*kp+1
+    const long long total = static_cast<long long>(N / 2) * (K / 2);
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int np = static_cast<int>(i % (N / 2)), kp = static_cast<int>(i / (N / 2));
+        const uint8_t r0 = in[static_cast<long long>(2 * kp) * (N / 2) + np];       // k even: n even (lo), n odd (hi)
+        const uint8_t r1 = in[static_cast<long long>(2 * kp + 1) * (N / 2) + np];   // k odd
+        out[static_cast<long long>(2 * np) * (K / 2) + kp] = static_cast<uint8_t>((r0 & 0xF) | ((r1 & 0xF) << 4));
+        out[static_cast<long long>(2 * np + 1) * (K / 2) + kp] = static_cast<uint8_t>((r0 >> 4) | (r1 & 0xF0));
+    }
+}
+
+// ---- amax: |x| maximum, combined into *out with an integer max on the bit pattern
+template <typename T>
+__global__ void amax_kernel(const T* __restrict__ x, long long n, float* __restrict__ out) {
+    float m = 0.0f;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+        m = fmaxf(m, fabsf(to_f32<T>(x[i])));
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    __shared__ float wm[32];
+    if ((threadIdx.x & 31) == 0) wm[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        m = threadIdx.x < (blockDim.x >> 5) ? wm[threadIdx.x] : 0.0f;
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(m));
+    }
+}
+
+// ---- FP8 per tensor: s = 448/amax (1 when amax == 0); q = e4m3_rn(x*s); scales = {s, 1/s}
+template <typename T>
+__global__ void quantize_fp8_kernel(const T* __restrict__ x, long long n, const float* __restrict__ amax,
+                                    uint8_t* __restrict__ q, float* __restrict__ scales) {
+    const float am = *amax;
+    const float s = am > 0.0f ? __fdiv_rn(448.0f, am) : 1.0f;
+    if (blockIdx.x == 0 && threadIdx.x == 0 && scales != nullptr) { scales[0] = s; scales[1] = __fdiv_rn(1.0f, s); }
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+        q[i] = f32_to_e4m3_bits(__fmul_rn(to_f32<T>(x[i]), s));
+}
+
+// ---- NVFP4: one thread per 16-value block
+template <typename T>
+__global__ void quantize_nvfp4_kernel(const T* __restrict__ x, long long rows, long long K, const float* __restrict__ amax,
+                                      uint8_t* __restrict__ data, uint8_t* __restrict__ sf, int tiled, long long katoms,
+                                      float* __restrict__ g_out) {
+    const float am_all = *amax;
+    const float g = am_all > 0.0f ? __fdiv_rn(am_all, 2688.0f) : 1.0f;   // 6 * 448
+    if (blockIdx.x == 0 && threadIdx.x == 0 && g_out != nullptr) *g_out = g;
+    const long long kb = K / 16, total = rows * kb;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long r = i / kb, b = i % kb;
+        const T* p = x + r * K + b * 16;
+        float v[16];
+        float am = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { v[j] = to_f32<T>(p[j]); am = fmaxf(am, fabsf(v[j])); }
+        const uint8_t s8 = f32_to_e4m3_bits(__fdiv_rn(__fdiv_rn(am, 6.0f), g));
+        const float sfv = e4m3_bits_to_f32(s8);
+        sf[tiled ? tiled_sf_offset(r, b, katoms) : (r * kb + b)] = s8;
+        const float d = __fmul_rn(g, sfv);
+        uint32_t w[2] = {0u, 0u};
+        if (sfv != 0.0f) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                w[j >> 3] |= static_cast<uint32_t>(f32_to_e2m1_bits(__fdiv_rn(v[j], d))) << (4 * (j & 7));
+        }
+        *reinterpret_cast<uint2*>(data + r * (K / 2) + b * 8) = make_uint2(w[0], w[1]);
+    }
+}
+
+// ---- NVFP4 weights -> 16-bit values q*sf (exact: 6 significant bits), global scale left out.
+//      data [rows, K/2], sf read through the tiled layout; out [rows, K].
+template <typename T>
+__global__ void dequant_nvfp4_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ sf_tiled, long long katoms,
+                                     long long rows, long long K, T* __restrict__ out) {
+    const long long kb = K / 16, total = rows * kb;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long r = i / kb, b = i % kb;
+        const float s = e4m3_bits_to_f32(sf_tiled[tiled_sf_offset(r, b, katoms)]);
+        const uint2 w = *reinterpret_cast<const uint2*>(data + r * (K / 2) + b * 8);
+        T o[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const uint32_t n = ((j < 8 ? w.x : w.y) >> (4 * (j & 7))) & 0xFu;
+            const float f = e2m1_bits_to_f32(n) * s;
+            if constexpr (sizeof(T) == 2 && std::is_same<T, __half>::value) o[j] = __float2half_rn(f);
+            else o[j] = __float2bfloat16_rn(f);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(out + r * K + b * 16);
+        dst[0] = *reinterpret_cast<uint4*>(&o[0]);
+        dst[1] = *reinterpret_cast<uint4*>(&o[8]);
+    }
+}
+
+}  // namespace blz

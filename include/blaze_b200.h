@@ -1,0 +1,187 @@
+/*
+ * blaze_b200.h -- C ABI of the B200 (sm_100a) GEMM library.
+ *
+ * Plain C: pointers, sizes, enums.  Every data pointer is a DEVICE pointer owned by the caller
+ * unless stated otherwise; `stream` arguments are cudaStream_t handles passed as void*.
+ * Every function returns a blz_status; nothing here calls exit() or prints.
+ *
+ * The entry points replace, one for one, the host API Blaze declares under include/gemm/
+ * (citations are paths inside the Blaze project):
+ *
+ *   blz_gemm_plan_create   <- create_fp8_gemm_plan            include/gemm/fp8_gemm_sm100.cuh:84
+ *                             create_fp4_gemm_plan            include/gemm/fp4_gemm_sm100.cuh:114
+ *                             create_fp4_blkscaled_gemm_plan  include/gemm/fp4_blkscaled_gemm_sm100.cuh:155
+ *                             create_fp4_blkscaled_persistent_gemm_plan                      ...:198
+ *                             create_mixed_gemm_plan          include/gemm/mixed_gemm_sm100.cuh:123
+ *   blz_gemm_execute       <- execute_fp8_gemm :95, execute_fp4_gemm :126,
+ *                             execute_fp4_blkscaled_gemm :163, execute_fp4_blkscaled_persistent_gemm :206,
+ *                             execute_mixed_gemm :136
+ *   blz_gemm_plan_destroy  <- destroy_*_plan (same headers)
+ *   blz_gemm_launch        <- launch_gemm_fp8 :63, launch_gemm_fp4 :93, launch_gemm_fp4_blkscaled :138,
+ *                             launch_gemm_fp4_blkscaled_persistent :180, launch_gemm_mixed :76
+ *   blz_tile_scales        <- interleave_scales_kernel / interleave_scales_transposed_kernel
+ *                             src/kernels/gemm_fp4_blkscaled_sm100.cu:59-104
+ *
+ * The C++ functions of namespace blaze with Blaze's own signatures are thin shims over this ABI
+ * (include/gemm/ *.cuh in this repository).
+ */
+#ifndef BLAZE_B200_H
+#define BLAZE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum blz_status {
+    BLZ_OK = 0,
+    BLZ_ERR_INVALID_ARGUMENT = 1, /* null pointer, non-positive size, misaligned pointer or pitch */
+    BLZ_ERR_UNSUPPORTED = 2,      /* a combination this build has no kernel for */
+    BLZ_ERR_CUDA = 3,             /* a CUDA runtime / driver call failed; see blz_last_cuda_error */
+    BLZ_ERR_DEVICE_TIMEOUT = 4,   /* a kernel gave up on a bounded wait; its output is invalid */
+    BLZ_ERR_NO_DEVICE = 5,        /* no sm_100 device is current */
+    BLZ_ERR_TOO_LARGE = 6,        /* exceeds a stated maximum */
+    BLZ_ERR_OUT_OF_MEMORY = 7
+} blz_status;
+
+/* What the two operands are.  A is always [M, K] row-major. */
+typedef enum blz_gemm_kind {
+    BLZ_GEMM_F16 = 0,       /* fp16 x fp16 */
+    BLZ_GEMM_BF16 = 1,      /* bf16 x bf16 */
+    BLZ_GEMM_FP8 = 2,       /* E4M3 x E4M3, one fp32 scale per tensor */
+    BLZ_GEMM_NVFP4 = 3,     /* E2M1 x E2M1, E4M3 scale per 16 values along K, fp32 scale per tensor */
+    BLZ_GEMM_W4A16_F16 = 4, /* fp16 activations x NVFP4 weights */
+    BLZ_GEMM_W4A16_BF16 = 5 /* bf16 activations x NVFP4 weights */
+} blz_gemm_kind;
+
+typedef enum blz_dtype { BLZ_F16 = 0, BLZ_BF16 = 1, BLZ_F32 = 2 } blz_dtype;
+
+/* Order: scale -> bias -> SiLU / residual -> narrow (Blaze: src/kernels/gemm_mixed_sm100.cu:202-229). */
+typedef enum blz_epilogue {
+    BLZ_EPI_NONE = 0,
+    BLZ_EPI_BIAS = 1,
+    BLZ_EPI_SILU = 2,
+    BLZ_EPI_BIAS_SILU = 3,
+    BLZ_EPI_RESIDUAL_ADD = 4
+} blz_epilogue;
+
+typedef enum blz_b_layout {
+    BLZ_B_KMAJOR = 0, /* B stored [N, K] row-major (K contiguous): used as is */
+    BLZ_B_NMAJOR = 1  /* B stored [K, N] row-major as Blaze's headers describe it; the plan keeps a
+                         K-major copy.  For 4-bit data two N-neighbours share a byte. */
+} blz_b_layout;
+
+typedef enum blz_sf_layout {
+    BLZ_SF_ROWMAJOR = 0, /* A: [M, K/16]; B: [N, K/16] (K-major B) or [K/16, N] (N-major B) */
+    BLZ_SF_TILED = 1     /* [ceil(rows/128)][katoms][512 bytes], see blz_tile_scales */
+} blz_sf_layout;
+
+typedef enum blz_variant {
+    BLZ_VARIANT_AUTO = 0,
+    BLZ_VARIANT_TILE_128x128 = 1, /* 128x128 tiles, two accumulator buffers */
+    BLZ_VARIANT_TILE_128x256 = 2, /* 128x256 tiles */
+    BLZ_VARIANT_DECODE = 3        /* weights as the 128-row operand, M <= 64, split along K */
+} blz_variant;
+
+typedef struct blz_gemm_desc {
+    int32_t kind;         /* blz_gemm_kind */
+    int32_t out_dtype;    /* blz_dtype of C, bias and residual (bias is fp32 when C is fp32) */
+    int32_t epilogue;     /* blz_epilogue */
+    int32_t variant;      /* blz_variant, 0 = choose */
+    int32_t M, N, K;      /* in elements */
+    int32_t b_layout;     /* blz_b_layout */
+    int32_t a_sf_layout;  /* blz_sf_layout (NVFP4 A only) */
+    int32_t b_sf_layout;  /* blz_sf_layout (NVFP4 B / W4A16 weights) */
+    const void* A;        /* [M, K] values, or packed E2M1 [M, K/2] (even K index in the low nibble) */
+    const void* A_sf;     /* E4M3 block scales of A, or null */
+    const void* B;        /* see b_layout */
+    const void* B_sf;     /* E4M3 block scales of B, or null */
+    float a_scale;        /* dequantisation multiplier of A: x ~ code * a_scale (1 for fp16/bf16) */
+    float b_scale;        /* same for B.  alpha = a_scale * b_scale is applied to the accumulator */
+    const void* bias;     /* [N] or null */
+    const void* residual; /* [M, ldc] or null */
+    int64_t ldc;          /* row pitch of C and residual in elements; 0 = N */
+} blz_gemm_desc;
+
+typedef struct blz_plan_info {
+    int32_t variant;          /* blz_variant actually used */
+    int32_t tile_m, tile_n;   /* output tile of one CTA */
+    int32_t stages;           /* shared-memory pipeline depth */
+    int32_t split_k;          /* 1 unless the decode variant splits K */
+    int32_t grid;             /* CTAs launched */
+    int32_t smem_bytes;       /* dynamic shared memory per CTA */
+    int32_t tmem_cols;        /* tensor-memory columns per CTA */
+    int32_t launches;         /* kernels one blz_gemm_execute launches */
+    int64_t workspace_bytes;  /* device memory the plan owns */
+} blz_plan_info;
+
+typedef struct blz_gemm_plan blz_gemm_plan;
+
+/* Version of this ABI (increments on incompatible change). */
+int blz_version(void);
+const char* blz_status_string(blz_status s);
+/* cudaError_t / CUresult of the last failed CUDA call on this thread, and its text. */
+int blz_last_cuda_error(void);
+const char* blz_last_cuda_error_string(void);
+
+/* Builds everything one GEMM needs ahead of time: operand repacking for the layouts above,
+ * tensor maps, workspace, kernel choice.  Uses the current device; synchronises the device
+ * before returning.  The operand pointers in `desc` must stay valid while the plan lives. */
+blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_plan);
+
+/* Launches the planned GEMM into C ([M, ldc], the plan's output type).  Asynchronous on `stream`,
+ * allocates nothing.  One plan must not run on two streams at the same time. */
+blz_status blz_gemm_execute(blz_gemm_plan* plan, void* C, void* stream);
+
+/* Rebinds the A operand (same shape, dtype and scale layout; NVFP4 scales must be BLZ_SF_TILED)
+ * without touching anything else.  Host-side only: re-encodes one tensor map. */
+blz_status blz_gemm_plan_set_a(blz_gemm_plan* plan, const void* A, const void* A_sf, float a_scale);
+
+/* Synchronises `stream` and reports BLZ_ERR_DEVICE_TIMEOUT if any launch of this plan gave up
+ * on a device-side wait since the last check (the error word is cleared). */
+blz_status blz_gemm_plan_check(blz_gemm_plan* plan, void* stream);
+
+blz_status blz_gemm_plan_info(const blz_gemm_plan* plan, blz_plan_info* info);
+
+/* Frees the plan and what it owns.  Null is accepted. */
+blz_status blz_gemm_plan_destroy(blz_gemm_plan* plan);
+
+/* plan_create + execute + stream sync + destroy, for callers that run a shape once. */
+blz_status blz_gemm_launch(const blz_gemm_desc* desc, void* C, void* stream);
+
+/* ---- operand preparation (device kernels, asynchronous on `stream`) ---- */
+
+/* |x| maximum of n values into *d_amax (device float; combined with its previous content, so
+ * zero it first).  x_dtype: BLZ_F32, BLZ_F16 or BLZ_BF16. */
+blz_status blz_amax(const void* x, int32_t x_dtype, int64_t n, float* d_amax, void* stream);
+
+/* Per-tensor E4M3 quantisation: s = 448 / *d_amax (1 if amax is 0); q = e4m3_rn(x * s);
+ * writes the dequantisation multiplier 1/s ... as two floats d_scales[0] = s, d_scales[1] = 1/s. */
+blz_status blz_quantize_fp8(const void* x, int32_t x_dtype, int64_t n, const float* d_amax,
+                            uint8_t* q, float* d_scales, void* stream);
+
+/* Two-level NVFP4 quantisation of a [rows, K] row-major matrix, K a multiple of 16:
+ *   g = *d_amax / (6*448) (1 if amax is 0); per 16 values along K sf = e4m3_rn((amax_blk/6)/g);
+ *   q = e2m1_rn(x / (g*float(sf))), zero when sf is zero.
+ * data: [rows, K/2]; sf: row-major [rows, K/16] or tiled (sf_layout), tiled buffers must be
+ * blz_tiled_scales_bytes(rows, K) long and are fully written; *d_global = g. */
+blz_status blz_quantize_nvfp4(const void* x, int32_t x_dtype, int64_t rows, int64_t K, const float* d_amax,
+                              uint8_t* data, uint8_t* sf, int32_t sf_layout, float* d_global, void* stream);
+
+/* Size of the tiled scale-factor array for a [rows, K] operand:
+ * ceil(rows/128) row blocks x (ceil(K/64) rounded up to a multiple of 4) atoms x 512 bytes. */
+int64_t blz_tiled_scales_bytes(int64_t rows, int64_t K);
+
+/* Row-major E4M3 scales -> tiled.  The scale of (row r, K block b) is read from
+ * sf[r*row_stride + b*blk_stride] and written to byte
+ *   ((r/128)*katoms + b/4)*512 + (r%32)*16 + ((r%128)/32)*4 + b%4,
+ * every other byte of `tiled` is set to zero. */
+blz_status blz_tile_scales(const uint8_t* sf, int64_t rows, int64_t K, int64_t row_stride, int64_t blk_stride,
+                           uint8_t* tiled, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BLAZE_B200_H */

@@ -10,6 +10,8 @@ Outputs
   oracle/_ref/libblaze_ref_naive.so  Blaze's own tests/test_gemm_naive.cu compiled where it lies
                                    (its main() renamed), exporting gemm_cpu_fp16 and
                                    init_random_fp16; only built when the reference tree is present
+  oracle/_ref/test_gemm, bench_gemm  Blaze's tests/test_gemm.cu and benchmarks/bench_gemm.cu compiled
+                                   unchanged against this repository's headers and library
 """
 from __future__ import annotations
 
@@ -75,6 +77,32 @@ def build_ref(force: bool = False) -> str | None:
     return out
 
 
+def build_ref_programs(force: bool = False) -> list[str]:
+    """Blaze's own tests/test_gemm.cu and benchmarks/bench_gemm.cu, compiled unchanged against THIS
+    repository's include/gemm headers and linked to blaze_b200/libblaze_b200.so (the drop-in check).
+    Outputs only into oracle/_ref; skipped when the reference tree or the library is absent."""
+    root = os.path.dirname(HERE)
+    lib_dir = os.path.join(root, "blaze_b200")
+    lib = os.path.join(lib_dir, "libblaze_b200.so")
+    out_dir = os.path.join(HERE, "_ref")
+    built = []
+    if not os.path.exists(lib) or not os.path.exists(NVCC):
+        return built
+    for rel, name in (("tests/test_gemm.cu", "test_gemm"), ("benchmarks/bench_gemm.cu", "bench_gemm")):
+        src = os.path.join(REF_ROOT, rel)
+        out = os.path.join(out_dir, name)
+        if not os.path.exists(src):
+            if os.path.exists(out):
+                built.append(out)
+            continue
+        os.makedirs(out_dir, exist_ok=True)
+        if force or _newer([src, lib], out):
+            _run([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17", "-w", "-I", os.path.join(root, "include"), src,
+                  "-L", lib_dir, "-lblaze_b200", "-lcublas", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../blaze_b200", "-o", out])
+        built.append(out)
+    return built
+
+
 def build_all(force: bool = False) -> dict:
     res = {"oracle": build_oracle(force)}
     try:
@@ -85,6 +113,10 @@ def build_all(force: bool = False) -> dict:
         res["ref_naive"] = build_ref(force)
     except RuntimeError as e:
         res["ref_naive_error"] = str(e)
+    try:
+        res["ref_programs"] = build_ref_programs(force)
+    except RuntimeError as e:
+        res["ref_programs_error"] = str(e)
     return res
 
 

@@ -1,0 +1,519 @@
+"""GPU parity tests: the CUDA path through the C ABI against the CPU oracle on the same seeded
+inputs.  Tolerance: |c - ref| / max(|ref|, 1) <= 1e-2 per element (fp32 accumulation, 16-bit or
+fp32 output); byte-level work (quantisers, scale tiling, repacking) must be bit-exact.
+Seeds follow Blaze's tests: 42 for A / activations, 123 for B / weights (tests/test_gemm.cu:130-131).
+"""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from helpers import assert_close, bits16_to_torch, torch_to_f32
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _out_tensor(M, N, out_dtype, device, ldc=0):
+    torch = _torch()
+    dt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[out_dtype]
+    return torch.full((M, ldc or N), -7.0, dtype=dt, device=device)
+
+
+def _u8(a, device):
+    return _torch().from_numpy(np.ascontiguousarray(a, np.uint8)).to(device)
+
+
+def _run(plan, C):
+    plan.execute(C)
+    plan.check()
+    return C
+
+
+# --------------------------------------------------------------------------- dense fp16 / bf16
+
+def _dense_inputs(oracle, kind, M, N, K, scale=1.0):
+    rng_a, rng_b = np.random.default_rng(42), np.random.default_rng(123)
+    enc = oracle.f32_to_f16 if kind == "f16" else oracle.f32_to_bf16
+    A = enc((rng_a.standard_normal((M, K)) * scale).astype(np.float32))
+    Bt = enc((rng_b.standard_normal((N, K)) * scale).astype(np.float32))
+    return A, Bt
+
+
+@pytest.mark.parametrize("kind,out_dtype,variant,shape", [
+    ("f16", "f32", "128x128", (128, 128, 64)),       # one tile, one K stage
+    ("f16", "f32", "128x128", (128, 128, 256)),      # one tile, four K stages
+    ("f16", "f32", "128x128", (256, 256, 256)),      # BASELINE config 1 shape
+    ("bf16", "bf16", "128x128", (256, 384, 512)),
+    ("bf16", "bf16", "128x256", (256, 512, 192)),
+    ("f16", "f16", "128x256", (384, 768, 1024)),
+    ("bf16", "f32", "auto", (300, 200, 136)),        # ragged in M, N and K
+    ("f16", "bf16", "auto", (1, 128, 64)),           # single row
+    ("bf16", "bf16", "128x256", (129, 520, 72)),     # ragged tiles, 256-wide variant
+    ("bf16", "bf16", "auto", (2048, 2304, 1024)),    # several tiles per CTA: ring wrap, both accumulators
+])
+def test_dense16(oracle, cuda_device, kind, out_dtype, variant, shape):
+    from blaze_b200 import GemmPlan
+    M, N, K = shape
+    A, Bt = _dense_inputs(oracle, kind, M, N, K)
+    ref = oracle.gemm_dense16(A, Bt, kind)
+    tA, tB = bits16_to_torch(A, kind, cuda_device), bits16_to_torch(Bt, kind, cuda_device)
+    C = _out_tensor(M, N, out_dtype, cuda_device)
+    plan = GemmPlan(kind, M, N, K, tA, tB, out_dtype=out_dtype, variant=variant)
+    _run(plan, C)
+    got = torch_to_f32(C, oracle, out_dtype)
+    want = oracle.widen(oracle.narrow(ref, out_dtype), out_dtype)
+    assert_close(got, want, "dense %s %s %s %s" % (kind, out_dtype, variant, shape))
+    plan.destroy()
+
+
+def test_fp16_config1_golden(oracle, cuda_device):
+    """BASELINE config 1: fp16 256^3, A row-major, B column-major, seeded fill 42 / 123, fp32 out,
+    checked against the rows Blaze's own gemm_cpu_fp16 produced (tests/golden)."""
+    from blaze_b200 import create_fp16_gemm_plan, destroy_fp16_gemm_plan, execute_fp16_gemm
+    g = np.load(os.path.join(GOLDEN, "ref_gemm_cpu_fp16_256.npz"))
+    M = N = K = 256
+    A = oracle.f32_to_f16(oracle.fill_uniform_rand(M * K, 42)).reshape(M, K)
+    B = oracle.f32_to_f16(oracle.fill_uniform_rand(K * N, 123)).reshape(K, N)
+    tA = bits16_to_torch(A, "f16", cuda_device)
+    tB = bits16_to_torch(np.ascontiguousarray(B.T), "f16", cuda_device)      # column-major B = [N, K] rows
+    C = _out_tensor(M, N, "f32", cuda_device)
+    plan = create_fp16_gemm_plan(tA, tB, M, N, K)
+    execute_fp16_gemm(plan, C)
+    plan.check()
+    got = C.cpu().numpy()
+    assert_close(got[g["rows"]], g["C_rows"], "config 1 vs golden rows")
+    ref = oracle.gemm_f32(oracle.f16_to_f32(A), np.ascontiguousarray(oracle.f16_to_f32(B).T))
+    assert_close(got, ref, "config 1 vs oracle")
+    destroy_fp16_gemm_plan(plan)
+
+
+def test_golden_small_through_cuda(oracle, cuda_device):
+    from blaze_b200 import GemmPlan
+    g = np.load(os.path.join(GOLDEN, "ref_gemm_cpu_fp16_48x80x96.npz"))
+    A, B, Cref = g["A"], g["B"], g["C"]
+    M, K = A.shape; N = B.shape[1]
+    tA = bits16_to_torch(A, "f16", cuda_device)
+    tB = bits16_to_torch(B, "f16", cuda_device)                                # Blaze's [K, N] layout
+    C = _out_tensor(M, N, "f32", cuda_device)
+    plan = GemmPlan("f16", M, N, K, tA, tB, out_dtype="f32", b_layout="nmajor")
+    _run(plan, C)
+    assert_close(C.cpu().numpy(), Cref, "golden 48x80x96, B given [K,N]")
+    plan.destroy()
+
+
+# --------------------------------------------------------------------------------------- FP8
+
+def _fp8_inputs(oracle, M, N, K):
+    rng_a, rng_b = np.random.default_rng(42), np.random.default_rng(123)
+    xa = rng_a.uniform(-1, 1, (M, K)).astype(np.float32)
+    xb = rng_b.uniform(-1, 1, (N, K)).astype(np.float32)
+    qa, sa = oracle.quantize_fp8(xa)
+    qb, sb = oracle.quantize_fp8(xb)
+    return qa, float(np.float32(1.0) / np.float32(sa)), qb, float(np.float32(1.0) / np.float32(sb))
+
+
+@pytest.mark.parametrize("variant,shape", [
+    ("128x128", (128, 128, 128)),
+    ("128x128", (256, 256, 512)),
+    ("128x256", (256, 512, 384)),
+    ("auto", (200, 328, 144)),
+    ("auto", (32, 4096, 1024)),
+    ("128x256", (1024, 2048, 2048)),
+])
+def test_fp8(oracle, cuda_device, variant, shape):
+    from blaze_b200 import GemmPlan
+    M, N, K = shape
+    qa, da, qb, db = _fp8_inputs(oracle, M, N, K)
+    acc = oracle.gemm_f32(oracle.e4m3_to_f32(qa), oracle.e4m3_to_f32(qb))
+    alpha = float(np.float32(da) * np.float32(db))
+    want = oracle.widen(oracle.narrow(oracle.epilogue(acc, alpha), "bf16"), "bf16")
+    C = _out_tensor(M, N, "bf16", cuda_device)
+    plan = GemmPlan("fp8", M, N, K, _u8(qa, cuda_device), _u8(qb, cuda_device), a_scale=da, b_scale=db, out_dtype="bf16", variant=variant)
+    _run(plan, C)
+    assert_close(torch_to_f32(C, oracle, "bf16"), want, "fp8 %s %s" % (variant, shape))
+    plan.destroy()
+
+
+def test_fp8_config2_sampled(oracle, cuda_device):
+    """BASELINE config 2 (4096^3, uniform[-1,1], per-tensor scales to 448, bf16 out): inputs are
+    quantised on the GPU (bit-checked against the oracle on a slice), 48 output rows are checked."""
+    torch = _torch()
+    from blaze_b200 import GemmPlan, quantize_fp8
+    M = N = K = 4096
+    ga = torch.Generator(device=cuda_device).manual_seed(42)
+    gb = torch.Generator(device=cuda_device).manual_seed(123)
+    xa = torch.rand((M, K), generator=ga, device=cuda_device) * 2 - 1
+    xb = torch.rand((N, K), generator=gb, device=cuda_device) * 2 - 1
+    qa, sca = quantize_fp8(xa)
+    qb, scb = quantize_fp8(xb)
+    sca, scb = sca.cpu().numpy(), scb.cpu().numpy()
+    # quantiser parity on the first rows
+    s_ref = np.float32(448.0) / np.float32(xa.abs().max().item())
+    assert np.float32(sca[0]) == s_ref
+    assert np.array_equal(qa[:8].cpu().numpy(), oracle.f32_to_e4m3(xa[:8].cpu().numpy() * s_ref))
+    C = _out_tensor(M, N, "bf16", cuda_device)
+    plan = GemmPlan("fp8", M, N, K, qa, qb, a_scale=float(sca[1]), b_scale=float(scb[1]), out_dtype="bf16")
+    _run(plan, C)
+    rows = np.array(sorted(set(np.random.default_rng(5).integers(0, M, 46).tolist() + [0, M - 1])))
+    acc = oracle.gemm_f32(oracle.e4m3_to_f32(qa[rows].cpu().numpy()), oracle.e4m3_to_f32(qb.cpu().numpy()))
+    alpha = float(np.float32(sca[1]) * np.float32(scb[1]))
+    want = oracle.widen(oracle.narrow(oracle.epilogue(acc, alpha), "bf16"), "bf16")
+    got = torch_to_f32(C[torch.from_numpy(rows).to(cuda_device)], oracle, "bf16")
+    assert_close(got, want, "fp8 config 2 sampled rows")
+    plan.destroy()
+
+
+# ------------------------------------------------------------------------------------- NVFP4
+
+def _nvfp4_inputs(oracle, M, N, K, w_std=1.0):
+    rng_a, rng_b = np.random.default_rng(42), np.random.default_rng(123)
+    xa = rng_a.standard_normal((M, K)).astype(np.float32)
+    xb = (rng_b.standard_normal((N, K)) * w_std).astype(np.float32)
+    return oracle.quantize_nvfp4(xa), oracle.quantize_nvfp4(xb)
+
+
+def _nvfp4_ref(oracle, qa, qb, out_dtype="bf16", **epi):
+    (ad, asf, ga), (bd, bsf, gb) = qa, qb
+    acc, alpha = oracle.gemm_nvfp4(ad, asf, ga, bd, bsf, gb)
+    return oracle.widen(oracle.narrow(oracle.epilogue(acc, alpha, **epi), out_dtype), out_dtype)
+
+
+@pytest.mark.parametrize("variant,shape", [
+    ("128x128", (128, 128, 256)),      # one tile, one K stage
+    ("128x128", (128, 128, 1024)),     # one tile, four K stages
+    ("128x128", (256, 384, 512)),
+    ("128x256", (128, 256, 256)),
+    ("128x256", (384, 768, 1536)),
+    ("auto", (200, 328, 160)),         # ragged M, N; K not a multiple of the 256-value stage
+    ("128x256", (129, 520, 96)),
+    ("128x128", (100, 72, 64)),
+    ("auto", (1024, 4096, 2048)),
+    ("128x256", (2048, 2304, 1024)),   # several tiles per CTA
+    ("decode", (16, 512, 1024)),
+    ("decode", (1, 128, 256)),
+    ("decode", (7, 200, 160)),
+    ("decode", (32, 1024, 2048)),
+    ("decode", (64, 640, 4096)),
+    ("decode", (16, 4096, 4096)),      # split-K across CTAs
+])
+def test_nvfp4(oracle, cuda_device, variant, shape):
+    from blaze_b200 import GemmPlan
+    M, N, K = shape
+    qa, qb = _nvfp4_inputs(oracle, M, N, K)
+    want = _nvfp4_ref(oracle, qa, qb)
+    (ad, asf, ga), (bd, bsf, gb) = qa, qb
+    C = _out_tensor(M, N, "bf16", cuda_device)
+    plan = GemmPlan("nvfp4", M, N, K, _u8(ad, cuda_device), _u8(bd, cuda_device), A_sf=_u8(asf, cuda_device), B_sf=_u8(bsf, cuda_device),
+                    a_scale=ga, b_scale=gb, out_dtype="bf16", variant=variant)
+    _run(plan, C)
+    assert_close(torch_to_f32(C, oracle, "bf16"), want, "nvfp4 %s %s %s" % (variant, shape, plan.info()))
+    plan.destroy()
+
+
+@pytest.mark.parametrize("variant,M", [("128x128", 128), ("decode", 16)])
+def test_nvfp4_position_coded(oracle, cuda_device, variant, M):
+    """Catches transposition, nibble order and scale-layout errors that constant fills hide:
+    row m of A is one-hot at k = (37*m + 5) % K with its own block scale, every weight and every
+    weight scale differs, so C[m, n] singles out one element and one scale of B."""
+    from blaze_b200 import GemmPlan
+    N, K = 256, 512
+    codes = np.array([1, 2, 3, 4, 5, 6, 7, 9, 10, 11, 12, 13, 14, 15], np.uint8)
+    a_nib = np.zeros((M, K), np.uint8)
+    a_sf = np.full((M, K // 16), 0x38, np.uint8)
+    for m in range(M):
+        k = (37 * m + 5) % K
+        a_nib[m, k] = codes[m % len(codes)]
+        a_sf[m, k // 16] = 0x30 + (m % 24)
+    rng = np.random.default_rng(3)
+    b_nib = rng.integers(0, 16, (N, K)).astype(np.uint8)
+    b_sf = (0x28 + rng.integers(0, 32, (N, K // 16))).astype(np.uint8)
+    pack = lambda nib: (nib[:, 0::2] | (nib[:, 1::2] << 4)).astype(np.uint8)
+    ad, bd = pack(a_nib), pack(b_nib)
+    want = _nvfp4_ref(oracle, (ad, a_sf, 1.0), (bd, b_sf, 0.5), out_dtype="f32")
+    C = _out_tensor(M, N, "f32", cuda_device)
+    plan = GemmPlan("nvfp4", M, N, K, _u8(ad, cuda_device), _u8(bd, cuda_device), A_sf=_u8(a_sf, cuda_device), B_sf=_u8(b_sf, cuda_device),
+                    a_scale=1.0, b_scale=0.5, out_dtype="f32", variant=variant)
+    _run(plan, C)
+    got = C.cpu().numpy()
+    assert np.array_equal(got, want), "position-coded NVFP4 (%s): %d of %d elements differ" % (variant, int((got != want).sum()), got.size)
+    plan.destroy()
+
+
+@pytest.mark.parametrize("N,K", [(12288, 4096), (4096, 4096), (22016, 4096), (4096, 11008)])
+def test_nvfp4_config3_decode(oracle, cuda_device, N, K):
+    """BASELINE config 3: Llama-7B decode projections at M = 16, N(0,1) both sides, bf16 out."""
+    from blaze_b200 import GemmPlan
+    M = 16
+    qa, qb = _nvfp4_inputs(oracle, M, N, K)
+    want = _nvfp4_ref(oracle, qa, qb)
+    (ad, asf, ga), (bd, bsf, gb) = qa, qb
+    C = _out_tensor(M, N, "bf16", cuda_device)
+    plan = GemmPlan("nvfp4", M, N, K, _u8(ad, cuda_device), _u8(bd, cuda_device), A_sf=_u8(asf, cuda_device), B_sf=_u8(bsf, cuda_device),
+                    a_scale=ga, b_scale=gb, out_dtype="bf16")
+    assert plan.info()["variant"] == 3
+    _run(plan, C)
+    first = C.clone()
+    assert_close(torch_to_f32(C, oracle, "bf16"), want, "config 3 decode N=%d K=%d %s" % (N, K, plan.info()))
+    for _ in range(3):                                   # run-to-run bit-identical (ordered split-K sum)
+        C.fill_(0)
+        _run(plan, C)
+        assert _torch().equal(C, first)
+    plan.destroy()
+
+
+def test_nvfp4_blaze_layout_and_known_answer(oracle, cuda_device):
+    """Blaze's own block-scaled test (tests/test_gemm.cu:338-389): data 0x22, scales 0x38, tensor
+    scale 1 => every output equals K, through the Blaze-named API with B given as [K, N/2]."""
+    torch = _torch()
+    import blaze_b200 as bz
+    for (M, N, K) in [(1, 4096, 4096), (32, 512, 1024), (128, 256, 11008), (512, 768, 512)]:
+        A = {"data": torch.full((M, K // 2), 0x22, dtype=torch.uint8, device=cuda_device),
+             "block_scales": torch.full((M, K // 16), 0x38, dtype=torch.uint8, device=cuda_device), "tensor_scale": 1.0}
+        B = {"data": torch.full((K, N // 2), 0x22, dtype=torch.uint8, device=cuda_device),
+             "block_scales": torch.full((K // 16, N), 0x38, dtype=torch.uint8, device=cuda_device), "tensor_scale": 1.0}
+        C = _out_tensor(M, N, "f16", cuda_device)
+        for create, execute, destroy in [
+                (bz.create_fp4_blkscaled_gemm_plan, bz.execute_fp4_blkscaled_gemm, bz.destroy_fp4_blkscaled_gemm_plan),
+                (bz.create_fp4_blkscaled_persistent_gemm_plan, bz.execute_fp4_blkscaled_persistent_gemm, bz.destroy_fp4_blkscaled_persistent_gemm_plan)]:
+            plan = create(A, B, M, N, K)
+            execute(plan, C)
+            plan.check()
+            got = C.float().cpu().numpy()
+            assert np.abs(got - K).max() / max(K, 1) < 0.01, (M, N, K, got[0, :4])
+            destroy(plan)
+
+
+def test_nvfp4_nmajor_weights(oracle, cuda_device):
+    """B in Blaze's convention: data [K, N/2] (two N-neighbours per byte), scales [K/16, N]."""
+    from blaze_b200 import GemmPlan
+    M, N, K = 96, 384, 512
+    qa, qb = _nvfp4_inputs(oracle, M, N, K)
+    want = _nvfp4_ref(oracle, qa, qb)
+    (ad, asf, ga), (bd, bsf, gb) = qa, qb
+    nib = np.empty((N, K), np.uint8); nib[:, 0::2] = bd & 15; nib[:, 1::2] = bd >> 4
+    nib_kn = np.ascontiguousarray(nib.T)                                      # [K, N]
+    b_kn = (nib_kn[:, 0::2] | (nib_kn[:, 1::2] << 4)).astype(np.uint8)        # [K, N/2]
+    sf_kn = np.ascontiguousarray(bsf.T)                                       # [K/16, N]
+    C = _out_tensor(M, N, "bf16", cuda_device)
+    plan = GemmPlan("nvfp4", M, N, K, _u8(ad, cuda_device), _u8(b_kn, cuda_device), A_sf=_u8(asf, cuda_device), B_sf=_u8(sf_kn, cuda_device),
+                    a_scale=ga, b_scale=gb, out_dtype="bf16", b_layout="nmajor")
+    _run(plan, C)
+    assert_close(torch_to_f32(C, oracle, "bf16"), want, "nvfp4 with [K,N] weights")
+    plan.destroy()
+
+
+def test_nvfp4_config5_sampled(oracle, cuda_device):
+    """BASELINE config 5 on one GPU (M=8192, N=28672, K=8192): operands quantised on the GPU,
+    24 rows of the output checked against the oracle, plus a linearity property at full size:
+    doubling the activations' tensor scale doubles every output bit-exactly (bf16 keeps exponent)."""
+    torch = _torch()
+    from blaze_b200 import GemmPlan, quantize_nvfp4
+    M, N, K = 8192, 28672, 8192
+    ga = torch.Generator(device=cuda_device).manual_seed(42)
+    gb = torch.Generator(device=cuda_device).manual_seed(123)
+    xa = torch.randn((M, K), generator=ga, device=cuda_device)
+    ad, asf, gA = quantize_nvfp4(xa, tiled=False); del xa
+    xb = torch.randn((N, K), generator=gb, device=cuda_device)
+    bd, bsf, gB = quantize_nvfp4(xb, tiled=False); del xb
+    gA, gB = float(gA.item()), float(gB.item())
+    C = _out_tensor(M, N, "bf16", cuda_device)
+    plan = GemmPlan("nvfp4", M, N, K, ad, bd, A_sf=asf, B_sf=bsf, a_scale=gA, b_scale=gB, out_dtype="bf16")
+    _run(plan, C)
+    rows = np.array(sorted(set(np.random.default_rng(9).integers(0, M, 22).tolist() + [0, M - 1])))
+    ridx = torch.from_numpy(rows).to(cuda_device)
+    acc, alpha = oracle.gemm_nvfp4(ad[ridx].cpu().numpy(), asf[ridx].cpu().numpy(), gA, bd.cpu().numpy(), bsf.cpu().numpy(), gB)
+    want = oracle.widen(oracle.narrow(oracle.epilogue(acc, alpha), "bf16"), "bf16")
+    assert_close(torch_to_f32(C[ridx], oracle, "bf16"), want, "config 5 sampled rows")
+    C2 = _out_tensor(M, N, "bf16", cuda_device)
+    plan2 = GemmPlan("nvfp4", M, N, K, ad, bd, A_sf=asf, B_sf=bsf, a_scale=2 * gA, b_scale=gB, out_dtype="bf16")
+    _run(plan2, C2)
+    assert torch.equal(C2, C * 2)
+    plan.destroy(); plan2.destroy()
+
+
+# ------------------------------------------------------------------------------------- W4A16
+
+@pytest.mark.parametrize("kind,shape", [("w4a16_bf16", (128, 256, 512)), ("w4a16_f16", (200, 328, 160)), ("w4a16_bf16", (512, 1024, 2048))])
+def test_w4a16(oracle, cuda_device, kind, shape):
+    from blaze_b200 import GemmPlan
+    M, N, K = shape
+    act = "bf16" if kind.endswith("bf16") else "f16"
+    rng_a, rng_b = np.random.default_rng(42), np.random.default_rng(123)
+    enc = oracle.f32_to_bf16 if act == "bf16" else oracle.f32_to_f16
+    A = enc(rng_a.standard_normal((M, K)).astype(np.float32))
+    bd, bsf, gb = oracle.quantize_nvfp4((rng_b.standard_normal((N, K)) * 0.02).astype(np.float32))
+    acc, alpha = oracle.gemm_w4a16(A, act, bd, bsf, gb)
+    want = oracle.widen(oracle.narrow(oracle.epilogue(acc, alpha), act), act)
+    C = _out_tensor(M, N, act, cuda_device)
+    plan = GemmPlan(kind, M, N, K, bits16_to_torch(A, act, cuda_device), _u8(bd, cuda_device), B_sf=_u8(bsf, cuda_device), b_scale=gb, out_dtype=act)
+    _run(plan, C)
+    assert_close(torch_to_f32(C, oracle, act), want, "w4a16 %s %s" % (kind, shape))
+    plan.destroy()
+
+
+def test_w4a16_config4_sampled(oracle, cuda_device):
+    """BASELINE config 4: M=4096, N=22016, K=4096, bf16 activations N(0,1), weights N(0,0.02) as NVFP4."""
+    torch = _torch()
+    from blaze_b200 import GemmPlan, quantize_nvfp4
+    M, N, K = 4096, 22016, 4096
+    ga = torch.Generator(device=cuda_device).manual_seed(42)
+    gb = torch.Generator(device=cuda_device).manual_seed(123)
+    A = torch.randn((M, K), generator=ga, device=cuda_device).to(torch.bfloat16)
+    W = torch.randn((N, K), generator=gb, device=cuda_device) * 0.02
+    bd, bsf, gB = quantize_nvfp4(W, tiled=False); del W
+    gB = float(gB.item())
+    C = _out_tensor(M, N, "bf16", cuda_device)
+    plan = GemmPlan("w4a16_bf16", M, N, K, A, bd, B_sf=bsf, b_scale=gB, out_dtype="bf16")
+    _run(plan, C)
+    rows = np.array(sorted(set(np.random.default_rng(11).integers(0, M, 22).tolist() + [0, M - 1])))
+    ridx = torch.from_numpy(rows).to(cuda_device)
+    a_raw = A[ridx].view(torch.int16).cpu().numpy().view(np.uint16)
+    acc, alpha = oracle.gemm_w4a16(a_raw, "bf16", bd.cpu().numpy(), bsf.cpu().numpy(), gB)
+    want = oracle.widen(oracle.narrow(oracle.epilogue(acc, alpha), "bf16"), "bf16")
+    assert_close(torch_to_f32(C[ridx], oracle, "bf16"), want, "config 4 sampled rows")
+    plan.destroy()
+
+
+# ---------------------------------------------------------------------------------- epilogues
+
+@pytest.mark.parametrize("mode", ["bias", "silu", "bias_silu", "residual"])
+@pytest.mark.parametrize("kind,out_dtype", [("fp8", "f16"), ("nvfp4", "bf16"), ("bf16", "f32")])
+def test_epilogues(oracle, cuda_device, mode, kind, out_dtype):
+    from blaze_b200 import GemmPlan
+    torch = _torch()
+    M, N, K = 160, 264, 256
+    rng = np.random.default_rng(77)
+    bias32 = rng.standard_normal(N).astype(np.float32)
+    res32 = rng.standard_normal((M, N)).astype(np.float32)
+    bias_n = oracle.widen(oracle.narrow(bias32, out_dtype), out_dtype)
+    res_n = oracle.widen(oracle.narrow(res32, out_dtype), out_dtype)
+
+    def dev(x32):
+        if out_dtype == "f32":
+            return torch.from_numpy(x32).to(cuda_device)
+        return bits16_to_torch(oracle.narrow(x32, out_dtype), out_dtype, cuda_device)
+
+    kw = {}
+    if kind == "fp8":
+        qa, da, qb, db = _fp8_inputs(oracle, M, N, K)
+        acc = oracle.gemm_f32(oracle.e4m3_to_f32(qa), oracle.e4m3_to_f32(qb)); alpha = float(np.float32(da) * np.float32(db))
+        args = (_u8(qa, cuda_device), _u8(qb, cuda_device)); kw = dict(a_scale=da, b_scale=db)
+    elif kind == "nvfp4":
+        (ad, asf, ga), (bd, bsf, gb) = _nvfp4_inputs(oracle, M, N, K)
+        acc, alpha = oracle.gemm_nvfp4(ad, asf, ga, bd, bsf, gb)
+        args = (_u8(ad, cuda_device), _u8(bd, cuda_device)); kw = dict(A_sf=_u8(asf, cuda_device), B_sf=_u8(bsf, cuda_device), a_scale=ga, b_scale=gb)
+    else:
+        A, Bt = _dense_inputs(oracle, "bf16", M, N, K, scale=0.25)
+        acc = oracle.gemm_dense16(A, Bt, "bf16"); alpha = 1.0
+        args = (bits16_to_torch(A, "bf16", cuda_device), bits16_to_torch(Bt, "bf16", cuda_device))
+    want32 = oracle.epilogue(acc, alpha, bias=bias_n if "bias" in mode else None, residual=res_n if mode == "residual" else None, mode=mode)
+    want = oracle.widen(oracle.narrow(want32, out_dtype), out_dtype)
+    C = _out_tensor(M, N, out_dtype, cuda_device)
+    plan = GemmPlan(kind, M, N, K, *args, out_dtype=out_dtype, epilogue=mode, bias=dev(bias32) if "bias" in mode else None,
+                    residual=dev(res32) if mode == "residual" else None, **kw)
+    _run(plan, C)
+    assert_close(torch_to_f32(C, oracle, out_dtype), want, "epilogue %s %s" % (mode, kind))
+    plan.destroy()
+
+
+def test_strided_output_and_fp16_saturation(oracle, cuda_device):
+    """ldc > N leaves the padding untouched; fp16 stores clamp to +-65504 (no infinities)."""
+    from blaze_b200 import GemmPlan
+    M, N, K, ldc = 130, 136, 128, 160
+    qa, da, qb, db = _fp8_inputs(oracle, M, N, K)
+    C = _out_tensor(M, N, "f16", cuda_device, ldc=ldc)
+    plan = GemmPlan("fp8", M, N, K, _u8(qa, cuda_device), _u8(qb, cuda_device), a_scale=1.0, b_scale=1.0, out_dtype="f16", ldc=ldc)
+    _run(plan, C)
+    acc = oracle.gemm_f32(oracle.e4m3_to_f32(qa), oracle.e4m3_to_f32(qb))
+    want = oracle.widen(oracle.narrow(acc, "f16"), "f16")
+    got = torch_to_f32(C, oracle, "f16")
+    assert np.abs(want).max() == 65504.0                       # the raw E4M3 product overflows fp16 here
+    assert_close(got[:, :N], want, "fp16 saturating store")
+    assert np.all(got[:, N:] == -7.0)
+    plan.destroy()
+
+
+def test_run_to_run_bit_identical(oracle, cuda_device):
+    from blaze_b200 import GemmPlan
+    torch = _torch()
+    M, N, K = 1024, 2048, 2048
+    (ad, asf, ga), (bd, bsf, gb) = _nvfp4_inputs(oracle, M, N, K)
+    plan = GemmPlan("nvfp4", M, N, K, _u8(ad, cuda_device), _u8(bd, cuda_device), A_sf=_u8(asf, cuda_device), B_sf=_u8(bsf, cuda_device),
+                    a_scale=ga, b_scale=gb, out_dtype="bf16")
+    outs = []
+    for _ in range(3):
+        C = _out_tensor(M, N, "bf16", cuda_device)
+        _run(plan, C)
+        outs.append(C)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    plan.destroy()
+
+
+def test_set_a_rebinds_activations(oracle, cuda_device):
+    from blaze_b200 import GemmPlan, tile_scales
+    M, N, K = 16, 512, 1024
+    qa, qb = _nvfp4_inputs(oracle, M, N, K)
+    (ad, asf, ga), (bd, bsf, gb) = qa, qb
+    rng = np.random.default_rng(1234)
+    ad2, asf2, ga2 = oracle.quantize_nvfp4(rng.standard_normal((M, K)).astype(np.float32))
+    t_asf = tile_scales(_u8(asf, cuda_device), M, K)
+    t_asf2 = tile_scales(_u8(asf2, cuda_device), M, K)
+    assert np.array_equal(t_asf.cpu().numpy(), oracle.tile_sf(asf, 2, (K // 64 + 3) // 4 * 4))
+    C = _out_tensor(M, N, "bf16", cuda_device)
+    plan = GemmPlan("nvfp4", M, N, K, _u8(ad, cuda_device), _u8(bd, cuda_device), A_sf=t_asf, B_sf=_u8(bsf, cuda_device),
+                    a_scale=ga, b_scale=gb, out_dtype="bf16", a_sf_layout="tiled")
+    _run(plan, C)
+    assert_close(torch_to_f32(C, oracle, "bf16"), _nvfp4_ref(oracle, qa, qb), "before set_a")
+    plan.set_a(_u8(ad2, cuda_device), t_asf2, ga2)
+    _run(plan, C)
+    assert_close(torch_to_f32(C, oracle, "bf16"), _nvfp4_ref(oracle, (ad2, asf2, ga2), qb), "after set_a")
+    plan.destroy()
+
+
+# ------------------------------------------------------------------------ byte-level kernels
+
+def test_quantizers_bit_exact(oracle, cuda_device):
+    torch = _torch()
+    from blaze_b200 import quantize_fp8, quantize_nvfp4
+    rng = np.random.default_rng(2024)
+    for (rows, K, dt) in [(64, 256, torch.float32), (200, 1040, torch.float32), (33, 4096, torch.bfloat16), (16, 160, torch.float16)]:
+        x = torch.from_numpy(rng.standard_normal((rows, K)).astype(np.float32)).to(cuda_device).to(dt)
+        x[1, 16:32] = 0                                         # an all-zero block
+        x32 = x.float().cpu().numpy()
+        q, sc = quantize_fp8(x)
+        q_ref, s_ref = oracle.quantize_fp8(x32)
+        assert np.float32(sc[0].item()) == np.float32(s_ref)
+        assert np.array_equal(q.cpu().numpy(), q_ref)
+        d, sf, g = quantize_nvfp4(x)
+        d_ref, sf_ref, g_ref = oracle.quantize_nvfp4(x32)
+        assert np.float32(g.item()) == np.float32(g_ref)
+        assert np.array_equal(sf.cpu().numpy(), sf_ref), "block scales differ"
+        assert np.array_equal(d.cpu().numpy(), d_ref), "E2M1 codes differ"
+        d2, sft, _ = quantize_nvfp4(x, tiled=True)
+        assert np.array_equal(d2.cpu().numpy(), d_ref)
+        ka = ((K + 63) // 64 + 3) // 4 * 4
+        rb = ((rows + 127) // 128 + 1) // 2 * 2
+        assert np.array_equal(sft.cpu().numpy(), oracle.tile_sf(sf_ref, rb, ka))
+
+
+# ------------------------------------------------------------- Blaze's own test program
+
+def test_blaze_test_program_builds_and_passes(cuda_device):
+    """Blaze's tests/test_gemm.cu, compiled unchanged against this library's include/gemm headers
+    (oracle/build_oracle.py builds it where the reference tree is present)."""
+    exe = os.path.join(ROOT, "oracle", "_ref", "test_gemm")
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/test_gemm not built (reference tree absent at build time)")
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=900)
+    tail = "\n".join((r.stdout + r.stderr).splitlines()[-40:])
+    assert r.returncode == 0, tail
+    assert "FAIL" not in r.stdout, tail
