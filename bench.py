@@ -429,7 +429,7 @@ def main() -> int:
         ms = float(t.item())
         # optional exchange step, timed beside the GEMM: NCCL all-gather of the bf16 output,
         # result layout [world][M][N/world]
-        full = torch.empty((world, M, n_local), dtype=res["C"].dtype, device=device)
+        full = torch.empty((world * M, n_local), dtype=res["C"].dtype, device=device)
 
         def step_gather():
             res["plan"].execute(res["C"])

@@ -9,7 +9,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libblaze_b200.so")
+# BLAZE_B200_LIBRARY points at another build of the same library (e.g. a tuning build).
+LIB_PATH = os.environ.get("BLAZE_B200_LIBRARY") or os.path.join(_HERE, "libblaze_b200.so")
 
 # enums of blaze_b200.h
 OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE, ERR_TOO_LARGE, ERR_OUT_OF_MEMORY = range(8)

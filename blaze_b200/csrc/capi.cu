@@ -548,6 +548,15 @@ blz_status blz_gemm_launch(const blz_gemm_desc* desc, void* C, void* stream) {
     return s;
 }
 
+#ifdef BLZ_KERNEL_TIMING
+// Tuning builds only: copies the per-CTA cycle counters of the last tiled-kernel launch to the host.
+blz_status blz_debug_read_timing(unsigned long long* out, int n_words) {
+    BLZ_CUDA(cudaDeviceSynchronize());
+    BLZ_CUDA(cudaMemcpyFromSymbol(out, g_blz_timing, sizeof(unsigned long long) * static_cast<size_t>(n_words)));
+    return BLZ_OK;
+}
+#endif
+
 // ------------------------------------------------------------ preparation
 
 blz_status blz_amax(const void* x, int32_t x_dtype, int64_t n, float* d_amax, void* stream_v) {

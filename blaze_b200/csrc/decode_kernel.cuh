@@ -83,6 +83,10 @@ decode_nvf4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     volatile int* ticket_slot = reinterpret_cast<volatile int*>(gen_base + slot_off + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    [[maybe_unused]] const long long t_entry = BLZ_T_NOW();
+#ifdef BLZ_KERNEL_TIMING
+    if (threadIdx.x == 0) BLZ_T_STORE(9, global_timer_ns());
+#endif
     const int n_tile = blockIdx.x % p.n_tiles, split_idx = blockIdx.x / p.n_tiles;
     const int ks_begin = split_idx * p.stages_per_split;
     const int ks_end = min(p.k_stages_total, ks_begin + p.stages_per_split);
@@ -105,16 +109,22 @@ decode_nvf4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+#ifdef BLZ_KERNEL_TIMING
+    if (threadIdx.x == 0) BLZ_T_STORE(11, clock64() - t_entry);   // set-up
+#endif
 
     if (warp == 0) {
         if (lane == 0) {
+            BLZ_T_DECL(t_wait);
             const uint64_t pol_stream = l2_policy_evict_first();   // weights are read once
             const uint64_t pol_keep = l2_policy_evict_last();      // activations are shared by every CTA
             int stage = 0; uint32_t phase = 0;
             for (int ks = ks_begin; ks < ks_end; ++ks) {
+                [[maybe_unused]] const long long tw = BLZ_T_NOW();
                 if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
                     atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_PRODUCER); *abort_flag = 1; break;
                 }
+                BLZ_T_ADD(t_wait, tw);
                 const uint32_t sw = base + stage * Cfg::STAGE_BYTES;
                 const uint32_t sx = sw + Cfg::W_BYTES;
                 const uint32_t ssfw = sx + Cfg::X_REGION;
@@ -127,16 +137,23 @@ decode_nvf4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 bulk_load_1d(ssfx, p.sfx + katom * 512, Cfg::SF_BYTES, full_bar(stage));
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
+            BLZ_T_STORE(0, t_wait); BLZ_T_STORE(1, BLZ_T_NOW() - t_entry);
         }
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
+            BLZ_T_DECL(t_wait_full);
             for (int ks = ks_begin; ks < ks_end; ++ks) {
+                [[maybe_unused]] const long long tf = BLZ_T_NOW();
                 if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
                     atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
                 }
+                BLZ_T_ADD(t_wait_full, tf);
+#ifdef BLZ_KERNEL_TIMING
+                if (ks == ks_begin) BLZ_T_STORE(12, clock64() - t_entry);   // first stage landed
+#endif
                 tc_fence_after_sync();
                 const uint32_t sw = base + stage * Cfg::STAGE_BYTES;
                 const uint32_t sx = sw + Cfg::W_BYTES;
@@ -157,6 +174,7 @@ decode_nvf4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
             if (ok) tc_commit(acc_full_bar);
+            BLZ_T_STORE(2, t_wait_full); BLZ_T_STORE(4, BLZ_T_NOW() - t_entry);
         }
         __syncwarp();
     } else if (warp >= 4) {
@@ -165,6 +183,9 @@ decode_nvf4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         // Every epilogue thread walks the same barrier sequence below whether or not its wait
         // succeeded, so a give-up in one warp can never strand the others at a named barrier.
         const bool ok = mbar_wait(acc_full_bar, 0u, abort_flag);
+#ifdef BLZ_KERNEL_TIMING
+        if (threadIdx.x == 128) BLZ_T_STORE(5, clock64() - t_entry);       // accumulator finished
+#endif
         if (!ok) { atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_EPILOGUE); *abort_flag = 1; }
         float acc[MMA_N];
 #pragma unroll
@@ -215,6 +236,9 @@ decode_nvf4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         }
     }
 
+#ifdef BLZ_KERNEL_TIMING
+    if (threadIdx.x == 128) BLZ_T_STORE(7, clock64() - t_entry);           // epilogue finished
+#endif
     tc_fence_before_sync();
     __syncthreads();
     if (*abort_flag != 0) {
@@ -226,6 +250,9 @@ decode_nvf4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
+#ifdef BLZ_KERNEL_TIMING
+    if (threadIdx.x == 0) { BLZ_T_STORE(10, global_timer_ns()); BLZ_T_STORE(8, clock64() - t_entry); }
+#endif
 }
 
 }  // namespace blz

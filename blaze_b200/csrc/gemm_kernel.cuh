@@ -53,6 +53,22 @@ struct GemmKernelParams {
     int* status;             // device error word, 0 = fine
 };
 
+// Optional per-role cycle accounting, compiled in only with -DBLZ_KERNEL_TIMING (a tuning build):
+// slot layout per CTA, 16 x u64: 0 producer wait-empty, 1 producer total, 2 mma wait-full,
+// 3 mma wait-accumulator, 4 mma total, 5 epilogue wait-full, 6 epilogue work, 7 epilogue total, 8 tiles.
+#ifdef BLZ_KERNEL_TIMING
+__device__ unsigned long long g_blz_timing[1024 * 16];
+#define BLZ_T_DECL(name) long long name = 0
+#define BLZ_T_NOW() clock64()
+#define BLZ_T_ADD(acc, t0) acc += clock64() - (t0)
+#define BLZ_T_STORE(slot, v) g_blz_timing[(blockIdx.x & 1023) * 16 + (slot)] = static_cast<unsigned long long>(v)
+#else
+#define BLZ_T_DECL(name)
+#define BLZ_T_NOW() 0
+#define BLZ_T_ADD(acc, t0)
+#define BLZ_T_STORE(slot, v)
+#endif
+
 __device__ __forceinline__ float silu_f32(float v) { return v / (1.0f + __expf(-v)); }
 
 // fp32 -> fp16 with finite overflow clamped to +-65504 (NaN stays NaN)
@@ -211,12 +227,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
+            BLZ_T_DECL(t_wait); BLZ_T_DECL(t_total);
+            [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
                 for (int ks = 0; ks < p.k_stages; ++ks) {
+                    [[maybe_unused]] const long long t0 = BLZ_T_NOW();
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
                         atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_PRODUCER); *abort_flag = 1; ok = false; break;
                     }
+                    BLZ_T_ADD(t_wait, t0);
                     const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
                     mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
@@ -236,6 +256,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
+            BLZ_T_ADD(t_total, t_begin);
+            BLZ_T_STORE(0, t_wait); BLZ_T_STORE(1, t_total);
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -244,18 +266,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             bool ok = true;
+            BLZ_T_DECL(t_wait_full); BLZ_T_DECL(t_wait_acc); BLZ_T_DECL(t_total);
+            [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
                 const int buf = it % ACC_BUFS;
                 const uint32_t use = static_cast<uint32_t>(it / ACC_BUFS);
+                [[maybe_unused]] const long long ta = BLZ_T_NOW();
                 if (!mbar_wait(acc_empty_bar(buf), (use & 1u) ^ 1u, abort_flag)) {
                     atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_ACC); *abort_flag = 1; ok = false; break;
                 }
+                BLZ_T_ADD(t_wait_acc, ta);
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int ks = 0; ks < p.k_stages; ++ks) {
+                    [[maybe_unused]] const long long tf = BLZ_T_NOW();
                     if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
                         atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
                     }
+                    BLZ_T_ADD(t_wait_full, tf);
                     tc_fence_after_sync();
                     const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
@@ -287,6 +315,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 }
                 if (ok) tc_commit(acc_full_bar(buf));
             }
+            BLZ_T_ADD(t_total, t_begin);
+            BLZ_T_STORE(2, t_wait_full); BLZ_T_STORE(3, t_wait_acc); BLZ_T_STORE(4, t_total); BLZ_T_STORE(8, it);
         }
         __syncwarp();
     } else if (warp >= 4) {
@@ -294,13 +324,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const int q = warp & 3;
         int it = 0;
         bool ok = true;
+        BLZ_T_DECL(t_wait); BLZ_T_DECL(t_work); BLZ_T_DECL(t_total);
+        [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
             const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
             const int buf = it % ACC_BUFS;
             const uint32_t use = static_cast<uint32_t>(it / ACC_BUFS);
+            [[maybe_unused]] const long long tw = BLZ_T_NOW();
             if (!mbar_wait(acc_full_bar(buf), use & 1u, abort_flag)) {
                 atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_EPILOGUE); *abort_flag = 1; ok = false; break;
             }
+            BLZ_T_ADD(t_wait, tw);
+            [[maybe_unused]] const long long te = BLZ_T_NOW();
             tc_fence_after_sync();
             const int row = m_tile * 128 + q * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
@@ -314,7 +349,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+            BLZ_T_ADD(t_work, te);
         }
+        BLZ_T_ADD(t_total, t_begin);
+        if (warp == 4 && lane == 0) { BLZ_T_STORE(5, t_wait); BLZ_T_STORE(6, t_work); BLZ_T_STORE(7, t_total); }
     }
 
     // ---------------------------------------------------------------- teardown

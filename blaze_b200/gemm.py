@@ -190,3 +190,4 @@ def tile_scales(sf, rows: int, K: int, row_stride: int | None = None, blk_stride
     out = torch.empty(tiled_scales_bytes(rows, K), dtype=torch.uint8, device=sf.device)
     nv.check("blz_tile_scales", nv.lib().blz_tile_scales(sf.data_ptr(), rows, K, row_stride, blk_stride, out.data_ptr(), _stream(stream)))
     return out
+
