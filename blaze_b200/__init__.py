@@ -4,7 +4,7 @@ The product is the CUDA library (blaze_b200/libblaze_b200.so, C ABI in include/b
 this package is the Python host-side mirror used by the tests and the bench.
 """
 from . import _native
-from .gemm import (GemmPlan, amax, create_fp4_blkscaled_gemm_plan, create_fp4_blkscaled_persistent_gemm_plan,
+from .gemm import (GemmPlan, amax, gemm_nvfp4_decode_static, create_fp4_blkscaled_gemm_plan, create_fp4_blkscaled_persistent_gemm_plan,
                    create_fp4_gemm_plan, create_fp8_gemm_plan, create_fp16_gemm_plan, create_mixed_gemm_plan,
                    destroy_fp4_blkscaled_gemm_plan, destroy_fp4_blkscaled_persistent_gemm_plan, destroy_fp4_gemm_plan,
                    destroy_fp8_gemm_plan, destroy_fp16_gemm_plan, destroy_mixed_gemm_plan, execute_fp4_blkscaled_gemm,

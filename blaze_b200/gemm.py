@@ -191,3 +191,15 @@ def tile_scales(sf, rows: int, K: int, row_stride: int | None = None, blk_stride
     nv.check("blz_tile_scales", nv.lib().blz_tile_scales(sf.data_ptr(), rows, K, row_stride, blk_stride, out.data_ptr(), _stream(stream)))
     return out
 
+
+# ---------------------------------------------------------------- allocation-free decode GEMM
+
+def gemm_nvfp4_decode_static(A, A_sf_tiled, a_scale: float, B, B_sf_tiled, b_scale: float, M: int, N: int, K: int, C,
+                             out_dtype: str = "bf16", ldc: int = 0, status=None, stream=None) -> None:
+    """blz_gemm_nvfp4_decode_static: the skinny-M NVFP4 GEMM for callers that must not allocate
+    device memory (an inference runtime that owns all of HBM through its own arena, a loop that
+    cannot take an allocation's synchronisation).  Scales must already be in the tiled layout; the
+    split-K workspace is a fixed array inside the library, shared by every call on the device."""
+    nv.check("blz_gemm_nvfp4_decode_static", nv.lib().blz_gemm_nvfp4_decode_static(
+        _ptr(A), _ptr(A_sf_tiled), float(a_scale), _ptr(B), _ptr(B_sf_tiled), float(b_scale), int(M), int(N), int(K), _ptr(C),
+        nv.DTYPES[out_dtype], int(ldc), _ptr(status), _stream(stream)))

@@ -181,6 +181,35 @@ int64_t blz_tiled_scales_bytes(int64_t rows, int64_t K);
 blz_status blz_tile_scales(const uint8_t* sf, int64_t rows, int64_t K, int64_t row_stride, int64_t blk_stride,
                            uint8_t* tiled, void* stream);
 
+/* ---- allocation-free entry point (no counterpart in the reference: Blaze's launchers and plans
+ *      all call cudaMalloc, e.g. src/kernels/gemm_fp4_blkscaled_sm100.cu:840-920) ----
+ *
+ * The skinny-M NVFP4 GEMM (M <= 64) for callers that must not allocate device memory: serving
+ * runtimes that gave all of HBM to their own arena at start-up, and loops that cannot afford an
+ * allocation's implicit synchronisation.  Same kernel and same result as a plan with
+ * BLZ_VARIANT_DECODE; its split-K workspace is a fixed array inside the library image
+ * (8 MiB + 8 KiB per GPU, held by every GPU that loads the library until the process exits)
+ * instead of plan-owned memory.  The call performs no cudaMalloc / cudaFree and uses no
+ * allocating library routine.
+ *
+ *   A, A_sf_tiled : activations, packed E2M1 [M, K/2] and their scales in the TILED layout
+ *   B, B_sf_tiled : weights, packed E2M1 [N, K/2] (K-major) and their TILED scales
+ *   C             : [M, ldc] of out_dtype (ldc 0 = N); no bias / activation / residual
+ *   d_status      : optional device int the kernel sets non-zero if it gives up on a bounded
+ *                   wait (caller clears and reads it); may be null
+ *
+ * Limits: M <= 64; ceil(N/128) <= 1024; split * rows * ceil(N/128)*128 * 4 bytes of partial sums
+ * <= 8 MiB (rows = 16, 32 or 64 for M <= 16, 32, 64).  Anything larger returns
+ * BLZ_ERR_TOO_LARGE and launches nothing.
+ * The first call on each device resolves the array's device address and raises the kernels'
+ * shared-memory limit (with that device current); make that first call before any stream capture.
+ * All calls on a device share the one array: the tile counters are cleared at the start of each
+ * call, and two calls whose kernels overlap on the GPU (different streams) race on it. */
+blz_status blz_gemm_nvfp4_decode_static(const void* A, const void* A_sf_tiled, float a_scale,
+                                        const void* B, const void* B_sf_tiled, float b_scale,
+                                        int32_t M, int32_t N, int32_t K, void* C, int32_t out_dtype, int64_t ldc,
+                                        int32_t* d_status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
