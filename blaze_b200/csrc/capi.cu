@@ -16,6 +16,7 @@
 
 #include "../../include/blaze_b200.h"
 #include "decode_kernel.cuh"
+#include "gemm_cluster_kernel.cuh"
 #include "gemm_kernel.cuh"
 #include "prep_kernels.cuh"
 
@@ -118,6 +119,33 @@ KernelChoice pick_kernel(int mma_kind, int bn) {
     }
 }
 
+struct ClusterChoice {
+    const void* fn;
+    int cg, bn, stages, acc_bufs, smem, tmem_cols, threads;
+};
+
+template <int KIND, int CG, int BN, int STAGES, int ACC>
+ClusterChoice cluster_choice() {
+    using Cfg = ClusterGemmConfig<KIND, CG, BN, STAGES, ACC>;
+    return ClusterChoice{reinterpret_cast<const void*>(&gemm_cluster_kernel<KIND, CG, BN, STAGES, ACC>), CG, BN, STAGES, ACC,
+                         static_cast<int>(Cfg::SMEM_BYTES), static_cast<int>(Cfg::TMEM_COLS), Cfg::THREADS};
+}
+
+ClusterChoice pick_cluster_kernel(int mma_kind, int cg) {
+    if (cg == 2) {
+        switch (mma_kind) {
+            case MMA_F16: return cluster_choice<MMA_F16, 2, 256, 6, 2>();
+            case MMA_F8: return cluster_choice<MMA_F8, 2, 256, 6, 2>();
+            default: return cluster_choice<MMA_NVF4, 2, 256, 5, 1>();
+        }
+    }
+    switch (mma_kind) {
+        case MMA_F16: return cluster_choice<MMA_F16, 1, 128, 6, 2>();
+        case MMA_F8: return cluster_choice<MMA_F8, 1, 128, 6, 2>();
+        default: return cluster_choice<MMA_NVF4, 1, 128, 5, 2>();
+    }
+}
+
 }  // namespace
 
 struct blz_gemm_plan {
@@ -145,6 +173,12 @@ struct blz_gemm_plan {
     CUtensorMap tm_a{}, tm_b{};
     GemmKernelParams kp{};
     int grid = 0;
+    // cluster-kernel launch (CTA groups of 1 or 2)
+    bool use_cluster = false;
+    ClusterChoice cc{};
+    ClusterGemmParams cp{};
+    CUtensorMap tm_c{};
+    const void* tm_c_ptr = nullptr;   // the C the cached output map was encoded for
     // decode-kernel launch
     DecodeKernelParams dp{};
     int decode_smem = 0, decode_stages = 0, decode_split = 1, decode_mma_n = 0, decode_tmem = 0;
@@ -272,6 +306,59 @@ blz_status setup_tiled(blz_gemm_plan* p) {
     kp.status = p->status;
     const int64_t tiles = static_cast<int64_t>(kp.m_tiles) * kp.n_tiles;
     p->grid = static_cast<int>(tiles < p->num_sms ? tiles : p->num_sms);
+    return BLZ_OK;
+}
+
+blz_status launch_config_cluster(const blz_gemm_plan* p, cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, cudaStream_t stream) {
+    cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(p->grid));
+    cfg.blockDim = dim3(static_cast<unsigned>(p->cc.threads));
+    cfg.dynamicSmemBytes = static_cast<size_t>(p->cc.smem);
+    cfg.stream = stream;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(p->cc.cg);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return BLZ_OK;
+}
+
+blz_status setup_cluster(blz_gemm_plan* p, int cg) {
+    const blz_gemm_desc& d = p->desc;
+    const int64_t rb = row_bytes(p->mma_kind, d.K);
+    p->cc = pick_cluster_kernel(p->mma_kind, cg);
+    p->use_cluster = true;
+    p->variant = cg == 2 ? BLZ_VARIANT_PAIR_256x256 : BLZ_VARIANT_TILE_128x128;
+    BLZ_CUDA(cudaFuncSetAttribute(p->cc.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, p->cc.smem));
+    const int bn = p->cc.bn, tile_m = 128 * cg;
+    blz_status s = encode_map(&p->tm_a, p->a_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.M), static_cast<uint64_t>(rb), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (s) return s;
+    s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rb), 128, static_cast<uint32_t>(bn / cg), CU_TENSOR_MAP_SWIZZLE_128B);
+    if (s) return s;
+    ClusterGemmParams& cp = p->cp;
+    cp.M = d.M; cp.N = d.N;
+    cp.m_tiles = static_cast<int>(ceil_div(d.M, tile_m));
+    cp.n_tiles = static_cast<int>(ceil_div(d.N, bn));
+    cp.k_stages = static_cast<int>(ceil_div(rb, 128));
+    const uint32_t fmt = d.kind == BLZ_GEMM_BF16 || d.kind == BLZ_GEMM_W4A16_BF16 ? 1u : 0u;
+    cp.idesc = p->mma_kind == MMA_NVF4 ? make_idesc_nvf4(tile_m, bn) : p->mma_kind == MMA_F8 ? make_idesc(0, 0, tile_m, bn) : make_idesc(fmt, fmt, tile_m, bn);
+    cp.sfa = p->sfa_used; cp.sfb = p->sfb_used;
+    cp.sf_katoms = static_cast<int>(sf_katoms(d.K));
+    cp.status = p->status;
+    const int64_t tiles = static_cast<int64_t>(cp.m_tiles) * cp.n_tiles;
+    int max_groups = p->num_sms / cg;
+    if (cg == 2) {
+        // how many pairs the device can hold at once (GPC shapes can leave SMs unpaired)
+        p->grid = max_groups * cg;
+        cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[1];
+        launch_config_cluster(p, cfg, attr, nullptr);
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, p->cc.fn, &cfg) == cudaSuccess && n > 0) { if (n < max_groups) max_groups = n; }
+        else (void)cudaGetLastError();
+    }
+    const int64_t groups = tiles < max_groups ? tiles : max_groups;
+    p->grid = static_cast<int>(groups) * cg;
     return BLZ_OK;
 }
 
@@ -447,7 +534,15 @@ blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_p
         const void* b_tc = w4a16 ? p->own_w16 : p->b_used;
         const void* keep = p->b_used;
         p->b_used = b_tc;
-        s = setup_tiled(p);
+        int v = desc->variant;
+        if (v == BLZ_VARIANT_AUTO) {
+            // CTA pairs when there is at least one 256x256 tile per pair of SMs, else single CTAs
+            const int64_t tiles256 = ceil_div(desc->M, 256) * ceil_div(desc->N, 256);
+            v = (desc->M > 128 && tiles256 >= p->num_sms / 2) ? BLZ_VARIANT_PAIR_256x256 : BLZ_VARIANT_TILE_128x128;
+        }
+        if (v == BLZ_VARIANT_PAIR_256x256) s = setup_cluster(p, 2);
+        else if (v == BLZ_VARIANT_TILE_128x128) s = setup_cluster(p, 1);
+        else s = setup_tiled(p);
         p->b_used = keep;
         if (s) return fail(s);
     }
@@ -470,6 +565,26 @@ blz_status blz_gemm_execute(blz_gemm_plan* p, void* C, void* stream_v) {
             dequant_nvfp4_kernel<__nv_bfloat16><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<__nv_bfloat16*>(p->own_w16));
         BLZ_CUDA(cudaGetLastError());
     }
+    if (p->use_cluster) {
+        ClusterGemmParams cp = p->cp;
+        fill_epilogue(p, C, cp.epi);
+        cp.use_tma_store = cp.epi.vec_ok;
+        if (cp.use_tma_store) {
+            if (p->tm_c_ptr != C) {
+                const int eb = elem_bytes_out(d.out_dtype);
+                blz_status s = encode_map(&p->tm_c, C, static_cast<uint64_t>(d.N) * eb, static_cast<uint64_t>(d.M), static_cast<uint64_t>(cp.epi.ldc) * eb, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+                if (s) return s;
+                p->tm_c_ptr = C;
+            }
+        } else if (p->tm_c_ptr == nullptr) {
+            p->tm_c = p->tm_a;                  // a valid descriptor the kernel never stores through
+        }
+        cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[1];
+        launch_config_cluster(p, cfg, attr, stream);
+        void* cargs[4] = {&p->tm_a, &p->tm_b, &p->tm_c, &cp};
+        BLZ_CUDA(cudaLaunchKernelExC(&cfg, p->cc.fn, cargs));
+        return BLZ_OK;
+    }
     GemmKernelParams kp = p->kp;
     fill_epilogue(p, C, kp.epi);
     void* args[3] = {&p->tm_a, &p->tm_b, &kp};
@@ -489,6 +604,7 @@ blz_status blz_gemm_plan_set_a(blz_gemm_plan* p, const void* A, const void* A_sf
     p->a_used = A;
     if (a_scale != 0.0f) d.a_scale = a_scale;
     if (p->variant == BLZ_VARIANT_DECODE) return decode_rebind_a(p);
+    p->cp.sfa = p->sfa_used;
     const int64_t rb = row_bytes(p->mma_kind, d.K);
     blz_status s = encode_map(&p->tm_a, A, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.M), static_cast<uint64_t>(rb), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (s) return s;
@@ -519,6 +635,10 @@ blz_status blz_gemm_plan_info(const blz_gemm_plan* p, blz_plan_info* info) {
         info->tile_m = p->decode_mma_n; info->tile_n = 128;
         info->stages = p->decode_stages; info->split_k = p->decode_split;
         info->grid = p->grid; info->smem_bytes = p->decode_smem; info->tmem_cols = p->decode_tmem;
+    } else if (p->use_cluster) {
+        info->tile_m = 128 * p->cc.cg; info->tile_n = p->cc.bn;
+        info->stages = p->cc.stages; info->split_k = 1;
+        info->grid = p->grid; info->smem_bytes = p->cc.smem; info->tmem_cols = p->cc.tmem_cols;
     } else {
         info->tile_m = 128; info->tile_n = p->kc.bn;
         info->stages = p->kc.stages; info->split_k = 1;

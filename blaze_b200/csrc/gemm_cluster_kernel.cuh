@@ -1,0 +1,378 @@
+// gemm_cluster_kernel.cuh -- persistent tcgen05 GEMM over CTA groups of CG = 1 or 2 SMs.
+//
+//   C[M,N] = epilogue( alpha * sum_k A[M,K] * B[N,K]^T )        (both operands K-major)
+//
+// A group of CG CTAs (one thread-block cluster) owns output tiles of (128*CG) x BN.  With CG = 2
+// the pair issues cta_group::2 instructions: each CTA stages its own 128 rows of A and its own
+// half of the B tile, so per CTA a pipeline stage is a third smaller than for a 128 x BN tile and
+// more stages fit; each CTA accumulates its 128 rows x BN in its own tensor memory.
+// No multicast loads: every CTA fetches its own tiles.
+//
+// Warp roles in every CTA (NVFP4: 12 warps, otherwise 8):
+//   warp 0      TMA producer: A tile, B tile (its share) and scale-factor atoms -> stage ring,
+//               completion on the CTA's own full barrier
+//   warp 1      MMA issuer (leader CTA only): waits for the stage's ready barrier, issues four
+//               tcgen05.mma (32 bytes of K each), commits to the stage's empty barrier in every CTA
+//               of the group and, after the last stage, to the accumulator-full barriers
+//   warp 2      tensor-memory alloc/free; for kinds without scale factors also the relay that turns
+//               "my tiles landed" into one arrive on the leader's ready barrier
+//   warps 4-7   epilogue: tcgen05.ld the CTA's 128 accumulator rows, alpha / bias / SiLU / residual,
+//               narrow, swizzled store to a staging buffer, TMA store (row-strided direct stores
+//               when C is not 16-byte aligned)
+//   warps 8-11  NVFP4 only: move the stage's scale factors shared memory -> registers -> tensor
+//               memory (tcgen05.st) into that stage's own columns, then arrive on the leader's ready
+//               barrier.  Measured on B200: a tcgen05.cp costs ~70 cycles of the tensor pipe whatever
+//               its size and does not overlap MMAs, tcgen05.st from other warps runs beside them.
+//
+// Counterpart of Blaze's gemm_fp8_kernel (src/kernels/gemm_fp8_sm100.cu:204-264) and
+// gemm_fp4_blkscaled_persistent_kernel (src/kernels/gemm_fp4_blkscaled_sm100.cu:507-624).
+#pragma once
+
+#include "gemm_kernel.cuh"
+
+namespace blz {
+
+struct ClusterGemmParams {
+    int M, N;
+    int m_tiles, n_tiles;    // tiles of (128*CG) x BN
+    int k_stages;            // ceil(K bytes per row / 128)
+    uint32_t idesc;
+    const uint8_t* sfa;      // tiled scale factors of A: [row blocks of 128][sf_katoms][512]
+    const uint8_t* sfb;      // tiled scale factors of B
+    int sf_katoms;
+    int use_tma_store;       // C (and its pitch) 16-byte aligned: epilogue stores through tm_c
+    EpilogueParams epi;
+    int* status;
+};
+
+template <int KIND, int CG, int BN, int STAGES, int ACC_BUFS>
+struct ClusterGemmConfig {
+    static constexpr bool HAS_SF = (KIND == MMA_NVF4);
+    static constexpr int THREADS = HAS_SF ? 384 : 256;
+    static constexpr uint32_t A_BYTES = 128 * 128;
+    static constexpr uint32_t B_ROWS = BN / CG;                        // rows of the B tile staged by one CTA
+    static constexpr uint32_t B_BYTES = B_ROWS * 128;
+    static constexpr uint32_t SF_BLOCK_BYTES = 4 * 512;                // one 128-row block, four K atoms
+    static constexpr uint32_t SFB_BLOCKS = BN / 128;                   // every CTA needs the scales of all BN columns
+    static constexpr uint32_t SFA_BYTES = HAS_SF ? SF_BLOCK_BYTES : 0;
+    static constexpr uint32_t SFB_BYTES = HAS_SF ? SFB_BLOCKS * SF_BLOCK_BYTES : 0;
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+    static constexpr uint32_t OUT_BUF_BYTES = 128 * 128;               // 128 rows x 128 bytes
+    static constexpr uint32_t OUT_BYTES = 2 * OUT_BUF_BYTES;
+    static constexpr uint32_t ACC_COLS = ACC_BUFS * BN;
+    static constexpr uint32_t SF_COLS = HAS_SF ? 16 + 4 * (BN / 32) : 0;  // per stage: A 4 per atom, B BN/32 per atom
+    static constexpr uint32_t SF_BASE = ACC_COLS;
+    static constexpr uint32_t TMEM_NEED = ACC_COLS + STAGES * SF_COLS;
+    static constexpr uint32_t TMEM_COLS = tmem_cols_pow2(TMEM_NEED);
+    static constexpr uint32_t NUM_BARS = 3 * STAGES + 2 * ACC_BUFS;
+    static constexpr uint32_t BAR_BYTES = 8 * NUM_BARS + 16;
+    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BYTES + BAR_BYTES + 1024;
+    static constexpr uint32_t READY_COUNT = HAS_SF ? 4 * CG : CG;      // arrivals that make a stage ready for the MMA
+    static_assert(CG == 1 || CG == 2, "CTA group of 1 or 2");
+    static_assert(TMEM_NEED <= 512, "accumulators and scale factors exceed tensor memory");
+    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared-memory limit");
+    static_assert(B_ROWS % 8 == 0 && BN % 128 == 0 && BN <= 256, "tile width");
+};
+
+template <int KIND, int CG, int BN, int STAGES, int ACC_BUFS>
+__global__ void __launch_bounds__(ClusterGemmConfig<KIND, CG, BN, STAGES, ACC_BUFS>::THREADS, 1)
+gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                    const __grid_constant__ CUtensorMap tm_c, const ClusterGemmParams p) {
+    using Cfg = ClusterGemmConfig<KIND, CG, BN, STAGES, ACC_BUFS>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;      // the same offset in every CTA of the cluster
+    uint8_t* gen_base = smem_raw + (base - raw);
+
+    const uint32_t out_base = base + STAGES * Cfg::STAGE_BYTES;
+    const uint32_t bar_base = out_base + Cfg::OUT_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto ready_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+    auto acc_full_bar = [&](int b) { return bar_base + 8u * (3 * STAGES + b); };
+    auto acc_empty_bar = [&](int b) { return bar_base + 8u * (3 * STAGES + ACC_BUFS + b); };
+    const uint32_t slot_off = STAGES * Cfg::STAGE_BYTES + Cfg::OUT_BYTES + 8u * Cfg::NUM_BARS;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + slot_off);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + slot_off + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = (CG == 1) ? 0u : cluster_cta_rank();
+    const bool leader = (rank == 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(ready_bar(s), Cfg::READY_COUNT);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < ACC_BUFS; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 4 * CG); }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if constexpr (CG == 2) cluster_sync_all();         // both CTAs are resident before the pair allocates
+    if (warp == 2) {
+        if constexpr (CG == 2) { tmem_alloc_pair(base + slot_off, Cfg::TMEM_COLS); tmem_relinquish_pair(); }
+        else { tmem_alloc(base + slot_off, Cfg::TMEM_COLS); tmem_relinquish(); }
+    }
+    if (warp == 0 && lane == 0) {
+        prefetch_tensormap(&tm_a);
+        prefetch_tensormap(&tm_b);
+        prefetch_tensormap(&tm_c);
+    }
+    tc_fence_before_sync();
+    if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();   // barriers of every CTA are initialised
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int group = blockIdx.x / CG, num_groups = gridDim.x / CG;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (every CTA)
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
+                const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+                const int a_row = (m_tile * CG + static_cast<int>(rank)) * 128;
+                const int b_row = n_tile * BN + static_cast<int>(rank) * static_cast<int>(Cfg::B_ROWS);
+                for (int ks = 0; ks < p.k_stages; ++ks) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                        atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_PRODUCER); *abort_flag = 1; ok = false; break;
+                    }
+                    const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
+                    const uint32_t sb = sa + Cfg::A_BYTES;
+                    mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+                    tma_load_2d(sa, &tm_a, ks * 128, a_row, full_bar(stage));
+                    tma_load_2d(sb, &tm_b, ks * 128, b_row, full_bar(stage));
+                    if constexpr (Cfg::HAS_SF) {
+                        const uint32_t ssfa = sb + Cfg::B_BYTES;
+                        const uint32_t ssfb = ssfa + Cfg::SFA_BYTES;
+                        const size_t katom = static_cast<size_t>(ks) * 4;
+                        const size_t a_blk = static_cast<size_t>(m_tile) * CG + rank;
+                        bulk_load_1d(ssfa, p.sfa + (a_blk * p.sf_katoms + katom) * 512, Cfg::SF_BLOCK_BYTES, full_bar(stage));
+#pragma unroll
+                        for (int blk = 0; blk < static_cast<int>(Cfg::SFB_BLOCKS); ++blk) {
+                            const size_t rb = static_cast<size_t>(n_tile) * Cfg::SFB_BLOCKS + blk;
+                            bulk_load_1d(ssfb + blk * Cfg::SF_BLOCK_BYTES, p.sfb + (rb * p.sf_katoms + katom) * 512, Cfg::SF_BLOCK_BYTES, full_bar(stage));
+                        }
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // -------------------------------------------------------------- MMA issuer (leader CTA)
+        if (leader && lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = group; ok && tile < total_tiles; tile += num_groups, ++it) {
+                const int buf = it % ACC_BUFS;
+                const uint32_t use = static_cast<uint32_t>(it / ACC_BUFS);
+                if (!mbar_wait(acc_empty_bar(buf), (use & 1u) ^ 1u, abort_flag)) {
+                    atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_ACC); *abort_flag = 1; ok = false; break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int ks = 0; ks < p.k_stages; ++ks) {
+                    if (!mbar_wait(ready_bar(stage), phase, abort_flag)) {
+                        atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
+                    const uint32_t sb = sa + Cfg::A_BYTES;
+                    const uint32_t sf_cols = tmem_base + Cfg::SF_BASE + stage * Cfg::SF_COLS;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint64_t ad = make_desc_k_sw128(sa + k * 32);
+                        const uint64_t bd = make_desc_k_sw128(sb + k * 32);
+                        const uint32_t accumulate = (ks | k) != 0 ? 1u : 0u;
+                        if constexpr (CG == 1) {
+                            if constexpr (KIND == MMA_F16) umma_f16(d_tmem, ad, bd, p.idesc, accumulate);
+                            else if constexpr (KIND == MMA_F8) umma_f8(d_tmem, ad, bd, p.idesc, accumulate);
+                            else umma_nvf4(d_tmem, ad, bd, p.idesc, sf_cols + 4 * k, sf_cols + 16 + k * (BN / 32), accumulate);
+                        } else {
+                            if constexpr (KIND == MMA_F16) umma_f16_pair(d_tmem, ad, bd, p.idesc, accumulate);
+                            else if constexpr (KIND == MMA_F8) umma_f8_pair(d_tmem, ad, bd, p.idesc, accumulate);
+                            else umma_nvf4_pair(d_tmem, ad, bd, p.idesc, sf_cols + 4 * k, sf_cols + 16 + k * (BN / 32), accumulate);
+                        }
+                    }
+                    if constexpr (CG == 1) tc_commit(empty_bar(stage)); else tc_commit_pair(empty_bar(stage), 0x3);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) {
+                    if constexpr (CG == 1) tc_commit(acc_full_bar(buf)); else tc_commit_pair(acc_full_bar(buf), 0x3);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 2) {
+        // ----------------------------------- relay for kinds without scale factors (every CTA)
+        if constexpr (!Cfg::HAS_SF) {
+            if (lane == 0) {
+                int stage = 0; uint32_t phase = 0;
+                bool ok = true;
+                for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
+                    for (int ks = 0; ks < p.k_stages; ++ks) {
+                        if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+                            atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
+                        }
+                        if constexpr (CG == 1) mbar_arrive(ready_bar(stage)); else mbar_arrive_cluster(ready_bar(stage), 0);
+                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    }
+                }
+            }
+            __syncwarp();
+        }
+    } else if (warp >= 4 && warp < 8) {
+        // ---------------------------------------------------------------- epilogue (every CTA)
+        const int q = warp & 3;
+        const int epi_tid = threadIdx.x - 128;
+        const int out_esize = p.epi.out_type == OUT_F32 ? 4 : 2;
+        const int chunk_cols = 128 / out_esize;                    // columns per 128-byte staging row
+        int it = 0;
+        int obuf = 0;
+        bool ok = true;
+        for (int tile = group; tile < total_tiles; tile += num_groups, ++it) {
+            const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+            const int buf = it % ACC_BUFS;
+            const uint32_t use = static_cast<uint32_t>(it / ACC_BUFS);
+            if (ok && !mbar_wait(acc_full_bar(buf), use & 1u, abort_flag)) {
+                atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_EPILOGUE); *abort_flag = 1; ok = false;
+            }
+            // After a give-up the warps still walk the same named-barrier sequence (without touching
+            // tensor memory or C) so that no epilogue warp is left waiting for another.
+            tc_fence_after_sync();
+            const int row0 = (m_tile * CG + static_cast<int>(rank)) * 128;
+            const int r_local = q * 32 + lane;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+            if (p.use_tma_store) {
+                for (int c0 = 0; c0 < BN; c0 += chunk_cols) {
+                    // staging buffer `obuf` was handed to a TMA store two chunks ago: wait until that
+                    // store has finished reading it
+                    if (epi_tid == 0) tma_store_wait_read<1>();
+                    named_barrier_sync(1, 128);
+                    const uint32_t sbuf = out_base + obuf * Cfg::OUT_BUF_BYTES;
+                    if (ok) {
+                        for (int h = 0; h < chunk_cols; h += 32) {
+                            uint32_t acc[32];
+                            tmem_ld32(t_row + c0 + h, acc);
+                            tmem_ld_wait();
+                            const int col = n_tile * BN + c0 + h;
+                            float v[32];
+                            epilogue_math32(p.epi, acc, v, row0 + r_local, col, p.M, p.N);
+                            // 128-byte swizzle: 16-byte unit j of row r lives at unit (j ^ (r % 8))
+                            const uint32_t srow = sbuf + r_local * 128;
+                            if (out_esize == 4) {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    const uint32_t dst = srow + (((h / 4 + j) ^ (r_local & 7)) << 4);
+                                    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3]) : "memory");
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    uint32_t w[4];
+#pragma unroll
+                                    for (int t = 0; t < 4; ++t) w[t] = pack2_out(p.epi.out_type, v[8 * j + 2 * t], v[8 * j + 2 * t + 1]);
+                                    const uint32_t dst = srow + (((h / 8 + j) ^ (r_local & 7)) << 4);
+                                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                                }
+                            }
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    named_barrier_sync(1, 128);
+                    if (epi_tid == 0) {
+                        if (ok) tma_store_2d(&tm_c, sbuf, (n_tile * BN + c0) * out_esize, row0);
+                        tma_store_commit();
+                    }
+                    obuf ^= 1;
+                }
+            } else if (ok) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t acc[32];
+                    tmem_ld32(t_row + c0, acc);
+                    tmem_ld_wait();
+                    epilogue_store32_dyn(p.epi, acc, row0 + r_local, n_tile * BN + c0, p.M, p.N);
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (ok && lane == 0) {
+                if constexpr (CG == 1) mbar_arrive(acc_empty_bar(buf)); else mbar_arrive_cluster(acc_empty_bar(buf), 0);
+            }
+        }
+        if (epi_tid == 0) tma_store_wait_all<0>();     // staging memory must outlive the last store's reads
+    } else if (warp >= 8) {
+        // -------------------------------- NVFP4: scale factors smem -> registers -> tensor memory
+        if constexpr (Cfg::HAS_SF) {
+            const int q = warp & 3;
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
+                for (int ks = 0; ks < p.k_stages; ++ks) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+                        atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
+                    }
+                    const uint8_t* ssfa = gen_base + stage * Cfg::STAGE_BYTES + Cfg::A_BYTES + Cfg::B_BYTES;
+                    const uint8_t* ssfb = ssfa + Cfg::SFA_BYTES;
+                    const uint32_t t_sf = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::SF_BASE + stage * Cfg::SF_COLS;
+                    {
+                        uint32_t r[16];
+#pragma unroll
+                        for (int a = 0; a < 4; ++a) {
+                            const uint4 v = *reinterpret_cast<const uint4*>(ssfa + a * 512 + lane * 16);
+                            r[4 * a] = v.x; r[4 * a + 1] = v.y; r[4 * a + 2] = v.z; r[4 * a + 3] = v.w;
+                        }
+                        tmem_st16(t_sf, r);
+                    }
+                    if constexpr (BN == 256) {
+                        uint32_t r[32];
+#pragma unroll
+                        for (int a = 0; a < 4; ++a)
+#pragma unroll
+                            for (int blk = 0; blk < 2; ++blk) {
+                                const uint4 v = *reinterpret_cast<const uint4*>(ssfb + blk * Cfg::SF_BLOCK_BYTES + a * 512 + lane * 16);
+                                r[8 * a + 4 * blk] = v.x; r[8 * a + 4 * blk + 1] = v.y; r[8 * a + 4 * blk + 2] = v.z; r[8 * a + 4 * blk + 3] = v.w;
+                            }
+                        tmem_st32(t_sf + 16, r);
+                    } else {
+                        uint32_t r[16];
+#pragma unroll
+                        for (int a = 0; a < 4; ++a) {
+                            const uint4 v = *reinterpret_cast<const uint4*>(ssfb + a * 512 + lane * 16);
+                            r[4 * a] = v.x; r[4 * a + 1] = v.y; r[4 * a + 2] = v.z; r[4 * a + 3] = v.w;
+                        }
+                        tmem_st16(t_sf + 16, r);
+                    }
+                    tmem_st_wait();
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (CG == 1) mbar_arrive(ready_bar(stage)); else mbar_arrive_cluster(ready_bar(stage), 0);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
+    if (*abort_flag != 0) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
+    if (warp == 2) {
+        tc_fence_after_sync();
+        if constexpr (CG == 2) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS); else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+}  // namespace blz

@@ -149,6 +149,38 @@ __device__ __forceinline__ void epilogue_store32(const EpilogueParams& e, const 
     }
 }
 
+// alpha, bias, SiLU, residual on 32 consecutive accumulator columns of one row (fp32 in, fp32 out);
+// bias / residual are read in the output's element type and only inside the matrix.
+__device__ __forceinline__ void epilogue_math32(const EpilogueParams& e, const uint32_t (&acc)[32], float (&v)[32], int row, int col0, int M, int N) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]) * e.alpha;
+    if (e.mode == EPI_NONE) return;
+    const bool has_bias = (e.mode == EPI_BIAS || e.mode == EPI_BIAS_SILU) && e.bias != nullptr;
+    const bool has_res = e.mode == EPI_RESIDUAL && e.residual != nullptr && row < M;
+    const long long roff = static_cast<long long>(row) * e.ldr + col0;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        if (col0 + i < N) {
+            if (has_bias) v[i] += e.out_type == OUT_BF16 ? load_out_elem<OUT_BF16>(e.bias, col0 + i) : e.out_type == OUT_F16 ? load_out_elem<OUT_F16>(e.bias, col0 + i) : load_out_elem<OUT_F32>(e.bias, col0 + i);
+            if (has_res) v[i] += e.out_type == OUT_BF16 ? load_out_elem<OUT_BF16>(e.residual, roff + i) : e.out_type == OUT_F16 ? load_out_elem<OUT_F16>(e.residual, roff + i) : load_out_elem<OUT_F32>(e.residual, roff + i);
+        }
+    }
+    if (e.mode == EPI_SILU || e.mode == EPI_BIAS_SILU) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = silu_f32(v[i]);
+    }
+}
+
+// two fp32 values -> one 32-bit word of two fp16 (saturating) or bf16 values
+__device__ __forceinline__ uint32_t pack2_out(int out_type, float a, float b) {
+    if (out_type == OUT_F16) {
+        __half2 h = __floats2half2_rn(clamp_f16_range(a), clamp_f16_range(b));
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
 __device__ __forceinline__ void epilogue_store32_dyn(const EpilogueParams& e, const uint32_t (&acc)[32], int row, int col0, int M, int N) {
     if (e.out_type == OUT_BF16) epilogue_store32<OUT_BF16>(e, acc, row, col0, M, N);
     else if (e.out_type == OUT_F16) epilogue_store32<OUT_F16>(e, acc, row, col0, M, N);
