@@ -17,7 +17,6 @@
 #include "../../include/blaze_b200.h"
 #include "decode_kernel.cuh"
 #include "gemm_cluster_kernel.cuh"
-#include "gemm_kernel.cuh"
 #include "prep_kernels.cuh"
 
 using namespace blz;
@@ -97,28 +96,6 @@ int grid_for(int64_t work_items, int threads) {
     return static_cast<int>(g);
 }
 
-using GemmKernelFn = void (*)(const CUtensorMap, const CUtensorMap, const GemmKernelParams);
-
-struct KernelChoice {
-    const void* fn;
-    int bn, stages, acc_bufs, smem, tmem_cols;
-};
-
-template <int KIND, int BN, int STAGES, int ACC>
-KernelChoice choice() {
-    using Cfg = GemmTileConfig<KIND, BN, STAGES, ACC>;
-    return KernelChoice{reinterpret_cast<const void*>(&gemm_tc_kernel<KIND, BN, STAGES, ACC>), BN, STAGES, ACC,
-                        static_cast<int>(Cfg::SMEM_BYTES), static_cast<int>(Cfg::TMEM_COLS)};
-}
-
-KernelChoice pick_kernel(int mma_kind, int bn) {
-    switch (mma_kind) {
-        case MMA_F16: return bn == 256 ? choice<MMA_F16, 256, 4, 2>() : choice<MMA_F16, 128, 6, 2>();
-        case MMA_F8: return bn == 256 ? choice<MMA_F8, 256, 4, 2>() : choice<MMA_F8, 128, 6, 2>();
-        default: return bn == 256 ? choice<MMA_NVF4, 256, 4, 1>() : choice<MMA_NVF4, 128, 5, 2>();
-    }
-}
-
 struct ClusterChoice {
     const void* fn;
     int cg, bn, stages, acc_bufs, smem, tmem_cols, threads;
@@ -158,7 +135,6 @@ struct blz_gemm_plan {
     const void* b_used = nullptr;
     const uint8_t* sfa_used = nullptr;
     const uint8_t* sfb_used = nullptr;
-    int a_elem_bits = 16;
     // device memory the plan owns
     void* own_b = nullptr;
     void* own_sfa = nullptr;
@@ -168,13 +144,9 @@ struct blz_gemm_plan {
     int* own_counters = nullptr;  // decode: per-tile arrival counters
     int* status = nullptr;
     int64_t owned_bytes = 0;
-    // tiled-kernel launch
-    KernelChoice kc{};
     CUtensorMap tm_a{}, tm_b{};
-    GemmKernelParams kp{};
     int grid = 0;
     // cluster-kernel launch (CTA groups of 1 or 2)
-    bool use_cluster = false;
     ClusterChoice cc{};
     ClusterGemmParams cp{};
     CUtensorMap tm_c{};
@@ -277,38 +249,6 @@ blz_status prepare_a_scales(blz_gemm_plan* p) {
 // bytes of one operand row as the tensor core reads it
 int64_t row_bytes(int mma_kind, int64_t K) { return mma_kind == MMA_F16 ? K * 2 : mma_kind == MMA_F8 ? K : K / 2; }
 
-blz_status setup_tiled(blz_gemm_plan* p) {
-    const blz_gemm_desc& d = p->desc;
-    const int64_t rb = row_bytes(p->mma_kind, d.K);
-    const int m_tiles = static_cast<int>(ceil_div(d.M, 128));
-    int bn;
-    if (p->variant == BLZ_VARIANT_TILE_128x256) bn = 256;
-    else if (p->variant == BLZ_VARIANT_TILE_128x128) bn = 128;
-    else bn = (d.N >= 256 && m_tiles * ceil_div(d.N, 256) >= p->num_sms) ? 256 : 128;
-    p->variant = bn == 256 ? BLZ_VARIANT_TILE_128x256 : BLZ_VARIANT_TILE_128x128;
-    p->kc = pick_kernel(p->mma_kind, bn);
-    BLZ_CUDA(cudaFuncSetAttribute(p->kc.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, p->kc.smem));
-
-    blz_status s = encode_map(&p->tm_a, p->a_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.M), static_cast<uint64_t>(rb), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (s) return s;
-    s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rb), 128, static_cast<uint32_t>(bn), CU_TENSOR_MAP_SWIZZLE_128B);
-    if (s) return s;
-
-    GemmKernelParams& kp = p->kp;
-    kp.M = d.M; kp.N = d.N;
-    kp.m_tiles = m_tiles;
-    kp.n_tiles = static_cast<int>(ceil_div(d.N, bn));
-    kp.k_stages = static_cast<int>(ceil_div(rb, 128));
-    const uint32_t fmt = d.kind == BLZ_GEMM_BF16 || d.kind == BLZ_GEMM_W4A16_BF16 ? 1u : 0u;
-    kp.idesc = p->mma_kind == MMA_NVF4 ? make_idesc_nvf4(128, bn) : p->mma_kind == MMA_F8 ? make_idesc(0, 0, 128, bn) : make_idesc(fmt, fmt, 128, bn);
-    kp.sfa = p->sfa_used; kp.sfb = p->sfb_used;
-    kp.sf_katoms = static_cast<int>(sf_katoms(d.K));
-    kp.status = p->status;
-    const int64_t tiles = static_cast<int64_t>(kp.m_tiles) * kp.n_tiles;
-    p->grid = static_cast<int>(tiles < p->num_sms ? tiles : p->num_sms);
-    return BLZ_OK;
-}
-
 blz_status launch_config_cluster(const blz_gemm_plan* p, cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, cudaStream_t stream) {
     cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(p->grid));
@@ -328,7 +268,6 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg) {
     const blz_gemm_desc& d = p->desc;
     const int64_t rb = row_bytes(p->mma_kind, d.K);
     p->cc = pick_cluster_kernel(p->mma_kind, cg);
-    p->use_cluster = true;
     p->variant = cg == 2 ? BLZ_VARIANT_PAIR_256x256 : BLZ_VARIANT_TILE_128x128;
     BLZ_CUDA(cudaFuncSetAttribute(p->cc.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, p->cc.smem));
     const int bn = p->cc.bn, tile_m = 128 * cg;
@@ -542,7 +481,7 @@ blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_p
         }
         if (v == BLZ_VARIANT_PAIR_256x256) s = setup_cluster(p, 2);
         else if (v == BLZ_VARIANT_TILE_128x128) s = setup_cluster(p, 1);
-        else s = setup_tiled(p);
+        else s = BLZ_ERR_INVALID_ARGUMENT;
         p->b_used = keep;
         if (s) return fail(s);
     }
@@ -565,7 +504,7 @@ blz_status blz_gemm_execute(blz_gemm_plan* p, void* C, void* stream_v) {
             dequant_nvfp4_kernel<__nv_bfloat16><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<__nv_bfloat16*>(p->own_w16));
         BLZ_CUDA(cudaGetLastError());
     }
-    if (p->use_cluster) {
+    {
         ClusterGemmParams cp = p->cp;
         fill_epilogue(p, C, cp.epi);
         cp.use_tma_store = cp.epi.vec_ok;
@@ -585,11 +524,6 @@ blz_status blz_gemm_execute(blz_gemm_plan* p, void* C, void* stream_v) {
         BLZ_CUDA(cudaLaunchKernelExC(&cfg, p->cc.fn, cargs));
         return BLZ_OK;
     }
-    GemmKernelParams kp = p->kp;
-    fill_epilogue(p, C, kp.epi);
-    void* args[3] = {&p->tm_a, &p->tm_b, &kp};
-    BLZ_CUDA(cudaLaunchKernel(p->kc.fn, dim3(p->grid), dim3(256), args, static_cast<size_t>(p->kc.smem), stream));
-    return BLZ_OK;
 }
 
 blz_status blz_gemm_plan_set_a(blz_gemm_plan* p, const void* A, const void* A_sf, float a_scale) {
@@ -606,10 +540,7 @@ blz_status blz_gemm_plan_set_a(blz_gemm_plan* p, const void* A, const void* A_sf
     if (p->variant == BLZ_VARIANT_DECODE) return decode_rebind_a(p);
     p->cp.sfa = p->sfa_used;
     const int64_t rb = row_bytes(p->mma_kind, d.K);
-    blz_status s = encode_map(&p->tm_a, A, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.M), static_cast<uint64_t>(rb), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (s) return s;
-    p->kp.sfa = p->sfa_used;
-    return BLZ_OK;
+    return encode_map(&p->tm_a, A, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.M), static_cast<uint64_t>(rb), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 blz_status blz_gemm_plan_check(blz_gemm_plan* p, void* stream_v) {
@@ -635,14 +566,10 @@ blz_status blz_gemm_plan_info(const blz_gemm_plan* p, blz_plan_info* info) {
         info->tile_m = p->decode_mma_n; info->tile_n = 128;
         info->stages = p->decode_stages; info->split_k = p->decode_split;
         info->grid = p->grid; info->smem_bytes = p->decode_smem; info->tmem_cols = p->decode_tmem;
-    } else if (p->use_cluster) {
+    } else {
         info->tile_m = 128 * p->cc.cg; info->tile_n = p->cc.bn;
         info->stages = p->cc.stages; info->split_k = 1;
         info->grid = p->grid; info->smem_bytes = p->cc.smem; info->tmem_cols = p->cc.tmem_cols;
-    } else {
-        info->tile_m = 128; info->tile_n = p->kc.bn;
-        info->stages = p->kc.stages; info->split_k = 1;
-        info->grid = p->grid; info->smem_bytes = p->kc.smem; info->tmem_cols = p->kc.tmem_cols;
     }
     info->launches = p->launches;
     info->workspace_bytes = p->owned_bytes;

@@ -1,0 +1,167 @@
+// common.cuh -- what the GEMM kernels share: operand / epilogue enums, the epilogue parameter block
+// and its arithmetic (alpha -> bias -> SiLU / residual -> narrow, the order of Blaze's
+// src/kernels/gemm_mixed_sm100.cu:202-229), and the optional per-role cycle counters of tuning builds.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "ptx.cuh"
+
+namespace blz {
+
+enum MmaKind : int { MMA_F16 = 0, MMA_F8 = 1, MMA_NVF4 = 2 };
+enum OutType : int { OUT_F16 = 0, OUT_BF16 = 1, OUT_F32 = 2 };
+enum EpiMode : int { EPI_NONE = 0, EPI_BIAS = 1, EPI_SILU = 2, EPI_BIAS_SILU = 3, EPI_RESIDUAL = 4 };
+
+struct EpilogueParams {
+    void* C;                 // [M, ldc] in the output type
+    const void* bias;        // [N] in the output type (fp32 when the output is fp32), or null
+    const void* residual;    // [M, ldr] in the output type, or null
+    long long ldc, ldr;      // row pitches in elements
+    float alpha;
+    int mode;                // EpiMode
+    int out_type;            // OutType
+    int vec_ok;              // rows of C (and residual) are 16-byte aligned: wide stores allowed
+};
+
+
+// Optional per-role cycle accounting, compiled in only with -DBLZ_KERNEL_TIMING (a tuning build):
+// slot layout per CTA, 16 x u64: 0 producer wait-empty, 1 producer total, 2 mma wait-ready,
+// 3 mma wait-accumulator, 4 mma total, 5 epilogue wait-full, 6 epilogue work, 7 epilogue total, 8 tiles.
+#ifdef BLZ_KERNEL_TIMING
+__device__ unsigned long long g_blz_timing[1024 * 16];
+#define BLZ_T_DECL(name) long long name = 0
+#define BLZ_T_NOW() clock64()
+#define BLZ_T_ADD(acc, t0) acc += clock64() - (t0)
+#define BLZ_T_STORE(slot, v) g_blz_timing[(blockIdx.x & 1023) * 16 + (slot)] = static_cast<unsigned long long>(v)
+#else
+#define BLZ_T_DECL(name)
+#define BLZ_T_NOW() 0
+#define BLZ_T_ADD(acc, t0)
+#define BLZ_T_STORE(slot, v)
+#endif
+
+__device__ __forceinline__ float silu_f32(float v) { return v / (1.0f + __expf(-v)); }
+
+// fp32 -> fp16 with finite overflow clamped to +-65504 (NaN stays NaN)
+__device__ __forceinline__ float clamp_f16_range(float v) {
+    return (v != v) ? v : fminf(fmaxf(v, -65504.0f), 65504.0f);
+}
+
+template <int OUT> struct OutElem;
+template <> struct OutElem<OUT_F16> { using type = __half; };
+template <> struct OutElem<OUT_BF16> { using type = __nv_bfloat16; };
+template <> struct OutElem<OUT_F32> { using type = float; };
+
+template <int OUT> __device__ __forceinline__ float load_out_elem(const void* p, long long i) {
+    if constexpr (OUT == OUT_F16) return __half2float(reinterpret_cast<const __half*>(p)[i]);
+    else if constexpr (OUT == OUT_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+    else return reinterpret_cast<const float*>(p)[i];
+}
+
+// Applies the epilogue to 32 consecutive accumulator columns of one row and stores them.
+//   acc: raw fp32 bits from tensor memory; row / col0: position in C.
+template <int OUT>
+__device__ __forceinline__ void epilogue_store32(const EpilogueParams& e, const uint32_t (&acc)[32], int row, int col0, int M, int N) {
+    if (row >= M || col0 >= N) return;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]) * e.alpha;
+    const bool full = (col0 + 32 <= N);
+    if (e.mode == EPI_BIAS || e.mode == EPI_BIAS_SILU) {
+        if (e.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (full || col0 + i < N) v[i] += load_out_elem<OUT>(e.bias, col0 + i);
+        }
+    }
+    if (e.mode == EPI_SILU || e.mode == EPI_BIAS_SILU) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = silu_f32(v[i]);
+    }
+    if (e.mode == EPI_RESIDUAL && e.residual != nullptr) {
+        const long long roff = static_cast<long long>(row) * e.ldr + col0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (full || col0 + i < N) v[i] += load_out_elem<OUT>(e.residual, roff + i);
+    }
+    using T = typename OutElem<OUT>::type;
+    T* dst = reinterpret_cast<T*>(e.C) + static_cast<long long>(row) * e.ldc + col0;
+    if (full && e.vec_ok) {
+        if constexpr (OUT == OUT_F32) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+                *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if constexpr (OUT == OUT_F16) {
+                        __half2 h = __floats2half2_rn(clamp_f16_range(v[i + 2 * j]), clamp_f16_range(v[i + 2 * j + 1]));
+                        w[j] = *reinterpret_cast<uint32_t*>(&h);
+                    } else {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
+                        w[j] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                }
+                *reinterpret_cast<uint4*>(dst + i) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (col0 + i < N) {
+                if constexpr (OUT == OUT_F16) dst[i] = __float2half_rn(clamp_f16_range(v[i]));
+                else if constexpr (OUT == OUT_BF16) dst[i] = __float2bfloat16_rn(v[i]);
+                else dst[i] = v[i];
+            }
+        }
+    }
+}
+
+// alpha, bias, SiLU, residual on 32 consecutive accumulator columns of one row (fp32 in, fp32 out);
+// bias / residual are read in the output's element type and only inside the matrix.
+__device__ __forceinline__ void epilogue_math32(const EpilogueParams& e, const uint32_t (&acc)[32], float (&v)[32], int row, int col0, int M, int N) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]) * e.alpha;
+    if (e.mode == EPI_NONE) return;
+    const bool has_bias = (e.mode == EPI_BIAS || e.mode == EPI_BIAS_SILU) && e.bias != nullptr;
+    const bool has_res = e.mode == EPI_RESIDUAL && e.residual != nullptr && row < M;
+    const long long roff = static_cast<long long>(row) * e.ldr + col0;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        if (col0 + i < N) {
+            if (has_bias) v[i] += e.out_type == OUT_BF16 ? load_out_elem<OUT_BF16>(e.bias, col0 + i) : e.out_type == OUT_F16 ? load_out_elem<OUT_F16>(e.bias, col0 + i) : load_out_elem<OUT_F32>(e.bias, col0 + i);
+            if (has_res) v[i] += e.out_type == OUT_BF16 ? load_out_elem<OUT_BF16>(e.residual, roff + i) : e.out_type == OUT_F16 ? load_out_elem<OUT_F16>(e.residual, roff + i) : load_out_elem<OUT_F32>(e.residual, roff + i);
+        }
+    }
+    if (e.mode == EPI_SILU || e.mode == EPI_BIAS_SILU) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = silu_f32(v[i]);
+    }
+}
+
+// two fp32 values -> one 32-bit word of two fp16 (saturating) or bf16 values
+__device__ __forceinline__ uint32_t pack2_out(int out_type, float a, float b) {
+    if (out_type == OUT_F16) {
+        __half2 h = __floats2half2_rn(clamp_f16_range(a), clamp_f16_range(b));
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ void epilogue_store32_dyn(const EpilogueParams& e, const uint32_t (&acc)[32], int row, int col0, int M, int N) {
+    if (e.out_type == OUT_BF16) epilogue_store32<OUT_BF16>(e, acc, row, col0, M, N);
+    else if (e.out_type == OUT_F16) epilogue_store32<OUT_F16>(e, acc, row, col0, M, N);
+    else epilogue_store32<OUT_F32>(e, acc, row, col0, M, N);
+}
+
+__host__ __device__ constexpr uint32_t tmem_cols_pow2(uint32_t need) {
+    return need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512;
+}
+
+}  // namespace blz

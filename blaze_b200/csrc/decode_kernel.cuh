@@ -9,11 +9,11 @@
 // streams weights; each split writes fp32 partial sums and the CTA that arrives last at a tile
 // adds them in split order 0..S-1, which keeps the result independent of arrival order.
 //
-// Warp roles as in gemm_kernel.cuh: warp 0 TMA producer, warp 1 MMA issuer, warp 2 tensor-memory
+// Warp roles as in gemm_cluster_kernel.cuh: warp 0 TMA producer, warp 1 MMA issuer, warp 2 tensor-memory
 // allocation, warps 4-7 epilogue.  Two CTAs fit one SM.
 #pragma once
 
-#include "gemm_kernel.cuh"
+#include "common.cuh"
 
 namespace blz {
 

@@ -28,7 +28,7 @@
 // gemm_fp4_blkscaled_persistent_kernel (src/kernels/gemm_fp4_blkscaled_sm100.cu:507-624).
 #pragma once
 
-#include "gemm_kernel.cuh"
+#include "common.cuh"
 
 namespace blz {
 
@@ -132,14 +132,18 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
+            BLZ_T_DECL(t_wait_empty);
+            [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
             for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
                 const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
                 const int a_row = (m_tile * CG + static_cast<int>(rank)) * 128;
                 const int b_row = n_tile * BN + static_cast<int>(rank) * static_cast<int>(Cfg::B_ROWS);
                 for (int ks = 0; ks < p.k_stages; ++ks) {
+                    [[maybe_unused]] const long long te = BLZ_T_NOW();
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
                         atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_PRODUCER); *abort_flag = 1; ok = false; break;
                     }
+                    BLZ_T_ADD(t_wait_empty, te);
                     const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
                     mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
@@ -160,6 +164,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
+            BLZ_T_STORE(0, t_wait_empty); BLZ_T_STORE(1, BLZ_T_NOW() - t_begin);
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -168,18 +173,24 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             bool ok = true;
+            BLZ_T_DECL(t_wait_ready); BLZ_T_DECL(t_wait_acc);
+            [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
             for (int tile = group; ok && tile < total_tiles; tile += num_groups, ++it) {
                 const int buf = it % ACC_BUFS;
                 const uint32_t use = static_cast<uint32_t>(it / ACC_BUFS);
+                [[maybe_unused]] const long long ta = BLZ_T_NOW();
                 if (!mbar_wait(acc_empty_bar(buf), (use & 1u) ^ 1u, abort_flag)) {
                     atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_ACC); *abort_flag = 1; ok = false; break;
                 }
+                BLZ_T_ADD(t_wait_acc, ta);
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int ks = 0; ks < p.k_stages; ++ks) {
+                    [[maybe_unused]] const long long tr = BLZ_T_NOW();
                     if (!mbar_wait(ready_bar(stage), phase, abort_flag)) {
                         atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
                     }
+                    BLZ_T_ADD(t_wait_ready, tr);
                     tc_fence_after_sync();
                     const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
@@ -206,6 +217,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     if constexpr (CG == 1) tc_commit(acc_full_bar(buf)); else tc_commit_pair(acc_full_bar(buf), 0x3);
                 }
             }
+            BLZ_T_STORE(2, t_wait_ready); BLZ_T_STORE(3, t_wait_acc); BLZ_T_STORE(4, BLZ_T_NOW() - t_begin); BLZ_T_STORE(8, it);
         }
         __syncwarp();
     } else if (warp == 2) {
@@ -235,13 +247,18 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         int it = 0;
         int obuf = 0;
         bool ok = true;
+        BLZ_T_DECL(t_wait); BLZ_T_DECL(t_work);
+        [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
         for (int tile = group; tile < total_tiles; tile += num_groups, ++it) {
             const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
             const int buf = it % ACC_BUFS;
             const uint32_t use = static_cast<uint32_t>(it / ACC_BUFS);
+            [[maybe_unused]] const long long tw = BLZ_T_NOW();
             if (ok && !mbar_wait(acc_full_bar(buf), use & 1u, abort_flag)) {
                 atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_EPILOGUE); *abort_flag = 1; ok = false;
             }
+            BLZ_T_ADD(t_wait, tw);
+            [[maybe_unused]] const long long tk = BLZ_T_NOW();
             // After a give-up the warps still walk the same named-barrier sequence (without touching
             // tensor memory or C) so that no epilogue warp is left waiting for another.
             tc_fence_after_sync();
@@ -305,7 +322,9 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             if (ok && lane == 0) {
                 if constexpr (CG == 1) mbar_arrive(acc_empty_bar(buf)); else mbar_arrive_cluster(acc_empty_bar(buf), 0);
             }
+            BLZ_T_ADD(t_work, tk);
         }
+        if (epi_tid == 0) { BLZ_T_STORE(5, t_wait); BLZ_T_STORE(6, t_work); BLZ_T_STORE(7, BLZ_T_NOW() - t_begin); }
         if (epi_tid == 0) tma_store_wait_all<0>();     // staging memory must outlive the last store's reads
     } else if (warp >= 8) {
         // -------------------------------- NVFP4: scale factors smem -> registers -> tensor memory

@@ -28,13 +28,13 @@ constexpr int FP4_BLOCK_SIZE = 16;            // values per E4M3 block scale
 constexpr int FP4_BLKSCALED_BLOCK_SIZE = 16;
 
 // Tile shapes of the kernels behind each entry point (informational).
-struct Fp8GemmConfig { static constexpr int TILE_M = 128, TILE_N = 256, TILE_K = 128, BLOCK_SIZE = 256, PIPELINE_STAGES = 4; };
-struct Fp4GemmConfig { static constexpr int TILE_M = 128, TILE_N = 256, TILE_K = 256, BLOCK_SIZE = 256, PIPELINE_STAGES = 4; };
+struct Fp8GemmConfig { static constexpr int TILE_M = 256, TILE_N = 256, TILE_K = 128, BLOCK_SIZE = 256, PIPELINE_STAGES = 6; };
+struct Fp4GemmConfig { static constexpr int TILE_M = 256, TILE_N = 256, TILE_K = 256, BLOCK_SIZE = 384, PIPELINE_STAGES = 5; };
 struct Fp4BlkScaledConfig {
-    static constexpr int TILE_M = 128, TILE_N = 256, TILE_K = 256, K_PER_MMA = 64, BLOCK_SIZE = 256, PIPELINE_STAGES = 4;
+    static constexpr int TILE_M = 256, TILE_N = 256, TILE_K = 256, K_PER_MMA = 64, BLOCK_SIZE = 384, PIPELINE_STAGES = 5;
     static constexpr int SF_VEC_SIZE = 16;
 };
-struct MixedGemmConfig { static constexpr int TILE_M = 128, TILE_N = 256, TILE_K = 64, BLOCK_SIZE = 256, PIPELINE_STAGES = 4; };
+struct MixedGemmConfig { static constexpr int TILE_M = 256, TILE_N = 256, TILE_K = 64, BLOCK_SIZE = 256, PIPELINE_STAGES = 6; };
 
 enum class GemmEpilogue { NONE, BIAS, SILU, BIAS_SILU };
 enum class Fp4Epilogue { NONE, BIAS, SILU, BIAS_SILU };

@@ -53,11 +53,11 @@ def _dense_inputs(oracle, kind, M, N, K, scale=1.0):
     ("f16", "f32", "128x128", (128, 128, 256)),      # one tile, four K stages
     ("f16", "f32", "128x128", (256, 256, 256)),      # BASELINE config 1 shape
     ("bf16", "bf16", "128x128", (256, 384, 512)),
-    ("bf16", "bf16", "128x256", (256, 512, 192)),
-    ("f16", "f16", "128x256", (384, 768, 1024)),
+    ("bf16", "bf16", "256x256", (256, 512, 192)),
+    ("f16", "f16", "256x256", (384, 768, 1024)),
     ("bf16", "f32", "auto", (300, 200, 136)),        # ragged in M, N and K
     ("f16", "bf16", "auto", (1, 128, 64)),           # single row
-    ("bf16", "bf16", "128x256", (129, 520, 72)),     # ragged tiles, 256-wide variant
+    ("bf16", "bf16", "256x256", (129, 520, 72)),     # ragged tiles, 256-wide variant
     ("bf16", "bf16", "auto", (2048, 2304, 1024)),    # several tiles per CTA: ring wrap, both accumulators
     ("bf16", "bf16", "256x256", (256, 256, 64)),     # CTA pair, one tile, one K stage
     ("bf16", "bf16", "256x256", (512, 512, 256)),
@@ -129,10 +129,10 @@ def _fp8_inputs(oracle, M, N, K):
 @pytest.mark.parametrize("variant,shape", [
     ("128x128", (128, 128, 128)),
     ("128x128", (256, 256, 512)),
-    ("128x256", (256, 512, 384)),
+    ("256x256", (256, 512, 384)),
     ("auto", (200, 328, 144)),
     ("auto", (32, 4096, 1024)),
-    ("128x256", (1024, 2048, 2048)),
+    ("256x256", (1024, 2048, 2048)),
     ("256x256", (256, 256, 128)),
     ("256x256", (512, 768, 512)),
     ("256x256", (200, 328, 144)),
@@ -200,13 +200,13 @@ def _nvfp4_ref(oracle, qa, qb, out_dtype="bf16", **epi):
     ("128x128", (128, 128, 256)),      # one tile, one K stage
     ("128x128", (128, 128, 1024)),     # one tile, four K stages
     ("128x128", (256, 384, 512)),
-    ("128x256", (128, 256, 256)),
-    ("128x256", (384, 768, 1536)),
+    ("256x256", (128, 256, 256)),
+    ("256x256", (384, 768, 1536)),
     ("auto", (200, 328, 160)),         # ragged M, N; K not a multiple of the 256-value stage
-    ("128x256", (129, 520, 96)),
+    ("256x256", (129, 520, 96)),
     ("128x128", (100, 72, 64)),
     ("auto", (1024, 4096, 2048)),
-    ("128x256", (2048, 2304, 1024)),   # several tiles per CTA
+    ("256x256", (2048, 2304, 1024)),   # several tiles per CTA
     ("256x256", (256, 256, 256)),      # CTA pair: one tile, one K stage
     ("256x256", (256, 256, 2048)),     # CTA pair: the stage ring wraps
     ("256x256", (512, 768, 1536)),
@@ -235,7 +235,7 @@ def test_nvfp4(oracle, cuda_device, variant, shape):
     plan.destroy()
 
 
-@pytest.mark.parametrize("variant,M", [("128x128", 128), ("256x256", 256), ("128x256", 128), ("decode", 16)])
+@pytest.mark.parametrize("variant,M", [("128x128", 128), ("256x256", 256), ("256x256", 128), ("decode", 16)])
 def test_nvfp4_position_coded(oracle, cuda_device, variant, M):
     """Catches transposition, nibble order and scale-layout errors that constant fills hide:
     row m of A is one-hot at k = (37*m + 5) % K with its own block scale, every weight and every
