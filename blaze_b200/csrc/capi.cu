@@ -15,7 +15,8 @@
 #include <type_traits>
 
 #include "../../include/blaze_b200.h"
-#include "decode_kernel.cuh"
+#include "decode_split.h"
+#include "decode_stream_kernel.cuh"
 #include "gemm_cluster_kernel.cuh"
 #include "prep_kernels.cuh"
 
@@ -140,8 +141,6 @@ struct blz_gemm_plan {
     void* own_sfa = nullptr;
     void* own_sfb = nullptr;
     void* own_w16 = nullptr;      // W4A16: weights expanded to 16 bit, refreshed by every execute
-    void* own_split = nullptr;    // decode: fp32 partial sums
-    int* own_counters = nullptr;  // decode: per-tile arrival counters
     int* status = nullptr;
     int64_t owned_bytes = 0;
     CUtensorMap tm_a{}, tm_b{};
@@ -152,7 +151,7 @@ struct blz_gemm_plan {
     CUtensorMap tm_c{};
     const void* tm_c_ptr = nullptr;   // the C the cached output map was encoded for
     // decode-kernel launch
-    DecodeKernelParams dp{};
+    DecodeStreamParams dp{};
     int decode_smem = 0, decode_stages = 0, decode_split = 1, decode_mma_n = 0, decode_tmem = 0;
     const void* decode_fn = nullptr;
     int launches = 1;
@@ -321,8 +320,8 @@ struct DecodeChoice { const void* fn; int mma_n, stages, smem; };
 
 template <int MMA_N, int STAGES>
 DecodeChoice decode_choice() {
-    return DecodeChoice{reinterpret_cast<const void*>(&decode_nvf4_kernel<MMA_N, STAGES>), MMA_N, STAGES,
-                        static_cast<int>(DecodeConfig<MMA_N, STAGES>::SMEM_BYTES)};
+    return DecodeChoice{reinterpret_cast<const void*>(&decode_stream_kernel<MMA_N, STAGES>), MMA_N, STAGES,
+                        static_cast<int>(DecodeStreamConfig<MMA_N, STAGES>::SMEM_BYTES)};
 }
 
 int env_int(const char* name, int fallback) {
@@ -342,39 +341,24 @@ blz_status decode_setup(blz_gemm_plan* p) {
     const blz_gemm_desc& d = p->desc;
     const DecodeChoice dc = d.M <= 16 ? decode_choice<16, 5>() : d.M <= 32 ? decode_choice<32, 4>() : decode_choice<64, 3>();
     p->decode_fn = dc.fn; p->decode_mma_n = dc.mma_n; p->decode_stages = dc.stages; p->decode_smem = dc.smem;
-    p->decode_tmem = 128;
+    p->decode_tmem = 256;
     BLZ_CUDA(cudaFuncSetAttribute(dc.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, dc.smem));
     const int64_t rb = d.K / 2;
     blz_status s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rb), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (s) return s;
     if ((s = decode_encode_x(p))) return s;
 
-    DecodeKernelParams& dp = p->dp;
+    DecodeStreamParams& dp = p->dp;
     dp.M = d.M; dp.N = d.N;
     dp.n_tiles = static_cast<int>(ceil_div(d.N, 128));
     dp.k_stages_total = static_cast<int>(ceil_div(rb, 128));
-    // Split K until every SM has a CTA, keeping at least two pipeline stages per split.
-    int want = env_int("BLZ_DECODE_SPLIT", 0);
-    if (want <= 0) want = static_cast<int>(ceil_div(p->num_sms, dp.n_tiles));
-    int max_split = dp.k_stages_total / 2 > 0 ? dp.k_stages_total / 2 : 1;
-    if (want > max_split) want = max_split;
-    if (want < 1) want = 1;
-    dp.stages_per_split = static_cast<int>(ceil_div(dp.k_stages_total, want));
-    dp.split = static_cast<int>(ceil_div(dp.k_stages_total, dp.stages_per_split));
+    dp.split = decode_pick_split(dp.n_tiles, dp.k_stages_total, p->num_sms, decode_max_split(dc.mma_n), env_int("BLZ_DECODE_SPLIT", 0));
+    dp.stages_per_split = static_cast<int>(ceil_div(dp.k_stages_total, dp.split));
     dp.idesc = make_idesc_nvf4(128, static_cast<uint32_t>(dc.mma_n));
     dp.sfw = p->sfb_used; dp.sfx = p->sfa_used;
     dp.sf_katoms = static_cast<int>(sf_katoms(d.K));
     dp.status = p->status;
     p->decode_split = dp.split;
-    if (dp.split > 1) {
-        const int64_t bytes = static_cast<int64_t>(dp.split) * dc.mma_n * dp.n_tiles * 128 * sizeof(float);
-        if ((s = dev_alloc(p, &p->own_split, bytes, false))) return s;
-        void* c = nullptr;
-        if ((s = dev_alloc(p, &c, static_cast<int64_t>(dp.n_tiles) * sizeof(int), true))) return s;
-        p->own_counters = static_cast<int*>(c);
-    }
-    dp.partial = static_cast<float*>(p->own_split);
-    dp.counters = p->own_counters;
     p->grid = dp.n_tiles * dp.split;
     return BLZ_OK;
 }
@@ -385,11 +369,30 @@ blz_status decode_rebind_a(blz_gemm_plan* p) {
 }
 
 blz_status decode_launch(blz_gemm_plan* p, void* C, cudaStream_t stream) {
-    DecodeKernelParams dp = p->dp;
+    DecodeStreamParams dp = p->dp;
     fill_epilogue(p, C, dp.epi);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(p->grid));
+    cfg.blockDim = dim3(384);
+    cfg.dynamicSmemBytes = static_cast<size_t>(p->decode_smem);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    // the K splits of one tile form a cluster (partial sums travel through distributed shared memory)
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = static_cast<unsigned>(dp.split);
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+    // programmatic dependent launch: set-up and weight prefetch overlap the previous kernel's tail
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = env_int("BLZ_DECODE_NO_PDL", 0) ? 0 : 1;
+    ++na;
+    cfg.attrs = attr;
+    cfg.numAttrs = static_cast<unsigned>(na);
     // tm_b maps the weights (the 128-row operand), tm_a the activations
     void* args[3] = {&p->tm_b, &p->tm_a, &dp};
-    BLZ_CUDA(cudaLaunchKernel(p->decode_fn, dim3(p->grid), dim3(256), args, static_cast<size_t>(p->decode_smem), stream));
+    BLZ_CUDA(cudaLaunchKernelExC(&cfg, p->decode_fn, args));
     return BLZ_OK;
 }
 
@@ -579,7 +582,7 @@ blz_status blz_gemm_plan_info(const blz_gemm_plan* p, blz_plan_info* info) {
 blz_status blz_gemm_plan_destroy(blz_gemm_plan* p) {
     if (!p) return BLZ_OK;
     cudaFree(p->own_b); cudaFree(p->own_sfa); cudaFree(p->own_sfb); cudaFree(p->own_w16);
-    cudaFree(p->own_split); cudaFree(p->own_counters); cudaFree(p->status);
+    cudaFree(p->status);
     (void)cudaGetLastError();
     delete p;
     return BLZ_OK;

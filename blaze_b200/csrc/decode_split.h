@@ -1,0 +1,23 @@
+// decode_split.h -- how the skinny-M kernels split K across CTAs; shared by the plan path and the
+// allocation-free entry point so that both partition K identically (bit-identical results).
+#pragma once
+
+namespace blz {
+
+// largest K split the skinny-M kernel supports for an instruction N of 16 / 32 / 64 (the partial
+// sums of the other splits must fit the leader's stage buffers)
+inline int decode_max_split(int mma_n) { return mma_n <= 16 ? 8 : mma_n <= 32 ? 4 : 2; }
+
+// Smallest power-of-two split that gives at least 0.8 CTAs per SM, capped by `max_split`, by two
+// pipeline stages per split and by "no split is empty".  `forced` > 0 overrides the first rule.
+inline int decode_pick_split(int n_tiles, int k_stages_total, int num_sms, int max_split, int forced) {
+    int s = 1;
+    if (forced > 0) { while (s * 2 <= forced) s *= 2; }
+    else { while (s < 8 && n_tiles * s * 10 < num_sms * 8) s *= 2; }
+    while (s > max_split) s /= 2;
+    while (s > 1 && k_stages_total / s < 2) s /= 2;
+    while (s > 1 && (s - 1) * ((k_stages_total + s - 1) / s) >= k_stages_total) s /= 2;
+    return s;
+}
+
+}  // namespace blz

@@ -19,6 +19,7 @@
 
 #include "../../include/blaze_b200.h"
 #include "decode_kernel.cuh"
+#include "decode_split.h"
 
 using namespace blz;
 
@@ -120,12 +121,9 @@ extern "C" blz_status blz_gemm_nvfp4_decode_static(const void* A, const void* A_
     dp.n_tiles = (N + 127) / 128;
     const int64_t row_bytes = K / 2;
     dp.k_stages_total = static_cast<int>((row_bytes + 127) / 128);
-    int want = (g_num_sms[dev] + dp.n_tiles - 1) / dp.n_tiles;
-    const int max_split = dp.k_stages_total / 2 > 0 ? dp.k_stages_total / 2 : 1;
-    if (want > max_split) want = max_split;
-    if (want < 1) want = 1;
-    dp.stages_per_split = (dp.k_stages_total + want - 1) / want;
-    dp.split = (dp.k_stages_total + dp.stages_per_split - 1) / dp.stages_per_split;
+    // the same K partition as the plan path, so both give bit-identical sums
+    dp.split = decode_pick_split(dp.n_tiles, dp.k_stages_total, g_num_sms[dev], decode_max_split(kc.mma_n), 0);
+    dp.stages_per_split = (dp.k_stages_total + dp.split - 1) / dp.split;
     if (static_cast<size_t>(dp.n_tiles) > MAX_TILES) return BLZ_ERR_TOO_LARGE;
     const size_t partial_need = dp.split > 1 ? static_cast<size_t>(dp.split) * kc.mma_n * dp.n_tiles * 128 * sizeof(float) : 0;
     if (partial_need > PARTIAL_BYTES) return BLZ_ERR_TOO_LARGE;
