@@ -68,7 +68,7 @@ struct DecodeStreamConfig {
     static_assert(MMA_N % 16 == 0 && MMA_N >= 16 && MMA_N <= 64, "activation rows per instruction");
     static_assert(SF_BASE + STAGES * SF_COLS <= TMEM_COLS, "scale-factor columns exceed the allocation");
     static_assert(SMEM_BYTES <= 115000, "two CTAs must fit one SM");
-    static_assert(MMA_N * 128 * 4 <= STAGES * STAGE_BYTES, "output staging must fit the stage buffers");
+    static_assert(MMA_N * 128 * 4 <= STAGES * STAGE_BYTES, "fp32 output staging must fit the stage buffers");
 };
 
 template <int MMA_N, int STAGES>
@@ -90,6 +90,10 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + slot_off + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    [[maybe_unused]] const long long t_entry = BLZ_T_NOW();
+#ifdef BLZ_KERNEL_TIMING
+    if (threadIdx.x == 0) BLZ_T_STORE(9, global_timer_ns());
+#endif
     const int n_tile = blockIdx.x / p.split;
     const int split_idx = blockIdx.x % p.split;             // = rank in the cluster
     const int ks_begin = split_idx * p.stages_per_split;
@@ -116,6 +120,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
     // Everything this grid still needs from its predecessor is read after griddep_wait(); the
     // successor may start its own set-up and weight prefetch now.
     griddep_launch_dependents();
+#ifdef BLZ_KERNEL_TIMING
+    if (threadIdx.x == 0) BLZ_T_STORE(11, clock64() - t_entry);
+#endif
 
     if (warp == 0) {
         if (lane == 0) {
@@ -133,6 +140,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
                 bulk_load_1d(ssfw, p.sfw + (static_cast<size_t>(n_tile) * p.sf_katoms + static_cast<size_t>(ks) * 4) * 512, Cfg::SF_BYTES, full_bar(i));
             }
             griddep_wait();
+#ifdef BLZ_KERNEL_TIMING
+            BLZ_T_STORE(12, clock64() - t_entry); BLZ_T_STORE(14, global_timer_ns());
+#endif
             for (int ks = ks_begin; ks < ks_end; ++ks) {
                 const uint32_t sw = base + stage * Cfg::STAGE_BYTES;
                 const uint32_t sx = sw + Cfg::W_BYTES;
@@ -161,6 +171,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
                 if (!mbar_wait(ready_bar(stage), phase, abort_flag)) {
                     atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
                 }
+#ifdef BLZ_KERNEL_TIMING
+                if (ks == ks_begin) BLZ_T_STORE(13, clock64() - t_entry);
+#endif
                 tc_fence_after_sync();
                 const uint32_t sw = base + stage * Cfg::STAGE_BYTES;
                 const uint32_t sx = sw + Cfg::W_BYTES;
@@ -175,6 +188,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
             if (ok) tc_commit(acc_full_bar);
+            BLZ_T_STORE(4, BLZ_T_NOW() - t_entry);
         }
         __syncwarp();
     } else if (warp >= 8) {
@@ -213,8 +227,21 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
     const bool is_epi = (warp >= 4 && warp < 8);
     const int q = warp & 3;
     const int n_local = q * 32 + lane;
+    // The epilogue's parameters are fetched now, while these warps would only wait: the first touch
+    // of a parameter line costs a constant-cache miss of several hundred cycles, and this kernel's
+    // epilogue runs once, on the critical path of the next kernel in the stream.
+    const float e_alpha = p.epi.alpha;
+    const int e_mode = p.epi.mode, e_out = p.epi.out_type, e_vec = p.epi.vec_ok, p_M = p.M, p_N = p.N, p_split = p.split;
+    const long long e_ldc = p.epi.ldc, e_ldr = p.epi.ldr;
+    void* const e_C = p.epi.C;
+    const void* const e_bias = p.epi.bias;
+    const void* const e_res = p.epi.residual;
+    asm volatile("" ::"f"(e_alpha), "r"(e_mode), "r"(e_out), "r"(e_vec), "r"(p_M), "r"(p_N), "r"(p_split), "l"(e_ldc), "l"(e_ldr), "l"(e_C), "l"(e_bias), "l"(e_res));
     if (is_epi) {
         epi_ok = mbar_wait(acc_full_bar, 0u, abort_flag);
+#ifdef BLZ_KERNEL_TIMING
+        if (threadIdx.x == 128) BLZ_T_STORE(5, clock64() - t_entry);
+#endif
         if (!epi_ok) { atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_EPILOGUE); *abort_flag = 1; }
 #pragma unroll
         for (int m = 0; m < MMA_N; ++m) acc[m] = 0.0f;
@@ -231,76 +258,104 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
             tmem_ld_wait();
             tc_fence_before_sync();
         }
+#ifdef BLZ_KERNEL_TIMING
+        if (threadIdx.x == 128) BLZ_T_STORE(1, clock64() - t_entry);
+#endif
     }
-    if (p.split > 1) {
+    if (p_split > 1) {
         cluster_sync_all();                 // every CTA of the tile is past its main loop: the leader's stage buffers are free
         if (is_epi && split_idx != 0) {
             // partial sums of split s go to slot s-1 of the leader: [slot][m][128] fp32
             const uint32_t dst = base + (static_cast<uint32_t>(split_idx - 1) * MMA_N * 128 + n_local) * 4;
 #pragma unroll
             for (int m = 0; m < MMA_N; ++m)
-                if (m < p.M) st_shared_cluster_f32(dst + m * 512, 0, acc[m]);
+                if (m < p_M) st_shared_cluster_f32(dst + m * 512, 0, acc[m]);
         }
         cluster_sync_all();                 // partial sums have landed in the leader
         if (is_epi && split_idx == 0) {
             const float* part = reinterpret_cast<const float*>(gen_base);
 #pragma unroll
             for (int m = 0; m < MMA_N; ++m) {
-                if (m < p.M) {
+                if (m < p_M) {
                     float sum = acc[m];
-                    for (int s = 1; s < p.split; ++s) sum += part[(s - 1) * MMA_N * 128 + m * 128 + n_local];
+                    for (int s = 1; s < p_split; ++s) sum += part[(s - 1) * MMA_N * 128 + m * 128 + n_local];
                     acc[m] = sum;
                 }
             }
         }
     }
     if (is_epi && split_idx == 0) {
-        // transpose through shared memory ([m][128] in the output type), then row-wise 16-byte stores
-        const EpilogueParams& e = p.epi;
-        const int esize = e.out_type == OUT_F32 ? 4 : 2;
-        const int n = n_tile * 128 + n_local;
+        // Transpose through shared memory: the raw fp32 sums go to [m][128] with the shortest
+        // possible straight-line code (this code runs once per CTA, so every instruction line is an
+        // instruction-cache miss on the critical path); the epilogue arithmetic and the narrowing
+        // happen in the compact row-store loop below.
+#ifdef BLZ_KERNEL_TIMING
+        if (threadIdx.x == 128) BLZ_T_STORE(2, clock64() - t_entry);
+#endif
         griddep_wait();                      // bias / residual may come from the predecessor; C may be read by it
         named_barrier_sync(1, 128);          // all reads of the partial sums are done: the buffer can be reused
-        uint8_t* stag = gen_base;
+        float* stag = reinterpret_cast<float*>(gen_base);
 #pragma unroll
-        for (int m = 0; m < MMA_N; ++m) {
-            if (m < p.M) {
-                float v = acc[m] * e.alpha;
-                if (n < p.N) {
-                    if ((e.mode == EPI_BIAS || e.mode == EPI_BIAS_SILU) && e.bias != nullptr)
-                        v += e.out_type == OUT_BF16 ? load_out_elem<OUT_BF16>(e.bias, n) : e.out_type == OUT_F16 ? load_out_elem<OUT_F16>(e.bias, n) : load_out_elem<OUT_F32>(e.bias, n);
-                    if (e.mode == EPI_SILU || e.mode == EPI_BIAS_SILU) v = silu_f32(v);
-                    if (e.mode == EPI_RESIDUAL && e.residual != nullptr) {
-                        const long long roff = static_cast<long long>(m) * e.ldr + n;
-                        v += e.out_type == OUT_BF16 ? load_out_elem<OUT_BF16>(e.residual, roff) : e.out_type == OUT_F16 ? load_out_elem<OUT_F16>(e.residual, roff) : load_out_elem<OUT_F32>(e.residual, roff);
+        for (int m = 0; m < MMA_N; ++m) stag[m * 128 + n_local] = acc[m];
+        named_barrier_sync(1, 128);
+#ifdef BLZ_KERNEL_TIMING
+        if (threadIdx.x == 128) BLZ_T_STORE(6, clock64() - t_entry);
+#endif
+        if (epi_ok) {
+            const int tid = threadIdx.x - 128;
+            const int esize = e_out == OUT_F32 ? 4 : 2;
+            // one item = 8 consecutive columns of one row: 128 / 8 = 16 items per row
+#pragma unroll 1
+            for (int c = tid; c < p_M * 16; c += 128) {
+                const int m = c >> 4, j = c & 15;
+                const int col = n_tile * 128 + j * 8;
+                if (col >= p_N) continue;
+                const float4 lo = *reinterpret_cast<const float4*>(stag + m * 128 + j * 8);
+                const float4 hi = *reinterpret_cast<const float4*>(stag + m * 128 + j * 8 + 4);
+                float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+                for (int t = 0; t < 8; ++t) v[t] *= e_alpha;
+                if (e_mode != EPI_NONE) {
+#pragma unroll 1
+                    for (int t = 0; t < 8; ++t) {
+                        const int n = col + t;
+                        if (n >= p_N) break;
+                        if ((e_mode == EPI_BIAS || e_mode == EPI_BIAS_SILU) && e_bias != nullptr)
+                            v[t] += e_out == OUT_BF16 ? load_out_elem<OUT_BF16>(e_bias, n) : e_out == OUT_F16 ? load_out_elem<OUT_F16>(e_bias, n) : load_out_elem<OUT_F32>(e_bias, n);
+                        if (e_mode == EPI_SILU || e_mode == EPI_BIAS_SILU) v[t] = silu_f32(v[t]);
+                        if (e_mode == EPI_RESIDUAL && e_res != nullptr) {
+                            const long long roff = static_cast<long long>(m) * e_ldr + n;
+                            v[t] += e_out == OUT_BF16 ? load_out_elem<OUT_BF16>(e_res, roff) : e_out == OUT_F16 ? load_out_elem<OUT_F16>(e_res, roff) : load_out_elem<OUT_F32>(e_res, roff);
+                        }
                     }
                 }
-                if (e.out_type == OUT_F32) reinterpret_cast<float*>(stag)[m * 128 + n_local] = v;
-                else if (e.out_type == OUT_BF16) reinterpret_cast<__nv_bfloat16*>(stag)[m * 128 + n_local] = __float2bfloat16_rn(v);
-                else reinterpret_cast<__half*>(stag)[m * 128 + n_local] = __float2half_rn(clamp_f16_range(v));
-            }
-        }
-        named_barrier_sync(1, 128);
-        if (epi_ok) {
-            const int row_bytes = 128 * esize;
-            const int chunks_per_row = row_bytes / 16;
-            const int tid = threadIdx.x - 128;
-            const int cols_per_chunk = 16 / esize;
-            for (int c = tid; c < p.M * chunks_per_row; c += 128) {
-                const int m = c / chunks_per_row, j = c % chunks_per_row;
-                const int col = n_tile * 128 + j * cols_per_chunk;
-                if (col >= p.N) continue;
-                uint8_t* dst = reinterpret_cast<uint8_t*>(e.C) + (static_cast<long long>(m) * e.ldc + col) * esize;
-                const uint8_t* src = stag + m * row_bytes + j * 16;
-                if (e.vec_ok && col + cols_per_chunk <= p.N) {
-                    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+                uint8_t* dst = reinterpret_cast<uint8_t*>(e_C) + (static_cast<long long>(m) * e_ldc + col) * esize;
+                const bool whole = e_vec && col + 8 <= p_N;
+                if (e_out == OUT_F32) {
+                    if (whole) {
+                        reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
+                        reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+                    } else {
+                        for (int t = 0; t < 8 && col + t < p_N; ++t) reinterpret_cast<float*>(dst)[t] = v[t];
+                    }
                 } else {
-                    for (int b = 0; b < 16 && col * esize + b < p.N * esize; ++b) dst[b] = src[b];
+                    uint32_t w[4];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) w[t] = pack2_out(e_out, v[2 * t], v[2 * t + 1]);
+                    if (whole) {
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                    } else {
+                        for (int t = 0; t < 8 && col + t < p_N; ++t)
+                            reinterpret_cast<uint16_t*>(dst)[t] = static_cast<uint16_t>(w[t >> 1] >> (16 * (t & 1)));
+                    }
                 }
             }
         }
     }
 
+#ifdef BLZ_KERNEL_TIMING
+    if (threadIdx.x == 128) BLZ_T_STORE(7, clock64() - t_entry);
+#endif
     tc_fence_before_sync();
     __syncthreads();
     if (*abort_flag != 0) {
@@ -312,6 +367,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
+#ifdef BLZ_KERNEL_TIMING
+    if (threadIdx.x == 0) { BLZ_T_STORE(10, global_timer_ns()); BLZ_T_STORE(8, clock64() - t_entry); }
+#endif
 }
 
 }  // namespace blz
