@@ -248,6 +248,8 @@ blz_status prepare_a_scales(blz_gemm_plan* p) {
 // bytes of one operand row as the tensor core reads it
 int64_t row_bytes(int mma_kind, int64_t K) { return mma_kind == MMA_F16 ? K * 2 : mma_kind == MMA_F8 ? K : K / 2; }
 
+int env_int(const char* name, int fallback);
+
 blz_status launch_config_cluster(const blz_gemm_plan* p, cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, cudaStream_t stream) {
     cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(p->grid));
@@ -278,6 +280,12 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg) {
     cp.M = d.M; cp.N = d.N;
     cp.m_tiles = static_cast<int>(ceil_div(d.M, tile_m));
     cp.n_tiles = static_cast<int>(ceil_div(d.N, bn));
+    // Rasterisation: when all of A stays in L2 anyway (it is re-read by every column of tiles),
+    // walk M fastest so that concurrent tiles share as few B panels as possible; otherwise cut M
+    // into bands of 8 tiles so that one wave of CTA groups covers a near-square block.
+    cp.group_m = (static_cast<int64_t>(d.M) * rb <= (48ll << 20)) ? cp.m_tiles : 8;
+    cp.group_m = env_int("BLZ_GROUP_M", cp.group_m);
+    if (cp.group_m < 1) cp.group_m = 1;
     cp.k_stages = static_cast<int>(ceil_div(rb, 128));
     const uint32_t fmt = d.kind == BLZ_GEMM_BF16 || d.kind == BLZ_GEMM_W4A16_BF16 ? 1u : 0u;
     cp.idesc = p->mma_kind == MMA_NVF4 ? make_idesc_nvf4(tile_m, bn) : p->mma_kind == MMA_F8 ? make_idesc(0, 0, tile_m, bn) : make_idesc(fmt, fmt, tile_m, bn);

@@ -117,9 +117,11 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+#ifndef BLZ_DECODE_LATE_DEPENDENTS
     // Everything this grid still needs from its predecessor is read after griddep_wait(); the
     // successor may start its own set-up and weight prefetch now.
     griddep_launch_dependents();
+#endif
 #ifdef BLZ_KERNEL_TIMING
     if (threadIdx.x == 0) BLZ_T_STORE(11, clock64() - t_entry);
 #endif
@@ -140,6 +142,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
                 bulk_load_1d(ssfw, p.sfw + (static_cast<size_t>(n_tile) * p.sf_katoms + static_cast<size_t>(ks) * 4) * 512, Cfg::SF_BYTES, full_bar(i));
             }
             griddep_wait();
+#ifdef BLZ_DECODE_LATE_DEPENDENTS
+            griddep_launch_dependents();     // at most one successor prefetches while this grid runs
+#endif
 #ifdef BLZ_KERNEL_TIMING
             BLZ_T_STORE(12, clock64() - t_entry); BLZ_T_STORE(14, global_timer_ns());
 #endif

@@ -8,7 +8,7 @@
 // more stages fit; each CTA accumulates its 128 rows x BN in its own tensor memory.
 // No multicast loads: every CTA fetches its own tiles.
 //
-// Warp roles in every CTA (NVFP4: 12 warps, otherwise 8):
+// Warp roles in every CTA (NVFP4: 12 or 16 warps, otherwise 8):
 //   warp 0      TMA producer: A tile, B tile (its share) and scale-factor atoms -> stage ring,
 //               completion on the CTA's own full barrier
 //   warp 1      MMA issuer (leader CTA only): waits for the stage's ready barrier, issues four
@@ -19,6 +19,8 @@
 //   warps 4-7   epilogue: tcgen05.ld the CTA's 128 accumulator rows, alpha / bias / SiLU / residual,
 //               narrow, swizzled store to a staging buffer, TMA store (row-strided direct stores
 //               when C is not 16-byte aligned)
+//   warps 12-15 NVFP4 with one accumulator buffer only: a second set of epilogue warps; the two
+//               sets drain alternate column chunks, which halves the time the tensor pipe waits
 //   warps 8-11  NVFP4 only: move the stage's scale factors shared memory -> registers -> tensor
 //               memory (tcgen05.st) into that stage's own columns, then arrive on the leader's ready
 //               barrier.  Measured on B200: a tcgen05.cp costs ~70 cycles of the tensor pipe whatever
@@ -35,6 +37,7 @@ namespace blz {
 struct ClusterGemmParams {
     int M, N;
     int m_tiles, n_tiles;    // tiles of (128*CG) x BN
+    int group_m;             // tile rasterisation: bands of this many M tiles are walked N-first
     int k_stages;            // ceil(K bytes per row / 128)
     uint32_t idesc;
     const uint8_t* sfa;      // tiled scale factors of A: [row blocks of 128][sf_katoms][512]
@@ -45,10 +48,27 @@ struct ClusterGemmParams {
     int* status;
 };
 
+// Tile order.  Tiles running at the same time should share operand panels through L2: the M tiles
+// are cut into bands of `group_m`; inside a band the tile index walks M fastest, then N, so one
+// wave of CTA groups covers a roughly square block of group_m x (wave / group_m) tiles instead of
+// a thin stripe that re-reads all of A for every few columns of B.
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int group_m, int& m_tile, int& n_tile) {
+    const int band_tiles = group_m * n_tiles;
+    const int band = tile / band_tiles;
+    const int first_m = band * group_m;
+    const int rows = min(m_tiles - first_m, group_m);
+    const int in_band = tile - band * band_tiles;
+    m_tile = first_m + in_band % rows;
+    n_tile = in_band / rows;
+}
+
 template <int KIND, int CG, int BN, int STAGES, int ACC_BUFS>
 struct ClusterGemmConfig {
     static constexpr bool HAS_SF = (KIND == MMA_NVF4);
-    static constexpr int THREADS = HAS_SF ? 384 : 256;
+    // With a single accumulator buffer the epilogue is on the critical path: two sets of four
+    // epilogue warps (warps 4-7 and 12-15) then drain alternate column chunks.
+    static constexpr int EPI_SETS = (HAS_SF && ACC_BUFS == 1) ? 2 : 1;
+    static constexpr int THREADS = HAS_SF ? (EPI_SETS == 2 ? 512 : 384) : 256;
     static constexpr uint32_t A_BYTES = 128 * 128;
     static constexpr uint32_t B_ROWS = BN / CG;                        // rows of the B tile staged by one CTA
     static constexpr uint32_t B_BYTES = B_ROWS * 128;
@@ -105,7 +125,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             mbar_init(ready_bar(s), Cfg::READY_COUNT);
             mbar_init(empty_bar(s), 1);
         }
-        for (int b = 0; b < ACC_BUFS; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 4 * CG); }
+        for (int b = 0; b < ACC_BUFS; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 4 * CG * Cfg::EPI_SETS); }
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -135,7 +155,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             BLZ_T_DECL(t_wait_empty);
             [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
             for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
-                const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+                int m_tile, n_tile;
+                tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_tile, n_tile);
                 const int a_row = (m_tile * CG + static_cast<int>(rank)) * 128;
                 const int b_row = n_tile * BN + static_cast<int>(rank) * static_cast<int>(Cfg::B_ROWS);
                 for (int ks = 0; ks < p.k_stages; ++ks) {
@@ -147,9 +168,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
                     mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
-                    tma_load_2d(sa, &tm_a, ks * 128, a_row, full_bar(stage));
-                    tma_load_2d(sb, &tm_b, ks * 128, b_row, full_bar(stage));
                     if constexpr (Cfg::HAS_SF) {
+                        // the small scale-factor copies go first: the helper warps need them before the MMA needs the tiles
                         const uint32_t ssfa = sb + Cfg::B_BYTES;
                         const uint32_t ssfb = ssfa + Cfg::SFA_BYTES;
                         const size_t katom = static_cast<size_t>(ks) * 4;
@@ -161,6 +181,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                             bulk_load_1d(ssfb + blk * Cfg::SF_BLOCK_BYTES, p.sfb + (rb * p.sf_katoms + katom) * 512, Cfg::SF_BLOCK_BYTES, full_bar(stage));
                         }
                     }
+                    tma_load_2d(sa, &tm_a, ks * 128, a_row, full_bar(stage));
+                    tma_load_2d(sb, &tm_b, ks * 128, b_row, full_bar(stage));
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -238,10 +260,12 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
             __syncwarp();
         }
-    } else if (warp >= 4 && warp < 8) {
+    } else if ((warp >= 4 && warp < 8) || (Cfg::EPI_SETS == 2 && warp >= 12)) {
         // ---------------------------------------------------------------- epilogue (every CTA)
         const int q = warp & 3;
-        const int epi_tid = threadIdx.x - 128;
+        const int eset = warp >= 12 ? 1 : 0;                       // which set of four epilogue warps
+        const int epi_tid = threadIdx.x - (eset ? 384 : 128);
+        const uint32_t bar_id = 1 + eset;
         const int out_esize = p.epi.out_type == OUT_F32 ? 4 : 2;
         const int chunk_cols = 128 / out_esize;                    // columns per 128-byte staging row
         int it = 0;
@@ -250,7 +274,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         BLZ_T_DECL(t_wait); BLZ_T_DECL(t_work);
         [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
         for (int tile = group; tile < total_tiles; tile += num_groups, ++it) {
-            const int m_tile = tile % p.m_tiles, n_tile = tile / p.m_tiles;
+            int m_tile, n_tile;
+            tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_tile, n_tile);
             const int buf = it % ACC_BUFS;
             const uint32_t use = static_cast<uint32_t>(it / ACC_BUFS);
             [[maybe_unused]] const long long tw = BLZ_T_NOW();
@@ -266,12 +291,13 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             const int r_local = q * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
             if (p.use_tma_store) {
-                for (int c0 = 0; c0 < BN; c0 += chunk_cols) {
-                    // staging buffer `obuf` was handed to a TMA store two chunks ago: wait until that
-                    // store has finished reading it
-                    if (epi_tid == 0) tma_store_wait_read<1>();
-                    named_barrier_sync(1, 128);
-                    const uint32_t sbuf = out_base + obuf * Cfg::OUT_BUF_BYTES;
+                for (int c0 = eset * chunk_cols; c0 < BN; c0 += chunk_cols * Cfg::EPI_SETS) {
+                    // One set: the two staging buffers alternate, buffer `obuf` was handed to a TMA
+                    // store two chunks ago.  Two sets: each set owns one buffer and waits for its own
+                    // previous store.  Either way: wait until that store has finished reading it.
+                    if (epi_tid == 0) { if constexpr (Cfg::EPI_SETS == 2) tma_store_wait_read<0>(); else tma_store_wait_read<1>(); }
+                    named_barrier_sync(bar_id, 128);
+                    const uint32_t sbuf = out_base + (Cfg::EPI_SETS == 2 ? eset : obuf) * Cfg::OUT_BUF_BYTES;
                     if (ok) {
                         for (int h = 0; h < chunk_cols; h += 32) {
                             uint32_t acc[32];
@@ -301,7 +327,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         }
                     }
                     fence_proxy_async_smem();
-                    named_barrier_sync(1, 128);
+                    named_barrier_sync(bar_id, 128);
                     if (epi_tid == 0) {
                         if (ok) tma_store_2d(&tm_c, sbuf, (n_tile * BN + c0) * out_esize, row0);
                         tma_store_commit();
@@ -310,7 +336,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 }
             } else if (ok) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
+                for (int c0 = eset * 32; c0 < BN; c0 += 32 * Cfg::EPI_SETS) {
                     uint32_t acc[32];
                     tmem_ld32(t_row + c0, acc);
                     tmem_ld_wait();
@@ -324,9 +350,9 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
             BLZ_T_ADD(t_work, tk);
         }
-        if (epi_tid == 0) { BLZ_T_STORE(5, t_wait); BLZ_T_STORE(6, t_work); BLZ_T_STORE(7, BLZ_T_NOW() - t_begin); }
+        if (epi_tid == 0 && eset == 0) { BLZ_T_STORE(5, t_wait); BLZ_T_STORE(6, t_work); BLZ_T_STORE(7, BLZ_T_NOW() - t_begin); }
         if (epi_tid == 0) tma_store_wait_all<0>();     // staging memory must outlive the last store's reads
-    } else if (warp >= 8) {
+    } else if (warp >= 8 && warp < 12) {
         // -------------------------------- NVFP4: scale factors smem -> registers -> tensor memory
         if constexpr (Cfg::HAS_SF) {
             const int q = warp & 3;
