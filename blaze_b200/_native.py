@@ -34,6 +34,7 @@ EXPORTS = (
     "blz_gemm_plan_info", "blz_gemm_plan_destroy", "blz_gemm_launch",
     "blz_amax", "blz_quantize_fp8", "blz_quantize_nvfp4", "blz_tiled_scales_bytes", "blz_tile_scales",
     "blz_gemm_nvfp4_decode_static",
+    "blz_peer_buffer_create", "blz_peer_buffer_open", "blz_peer_buffer_close", "blz_peer_buffer_destroy", "blz_gemm_execute_gather",
 )
 
 
@@ -98,6 +99,13 @@ def lib() -> ctypes.CDLL:
     L.blz_tile_scales.argtypes = [vp, i64, i64, i64, i64, vp, vp]
     L.blz_gemm_nvfp4_decode_static.argtypes = [vp, vp, ctypes.c_float, vp, vp, ctypes.c_float, i32, i32, i32, vp, i32, i64, vp, vp]
     L.blz_gemm_nvfp4_decode_static.restype = ctypes.c_int
+    L.blz_peer_buffer_create.argtypes = [i64, ctypes.POINTER(vp), ctypes.c_char_p]
+    L.blz_peer_buffer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+    L.blz_peer_buffer_close.argtypes = [vp]
+    L.blz_peer_buffer_destroy.argtypes = [vp]
+    L.blz_gemm_execute_gather.argtypes = [vp, i32, ctypes.POINTER(vp), i64, i64, vp]
+    for name in ("blz_peer_buffer_create", "blz_peer_buffer_open", "blz_peer_buffer_close", "blz_peer_buffer_destroy", "blz_gemm_execute_gather"):
+        getattr(L, name).restype = ctypes.c_int
     for name in ("blz_gemm_plan_create", "blz_gemm_execute", "blz_gemm_plan_set_a", "blz_gemm_plan_check", "blz_gemm_plan_info",
                  "blz_gemm_plan_destroy", "blz_gemm_launch", "blz_amax", "blz_quantize_fp8", "blz_quantize_nvfp4", "blz_tile_scales"):
         getattr(L, name).restype = ctypes.c_int

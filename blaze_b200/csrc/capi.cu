@@ -148,8 +148,10 @@ struct blz_gemm_plan {
     // cluster-kernel launch (CTA groups of 1 or 2)
     ClusterChoice cc{};
     ClusterGemmParams cp{};
-    CUtensorMap tm_c{};
-    const void* tm_c_ptr = nullptr;   // the C the cached output map was encoded for
+    OutputMaps out{};
+    const void* out_ptr[BLZ_MAX_DST] = {};   // what the cached output maps were encoded for
+    int64_t out_ld = 0;
+    int out_n = 0;
     // decode-kernel launch
     DecodeStreamParams dp{};
     int decode_smem = 0, decode_stages = 0, decode_split = 1, decode_mma_n = 0, decode_tmem = 0;
@@ -404,6 +406,55 @@ blz_status decode_launch(blz_gemm_plan* p, void* C, cudaStream_t stream) {
     return BLZ_OK;
 }
 
+// Launches the cluster kernel.  `dst` are the bases of n_dst output matrices with row pitch `ld`
+// (elements); the tile block goes to columns [col_offset, col_offset + N) of each.
+blz_status launch_cluster(blz_gemm_plan* p, int n_dst, void* const* dst, int64_t ld, int64_t col_offset, cudaStream_t stream) {
+    const blz_gemm_desc& d = p->desc;
+    if (p->own_w16) {
+        const int64_t blocks16 = static_cast<int64_t>(d.N) * (d.K / 16);
+        if (d.kind == BLZ_GEMM_W4A16_F16)
+            dequant_nvfp4_kernel<__half><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<__half*>(p->own_w16));
+        else
+            dequant_nvfp4_kernel<__nv_bfloat16><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<__nv_bfloat16*>(p->own_w16));
+        BLZ_CUDA(cudaGetLastError());
+    }
+    const int eb = elem_bytes_out(d.out_dtype);
+    ClusterGemmParams cp = p->cp;
+    cp.epi.C = static_cast<uint8_t*>(dst[0]) + col_offset * eb;
+    cp.epi.bias = d.bias; cp.epi.residual = d.residual;
+    cp.epi.ldc = ld; cp.epi.ldr = ld;
+    cp.epi.alpha = d.a_scale * d.b_scale;
+    cp.epi.mode = d.epilogue;
+    cp.epi.out_type = d.out_dtype;
+    bool vec = ((ld * eb) & 15) == 0 && ((col_offset * eb) & 15) == 0;
+    for (int i = 0; i < n_dst; ++i) vec = vec && (reinterpret_cast<uintptr_t>(dst[i]) & 15u) == 0;
+    if (d.residual) vec = vec && (reinterpret_cast<uintptr_t>(d.residual) & 15u) == 0;
+    cp.epi.vec_ok = vec ? 1 : 0;
+    cp.use_tma_store = cp.epi.vec_ok;
+    cp.n_dst = n_dst;
+    if (n_dst > 1 && !cp.use_tma_store) return BLZ_ERR_INVALID_ARGUMENT;   // peer outputs go through TMA stores only
+    if (cp.use_tma_store) {
+        bool same = p->out_n == n_dst && p->out_ld == ld * 1000003 + col_offset;
+        for (int i = 0; same && i < n_dst; ++i) same = p->out_ptr[i] == dst[i];
+        if (!same) {
+            for (int i = 0; i < n_dst; ++i) {
+                blz_status s = encode_map(&p->out.m[i], static_cast<uint8_t*>(dst[i]) + col_offset * eb, static_cast<uint64_t>(d.N) * eb,
+                                          static_cast<uint64_t>(d.M), static_cast<uint64_t>(ld) * eb, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+                if (s) return s;
+                p->out_ptr[i] = dst[i];
+            }
+            p->out_n = n_dst; p->out_ld = ld * 1000003 + col_offset;
+        }
+    } else if (p->out_n == 0) {
+        p->out.m[0] = p->tm_a;                  // a valid descriptor the kernel never stores through
+    }
+    cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[1];
+    launch_config_cluster(p, cfg, attr, stream);
+    void* cargs[4] = {&p->tm_a, &p->tm_b, &p->out, &cp};
+    BLZ_CUDA(cudaLaunchKernelExC(&cfg, p->cc.fn, cargs));
+    return BLZ_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -507,34 +558,18 @@ blz_status blz_gemm_execute(blz_gemm_plan* p, void* C, void* stream_v) {
     const blz_gemm_desc& d = p->desc;
     if (p->variant == BLZ_VARIANT_DECODE) return decode_launch(p, C, stream);
 
-    if (p->own_w16) {
-        const int64_t blocks16 = static_cast<int64_t>(d.N) * (d.K / 16);
-        if (d.kind == BLZ_GEMM_W4A16_F16)
-            dequant_nvfp4_kernel<__half><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<__half*>(p->own_w16));
-        else
-            dequant_nvfp4_kernel<__nv_bfloat16><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<__nv_bfloat16*>(p->own_w16));
-        BLZ_CUDA(cudaGetLastError());
-    }
-    {
-        ClusterGemmParams cp = p->cp;
-        fill_epilogue(p, C, cp.epi);
-        cp.use_tma_store = cp.epi.vec_ok;
-        if (cp.use_tma_store) {
-            if (p->tm_c_ptr != C) {
-                const int eb = elem_bytes_out(d.out_dtype);
-                blz_status s = encode_map(&p->tm_c, C, static_cast<uint64_t>(d.N) * eb, static_cast<uint64_t>(d.M), static_cast<uint64_t>(cp.epi.ldc) * eb, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
-                if (s) return s;
-                p->tm_c_ptr = C;
-            }
-        } else if (p->tm_c_ptr == nullptr) {
-            p->tm_c = p->tm_a;                  // a valid descriptor the kernel never stores through
-        }
-        cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[1];
-        launch_config_cluster(p, cfg, attr, stream);
-        void* cargs[4] = {&p->tm_a, &p->tm_b, &p->tm_c, &cp};
-        BLZ_CUDA(cudaLaunchKernelExC(&cfg, p->cc.fn, cargs));
-        return BLZ_OK;
-    }
+    void* one[1] = {C};
+    return launch_cluster(p, 1, one, d.ldc ? d.ldc : d.N, 0, stream);
+}
+
+blz_status blz_gemm_execute_gather(blz_gemm_plan* p, int32_t n_dst, void* const* dst, int64_t ld_total, int64_t col_offset, void* stream_v) {
+    if (!p || !dst || n_dst < 1 || n_dst > BLZ_MAX_DST) return BLZ_ERR_INVALID_ARGUMENT;
+    if (p->variant == BLZ_VARIANT_DECODE) return BLZ_ERR_UNSUPPORTED;
+    const blz_gemm_desc& d = p->desc;
+    if (ld_total < col_offset + d.N || col_offset < 0) return BLZ_ERR_INVALID_ARGUMENT;
+    if (d.epilogue == BLZ_EPI_RESIDUAL_ADD) return BLZ_ERR_UNSUPPORTED;
+    for (int i = 0; i < n_dst; ++i) if (!dst[i]) return BLZ_ERR_INVALID_ARGUMENT;
+    return launch_cluster(p, n_dst, dst, ld_total, col_offset, static_cast<cudaStream_t>(stream_v));
 }
 
 blz_status blz_gemm_plan_set_a(blz_gemm_plan* p, const void* A, const void* A_sf, float a_scale) {
@@ -614,6 +649,38 @@ blz_status blz_debug_read_timing(unsigned long long* out, int n_words) {
     return BLZ_OK;
 }
 #endif
+
+// ------------------------------------------------------------ peer-visible buffers
+
+blz_status blz_peer_buffer_create(int64_t bytes, void** ptr, uint8_t* handle64) {
+    if (!ptr || !handle64 || bytes <= 0) return BLZ_ERR_INVALID_ARGUMENT;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    if (!cuda_ok(cudaMalloc(ptr, static_cast<size_t>(bytes)), "cudaMalloc")) return BLZ_ERR_OUT_OF_MEMORY;
+    cudaIpcMemHandle_t h;
+    if (!cuda_ok(cudaIpcGetMemHandle(&h, *ptr), "cudaIpcGetMemHandle")) { cudaFree(*ptr); *ptr = nullptr; return BLZ_ERR_CUDA; }
+    memcpy(handle64, &h, 64);
+    return BLZ_OK;
+}
+
+blz_status blz_peer_buffer_open(const uint8_t* handle64, void** ptr) {
+    if (!ptr || !handle64) return BLZ_ERR_INVALID_ARGUMENT;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    BLZ_CUDA(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return BLZ_OK;
+}
+
+blz_status blz_peer_buffer_close(void* ptr) {
+    if (!ptr) return BLZ_OK;
+    BLZ_CUDA(cudaIpcCloseMemHandle(ptr));
+    return BLZ_OK;
+}
+
+blz_status blz_peer_buffer_destroy(void* ptr) {
+    if (!ptr) return BLZ_OK;
+    BLZ_CUDA(cudaFree(ptr));
+    return BLZ_OK;
+}
 
 // ------------------------------------------------------------ preparation
 

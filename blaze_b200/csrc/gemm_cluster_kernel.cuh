@@ -43,7 +43,8 @@ struct ClusterGemmParams {
     const uint8_t* sfa;      // tiled scale factors of A: [row blocks of 128][sf_katoms][512]
     const uint8_t* sfb;      // tiled scale factors of B
     int sf_katoms;
-    int use_tma_store;       // C (and its pitch) 16-byte aligned: epilogue stores through tm_c
+    int use_tma_store;       // C (and its pitch) 16-byte aligned: epilogue stores through the output maps
+    int n_dst;               // output maps in use: 1, or one per GPU for the fused all-gather
     EpilogueParams epi;
     int* status;
 };
@@ -61,6 +62,16 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
     m_tile = first_m + in_band % rows;
     n_tile = in_band / rows;
 }
+
+// Where the epilogue stores a tile.  Normally one map (C).  For the fused GEMM + all-gather every
+// GPU of the box passes one map per GPU: map d describes this rank's column block inside GPU d's
+// full [M, N_total] output (its own buffer or a peer's, mapped through CUDA IPC), and each staged
+// chunk is written once per destination with plain TMA stores -- the NVLink traffic overlaps the
+// main loop tile by tile instead of following the GEMM as a separate collective.
+constexpr int BLZ_MAX_DST = 8;
+struct alignas(64) OutputMaps {
+    CUtensorMap m[BLZ_MAX_DST];
+};
 
 template <int KIND, int CG, int BN, int STAGES, int ACC_BUFS>
 struct ClusterGemmConfig {
@@ -97,7 +108,7 @@ struct ClusterGemmConfig {
 template <int KIND, int CG, int BN, int STAGES, int ACC_BUFS>
 __global__ void __launch_bounds__(ClusterGemmConfig<KIND, CG, BN, STAGES, ACC_BUFS>::THREADS, 1)
 gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                    const __grid_constant__ CUtensorMap tm_c, const ClusterGemmParams p) {
+                    const __grid_constant__ OutputMaps out, const ClusterGemmParams p) {
     using Cfg = ClusterGemmConfig<KIND, CG, BN, STAGES, ACC_BUFS>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -137,7 +148,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     if (warp == 0 && lane == 0) {
         prefetch_tensormap(&tm_a);
         prefetch_tensormap(&tm_b);
-        prefetch_tensormap(&tm_c);
+        prefetch_tensormap(&out.m[0]);
     }
     tc_fence_before_sync();
     if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();   // barriers of every CTA are initialised
@@ -329,7 +340,9 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     fence_proxy_async_smem();
                     named_barrier_sync(bar_id, 128);
                     if (epi_tid == 0) {
-                        if (ok) tma_store_2d(&tm_c, sbuf, (n_tile * BN + c0) * out_esize, row0);
+                        if (ok) {
+                            for (int d = 0; d < p.n_dst; ++d) tma_store_2d(&out.m[d], sbuf, (n_tile * BN + c0) * out_esize, row0);
+                        }
                         tma_store_commit();
                     }
                     obuf ^= 1;

@@ -60,6 +60,13 @@ class GemmPlan:
     def execute(self, C, stream=None) -> None:
         nv.check("blz_gemm_execute", nv.lib().blz_gemm_execute(self._handle, _ptr(C), _stream(stream)))
 
+    def execute_gather(self, dst_ptrs, ld_total: int, col_offset: int, stream=None) -> None:
+        """Fused GEMM + all-gather: writes this plan's [M, N] block at columns [col_offset, ...) of every
+        full-width output in `dst_ptrs` (device pointers, own buffer and peers')."""
+        n = len(dst_ptrs)
+        arr = (ctypes.c_void_p * n)(*[int(x) for x in dst_ptrs])
+        nv.check("blz_gemm_execute_gather", nv.lib().blz_gemm_execute_gather(self._handle, n, arr, int(ld_total), int(col_offset), _stream(stream)))
+
     def set_a(self, A, A_sf=None, a_scale: float = 0.0) -> None:
         nv.check("blz_gemm_plan_set_a", nv.lib().blz_gemm_plan_set_a(self._handle, _ptr(A), _ptr(A_sf), float(a_scale)))
         self._keep = (A, A_sf) + self._keep[1:]

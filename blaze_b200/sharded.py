@@ -41,3 +41,56 @@ def gathered_to_full(gathered):
     """[world, M, N/world] -> [M, N] (column blocks in rank order)."""
     world, m, n_local = gathered.shape
     return gathered.permute(1, 0, 2).reshape(m, world * n_local)
+
+
+class PeerOutput:
+    """A full-width [M, N_total] output on every rank, each visible to every other rank of the box
+    (CUDA IPC), for the fused GEMM + all-gather (`GemmPlan.execute_gather`).
+
+    `ptrs[i]` is the address of rank i's buffer as seen from this process; `local` is this rank's
+    buffer as a torch tensor.  Call `close()` on every rank before the process group goes away."""
+
+    def __init__(self, M: int, n_total: int, dtype, group=None):
+        import ctypes
+        import torch
+        import torch.distributed as dist
+        from . import _native as nv
+        self._nv, self._torch = nv, torch
+        self.M, self.n_total, self.dtype = int(M), int(n_total), dtype
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        esize = torch.empty((), dtype=dtype).element_size()
+        self.bytes = self.M * self.n_total * esize
+        L = nv.lib()
+        own = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        nv.check("blz_peer_buffer_create", L.blz_peer_buffer_create(self.bytes, ctypes.byref(own), handle))
+        self._own = own.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self.ptrs, self._opened = [], []
+        for r in range(self.world):
+            if r == self.rank:
+                self.ptrs.append(self._own)
+                continue
+            p = ctypes.c_void_p()
+            nv.check("blz_peer_buffer_open", L.blz_peer_buffer_open(handles[r], ctypes.byref(p)))
+            self.ptrs.append(p.value)
+            self._opened.append(p.value)
+        typestr = {torch.bfloat16: "<u2", torch.float16: "<f2", torch.float32: "<f4"}[dtype]
+
+        class _Cai:
+            __cuda_array_interface__ = {"shape": (self.M, self.n_total), "typestr": typestr, "data": (self._own, False), "version": 3}
+        t = torch.as_tensor(_Cai(), device=torch.device("cuda", torch.cuda.current_device()))
+        self.local = t.view(torch.bfloat16) if dtype == torch.bfloat16 else t
+        dist.barrier(group=group)
+
+    def close(self) -> None:
+        L = self._nv.lib()
+        self._torch.cuda.synchronize()
+        self.local = None
+        for p in self._opened:
+            L.blz_peer_buffer_close(p)
+        self._opened = []
+        if self._own:
+            L.blz_peer_buffer_destroy(self._own)
+            self._own = None

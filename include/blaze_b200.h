@@ -181,6 +181,28 @@ int64_t blz_tiled_scales_bytes(int64_t rows, int64_t K);
 blz_status blz_tile_scales(const uint8_t* sf, int64_t rows, int64_t K, int64_t row_stride, int64_t blk_stride,
                            uint8_t* tiled, void* stream);
 
+/* ---- several GPUs: fused GEMM + all-gather (no counterpart in the reference, which has no
+ *      multi-GPU code; BASELINE's sharded configuration gathers with NCCL after the GEMM) ----
+ *
+ * Peer-visible buffers: blz_peer_buffer_create allocates device memory and returns a 64-byte
+ * CUDA IPC handle; another process of the same box opens it with blz_peer_buffer_open (peer
+ * access is enabled lazily) and gets a pointer it may pass as a destination below.
+ *
+ * blz_gemm_execute_gather runs the planned GEMM (M x N_local x K, tiled variants only) and
+ * stores its [M, N_local] block at columns [col_offset, col_offset + N_local) of EVERY
+ * destination: dst[i] is the base of the full [M, ld_total] output on GPU i (the caller's own
+ * buffer included).  The epilogue writes each staged chunk once per destination with TMA stores,
+ * so NVLink traffic overlaps the main loop; when every rank has run it and the ranks have met at
+ * a barrier, every GPU holds the whole [M, N_total] matrix in row-major order.  ld_total and
+ * col_offset in elements; all bases 16-byte aligned, col_offset a multiple of 8; n_dst <= 8;
+ * residual-add epilogues are not supported here. */
+blz_status blz_peer_buffer_create(int64_t bytes, void** ptr, uint8_t* handle64);
+blz_status blz_peer_buffer_open(const uint8_t* handle64, void** ptr);
+blz_status blz_peer_buffer_close(void* ptr);
+blz_status blz_peer_buffer_destroy(void* ptr);
+blz_status blz_gemm_execute_gather(blz_gemm_plan* plan, int32_t n_dst, void* const* dst, int64_t ld_total,
+                                   int64_t col_offset, void* stream);
+
 /* ---- allocation-free entry point (no counterpart in the reference: Blaze's launchers and plans
  *      all call cudaMalloc, e.g. src/kernels/gemm_fp4_blkscaled_sm100.cu:840-920) ----
  *
