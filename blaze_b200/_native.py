@@ -35,6 +35,7 @@ EXPORTS = (
     "blz_amax", "blz_quantize_fp8", "blz_quantize_nvfp4", "blz_tiled_scales_bytes", "blz_tile_scales",
     "blz_gemm_nvfp4_decode_static",
     "blz_peer_buffer_create", "blz_peer_buffer_open", "blz_peer_buffer_close", "blz_peer_buffer_destroy", "blz_gemm_execute_gather",
+    "blz_wait_probe",
 )
 
 
@@ -104,6 +105,8 @@ def lib() -> ctypes.CDLL:
     L.blz_peer_buffer_close.argtypes = [vp]
     L.blz_peer_buffer_destroy.argtypes = [vp]
     L.blz_gemm_execute_gather.argtypes = [vp, i32, ctypes.POINTER(vp), i64, i64, vp]
+    L.blz_wait_probe.argtypes = [ctypes.c_uint64, vp, vp, vp]
+    L.blz_wait_probe.restype = ctypes.c_int
     for name in ("blz_peer_buffer_create", "blz_peer_buffer_open", "blz_peer_buffer_close", "blz_peer_buffer_destroy", "blz_gemm_execute_gather"):
         getattr(L, name).restype = ctypes.c_int
     for name in ("blz_gemm_plan_create", "blz_gemm_execute", "blz_gemm_plan_set_a", "blz_gemm_plan_check", "blz_gemm_plan_info",

@@ -650,6 +650,39 @@ blz_status blz_debug_read_timing(unsigned long long* out, int n_words) {
 }
 #endif
 
+// ------------------------------------------------------------ bounded-wait self test
+
+}  // extern "C"
+
+namespace {
+// One CTA waits on a barrier nobody will ever arrive on, with the same bounded wait every kernel of
+// this library uses, gives up after `limit_ns`, records the error word and returns normally.
+__global__ void wait_probe_kernel(unsigned long long limit_ns, int* status, unsigned long long* waited_ns) {
+    __shared__ __align__(8) unsigned long long bar_storage;
+    __shared__ int abort_flag;
+    const uint32_t bar = smem_u32(&bar_storage);
+    if (threadIdx.x == 0) { mbar_init(bar, 1); abort_flag = 0; fence_mbar_init(); }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint64_t t0 = global_timer_ns();
+        const bool ok = mbar_wait_limit(bar, 0u, &abort_flag, limit_ns);
+        if (waited_ns) *waited_ns = global_timer_ns() - t0;
+        if (!ok) atomicCAS(status, 0, BLZ_DEV_TIMEOUT_PRODUCER);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_inval(bar);
+}
+}  // namespace
+
+extern "C" {
+
+blz_status blz_wait_probe(uint64_t limit_ns, int32_t* d_status, uint64_t* d_waited_ns, void* stream_v) {
+    if (!d_status || limit_ns == 0 || limit_ns > 100000000ull) return BLZ_ERR_INVALID_ARGUMENT;   // at most 100 ms
+    wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_v)>>>(limit_ns, d_status, reinterpret_cast<unsigned long long*>(d_waited_ns));
+    BLZ_CUDA(cudaGetLastError());
+    return BLZ_OK;
+}
+
 // ------------------------------------------------------------ peer-visible buffers
 
 blz_status blz_peer_buffer_create(int64_t bytes, void** ptr, uint8_t* handle64) {

@@ -84,9 +84,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 #endif
     return ok != 0;
 }
-// Bounded wait: true when the phase completed; false when the limit ran out or another role of
+// Bounded wait: true when the phase completed; false when `limit_ns` ran out or another role of
 // this CTA already gave up (`abort_flag`, a word in shared memory, non-zero).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, const volatile int* abort_flag, uint64_t limit_ns) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
         if (mbar_try_wait(bar, parity)) return true;
@@ -97,8 +97,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const v
         for (int i = 0; i < 128; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag != 0) return false;
-        if (global_timer_ns() - t0 > BLZ_WAIT_LIMIT_NS) return false;
+        if (global_timer_ns() - t0 > limit_ns) return false;
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
+    return mbar_wait_limit(bar, parity, abort_flag, BLZ_WAIT_LIMIT_NS);
 }
 
 // ---------------------------------------------------------------------- TMA

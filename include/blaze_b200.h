@@ -181,6 +181,14 @@ int64_t blz_tiled_scales_bytes(int64_t rows, int64_t K);
 blz_status blz_tile_scales(const uint8_t* sf, int64_t rows, int64_t K, int64_t row_stride, int64_t blk_stride,
                            uint8_t* tiled, void* stream);
 
+/* ---- bounded-wait self test (no counterpart in the reference, whose waits spin forever:
+ *      include/gemm/tma_utils.cuh:217-230) ----
+ * Launches one CTA that waits, with the bounded wait every kernel here uses, on a barrier nothing
+ * will ever complete; after limit_ns (<= 100 ms) it gives up, sets *d_status non-zero, writes the
+ * time it waited to *d_waited_ns (optional) and returns normally.  Shows, without faulting or
+ * hanging anything, that a lost arrival becomes an error word instead of a hung GPU. */
+blz_status blz_wait_probe(uint64_t limit_ns, int32_t* d_status, uint64_t* d_waited_ns, void* stream);
+
 /* ---- several GPUs: fused GEMM + all-gather (no counterpart in the reference, which has no
  *      multi-GPU code; BASELINE's sharded configuration gathers with NCCL after the GEMM) ----
  *

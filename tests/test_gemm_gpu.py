@@ -521,6 +521,25 @@ def test_quantizers_bit_exact(oracle, cuda_device):
         assert np.array_equal(sft.cpu().numpy(), oracle.tile_sf(sf_ref, rb, ka))
 
 
+# ------------------------------------------------------------------ failure detection
+
+def test_lost_arrival_becomes_an_error_word(cuda_device):
+    """A wait nobody completes runs out after its limit (2 ms here) and the kernel reports it through
+    its status word; the context stays usable.  Nothing faults, traps or hangs."""
+    torch = _torch()
+    from blaze_b200 import _native as nv
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    waited = torch.zeros(1, dtype=torch.int64, device=cuda_device)
+    L = nv.lib()
+    assert L.blz_wait_probe(2_000_000, status.data_ptr(), waited.data_ptr(), torch.cuda.current_stream().cuda_stream) == nv.OK
+    torch.cuda.synchronize()
+    assert int(status.item()) != 0
+    assert 2_000_000 <= int(waited.item()) < 50_000_000
+    assert L.blz_wait_probe(0, status.data_ptr(), None, None) == nv.ERR_INVALID_ARGUMENT
+    # the device still works
+    assert float((torch.ones(8, device=cuda_device) * 2).sum().item()) == 16.0
+
+
 # ------------------------------------------------------------- Blaze's own test program
 
 def test_blaze_test_program_builds_and_passes(cuda_device):
