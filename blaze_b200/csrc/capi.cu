@@ -99,17 +99,24 @@ int grid_for(int64_t work_items, int threads) {
 
 struct ClusterChoice {
     const void* fn;
-    int cg, bn, stages, acc_bufs, smem, tmem_cols, threads;
+    int cg, bn, stages, acc_bufs, smem, tmem_cols, threads, share;
 };
 
-template <int KIND, int CG, int BN, int STAGES, int ACC>
+template <int KIND, int CG, int BN, int STAGES, int ACC, int SHARE = 1>
 ClusterChoice cluster_choice() {
-    using Cfg = ClusterGemmConfig<KIND, CG, BN, STAGES, ACC>;
-    return ClusterChoice{reinterpret_cast<const void*>(&gemm_cluster_kernel<KIND, CG, BN, STAGES, ACC>), CG, BN, STAGES, ACC,
-                         static_cast<int>(Cfg::SMEM_BYTES), static_cast<int>(Cfg::TMEM_COLS), Cfg::THREADS};
+    using Cfg = ClusterGemmConfig<KIND, CG, BN, STAGES, ACC, SHARE>;
+    return ClusterChoice{reinterpret_cast<const void*>(&gemm_cluster_kernel<KIND, CG, BN, STAGES, ACC, SHARE>), CG, BN, STAGES, ACC,
+                         static_cast<int>(Cfg::SMEM_BYTES), static_cast<int>(Cfg::TMEM_COLS), Cfg::THREADS, SHARE};
 }
 
-ClusterChoice pick_cluster_kernel(int mma_kind, int cg) {
+ClusterChoice pick_cluster_kernel(int mma_kind, int cg, int share) {
+    if (cg == 2 && share == 2) {
+        switch (mma_kind) {
+            case MMA_F16: return cluster_choice<MMA_F16, 2, 256, 6, 2, 2>();
+            case MMA_F8: return cluster_choice<MMA_F8, 2, 256, 6, 2, 2>();
+            default: return cluster_choice<MMA_NVF4, 2, 256, 5, 1, 2>();
+        }
+    }
     if (cg == 2) {
         switch (mma_kind) {
             case MMA_F16: return cluster_choice<MMA_F16, 2, 256, 6, 2>();
@@ -259,7 +266,7 @@ blz_status launch_config_cluster(const blz_gemm_plan* p, cudaLaunchConfig_t& cfg
     cfg.dynamicSmemBytes = static_cast<size_t>(p->cc.smem);
     cfg.stream = stream;
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = static_cast<unsigned>(p->cc.cg);
+    attr[0].val.clusterDim.x = static_cast<unsigned>(p->cc.cg * p->cc.share);
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
@@ -267,20 +274,20 @@ blz_status launch_config_cluster(const blz_gemm_plan* p, cudaLaunchConfig_t& cfg
     return BLZ_OK;
 }
 
-blz_status setup_cluster(blz_gemm_plan* p, int cg) {
+blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1) {
     const blz_gemm_desc& d = p->desc;
     const int64_t rb = row_bytes(p->mma_kind, d.K);
-    p->cc = pick_cluster_kernel(p->mma_kind, cg);
-    p->variant = cg == 2 ? BLZ_VARIANT_PAIR_256x256 : BLZ_VARIANT_TILE_128x128;
+    p->cc = pick_cluster_kernel(p->mma_kind, cg, share);
+    p->variant = share == 2 ? BLZ_VARIANT_QUAD_512x256 : cg == 2 ? BLZ_VARIANT_PAIR_256x256 : BLZ_VARIANT_TILE_128x128;
     BLZ_CUDA(cudaFuncSetAttribute(p->cc.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, p->cc.smem));
     const int bn = p->cc.bn, tile_m = 128 * cg;
     blz_status s = encode_map(&p->tm_a, p->a_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.M), static_cast<uint64_t>(rb), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (s) return s;
-    s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rb), 128, static_cast<uint32_t>(bn / cg), CU_TENSOR_MAP_SWIZZLE_128B);
+    s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rb), 128, static_cast<uint32_t>(bn / cg / share), CU_TENSOR_MAP_SWIZZLE_128B);
     if (s) return s;
     ClusterGemmParams& cp = p->cp;
     cp.M = d.M; cp.N = d.N;
-    cp.m_tiles = static_cast<int>(ceil_div(d.M, tile_m));
+    cp.m_tiles = static_cast<int>(ceil_div(d.M, tile_m * share));
     cp.n_tiles = static_cast<int>(ceil_div(d.N, bn));
     // Rasterisation: when all of A stays in L2 anyway (it is re-read by every column of tiles),
     // walk M fastest so that concurrent tiles share as few B panels as possible; otherwise cut M
@@ -295,10 +302,11 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg) {
     cp.sf_katoms = static_cast<int>(sf_katoms(d.K));
     cp.status = p->status;
     const int64_t tiles = static_cast<int64_t>(cp.m_tiles) * cp.n_tiles;
-    int max_groups = p->num_sms / cg;
-    if (cg == 2) {
+    const int csize = cg * share;
+    int max_groups = p->num_sms / csize;
+    if (csize > 1) {
         // how many pairs the device can hold at once (GPC shapes can leave SMs unpaired)
-        p->grid = max_groups * cg;
+        p->grid = max_groups * csize;
         cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[1];
         launch_config_cluster(p, cfg, attr, nullptr);
         int n = 0;
@@ -306,7 +314,7 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg) {
         else (void)cudaGetLastError();
     }
     const int64_t groups = tiles < max_groups ? tiles : max_groups;
-    p->grid = static_cast<int>(groups) * cg;
+    p->grid = static_cast<int>(groups) * csize;
     return BLZ_OK;
 }
 
@@ -541,7 +549,8 @@ blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_p
             const int64_t tiles256 = ceil_div(desc->M, 256) * ceil_div(desc->N, 256);
             v = (desc->M > 128 && tiles256 >= p->num_sms / 2) ? BLZ_VARIANT_PAIR_256x256 : BLZ_VARIANT_TILE_128x128;
         }
-        if (v == BLZ_VARIANT_PAIR_256x256) s = setup_cluster(p, 2);
+        if (v == BLZ_VARIANT_QUAD_512x256) s = setup_cluster(p, 2, 2);
+        else if (v == BLZ_VARIANT_PAIR_256x256) s = setup_cluster(p, 2);
         else if (v == BLZ_VARIANT_TILE_128x128) s = setup_cluster(p, 1);
         else s = BLZ_ERR_INVALID_ARGUMENT;
         p->b_used = keep;
@@ -613,7 +622,7 @@ blz_status blz_gemm_plan_info(const blz_gemm_plan* p, blz_plan_info* info) {
         info->stages = p->decode_stages; info->split_k = p->decode_split;
         info->grid = p->grid; info->smem_bytes = p->decode_smem; info->tmem_cols = p->decode_tmem;
     } else {
-        info->tile_m = 128 * p->cc.cg; info->tile_n = p->cc.bn;
+        info->tile_m = 128 * p->cc.cg * p->cc.share; info->tile_n = p->cc.bn;
         info->stages = p->cc.stages; info->split_k = 1;
         info->grid = p->grid; info->smem_bytes = p->cc.smem; info->tmem_cols = p->cc.tmem_cols;
     }

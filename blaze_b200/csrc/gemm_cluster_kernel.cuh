@@ -73,8 +73,13 @@ struct alignas(64) OutputMaps {
     CUtensorMap m[BLZ_MAX_DST];
 };
 
-template <int KIND, int CG, int BN, int STAGES, int ACC_BUFS>
+template <int KIND, int CG, int BN, int STAGES, int ACC_BUFS, int SHARE = 1>
 struct ClusterGemmConfig {
+    // SHARE = 2: two CTA pairs (a cluster of four, tile 512 x BN) need the same B tile; each CTA
+    // fetches only half of its share from L2 and forwards it to the matching CTA of the other
+    // pair through distributed shared memory (and receives the other half the same way), which
+    // cuts the B bytes every SM pulls from L2 in two.
+    static constexpr int CLUSTER = CG * SHARE;
     static constexpr bool HAS_SF = (KIND == MMA_NVF4);
     // With a single accumulator buffer the epilogue is on the critical path: two sets of four
     // epilogue warps (warps 4-7 and 12-15) then drain alternate column chunks.
@@ -83,6 +88,8 @@ struct ClusterGemmConfig {
     static constexpr uint32_t A_BYTES = 128 * 128;
     static constexpr uint32_t B_ROWS = BN / CG;                        // rows of the B tile staged by one CTA
     static constexpr uint32_t B_BYTES = B_ROWS * 128;
+    static constexpr uint32_t B_LOAD_ROWS = B_ROWS / SHARE;            // rows this CTA itself fetches from L2
+    static constexpr uint32_t B_LOAD_BYTES = B_LOAD_ROWS * 128;
     static constexpr uint32_t SF_BLOCK_BYTES = 4 * 512;                // one 128-row block, four K atoms
     static constexpr uint32_t SFB_BLOCKS = BN / 128;                   // every CTA needs the scales of all BN columns
     static constexpr uint32_t SFA_BYTES = HAS_SF ? SF_BLOCK_BYTES : 0;
@@ -95,21 +102,22 @@ struct ClusterGemmConfig {
     static constexpr uint32_t SF_BASE = ACC_COLS;
     static constexpr uint32_t TMEM_NEED = ACC_COLS + STAGES * SF_COLS;
     static constexpr uint32_t TMEM_COLS = tmem_cols_pow2(TMEM_NEED);
-    static constexpr uint32_t NUM_BARS = 3 * STAGES + 2 * ACC_BUFS;
+    static constexpr uint32_t NUM_BARS = (SHARE == 2 ? 5 : 3) * STAGES + 2 * ACC_BUFS;
     static constexpr uint32_t BAR_BYTES = 8 * NUM_BARS + 16;
     static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BYTES + BAR_BYTES + 1024;
     static constexpr uint32_t READY_COUNT = HAS_SF ? 4 * CG : CG;      // arrivals that make a stage ready for the MMA
     static_assert(CG == 1 || CG == 2, "CTA group of 1 or 2");
+    static_assert(SHARE == 1 || (SHARE == 2 && CG == 2), "B sharing needs CTA pairs");
     static_assert(TMEM_NEED <= 512, "accumulators and scale factors exceed tensor memory");
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared-memory limit");
     static_assert(B_ROWS % 8 == 0 && BN % 128 == 0 && BN <= 256, "tile width");
 };
 
-template <int KIND, int CG, int BN, int STAGES, int ACC_BUFS>
-__global__ void __launch_bounds__(ClusterGemmConfig<KIND, CG, BN, STAGES, ACC_BUFS>::THREADS, 1)
+template <int KIND, int CG, int BN, int STAGES, int ACC_BUFS, int SHARE = 1>
+__global__ void __launch_bounds__(ClusterGemmConfig<KIND, CG, BN, STAGES, ACC_BUFS, SHARE>::THREADS, 1)
 gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const __grid_constant__ OutputMaps out, const ClusterGemmParams p) {
-    using Cfg = ClusterGemmConfig<KIND, CG, BN, STAGES, ACC_BUFS>;
+    using Cfg = ClusterGemmConfig<KIND, CG, BN, STAGES, ACC_BUFS, SHARE>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;      // the same offset in every CTA of the cluster
@@ -122,25 +130,34 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     auto empty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
     auto acc_full_bar = [&](int b) { return bar_base + 8u * (3 * STAGES + b); };
     auto acc_empty_bar = [&](int b) { return bar_base + 8u * (3 * STAGES + ACC_BUFS + b); };
+    // B sharing only: "my own part of B landed" and "the other pair's CTA can take my part"
+    auto bpart_bar = [&](int s) { return bar_base + 8u * (3 * STAGES + 2 * ACC_BUFS + s); };
+    auto partner_ready_bar = [&](int s) { return bar_base + 8u * (4 * STAGES + 2 * ACC_BUFS + s); };
     const uint32_t slot_off = STAGES * Cfg::STAGE_BYTES + Cfg::OUT_BYTES + 8u * Cfg::NUM_BARS;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + slot_off);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + slot_off + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = (CG == 1) ? 0u : cluster_cta_rank();
-    const bool leader = (rank == 0);
+    const uint32_t rank = (Cfg::CLUSTER == 1) ? 0u : cluster_cta_rank();
+    const uint32_t pair = rank / CG;                 // which CTA group of the cluster (0 unless B is shared)
+    const uint32_t prank = rank % CG;                // position inside the CTA group
+    const bool leader = (prank == 0);
+    const uint32_t leader_rank = rank - prank;       // cluster rank of this group's leader
+    const uint32_t partner = rank ^ CG;              // B sharing: the CTA of the other pair that needs the same B rows
+    const uint16_t commit_mask = static_cast<uint16_t>(0x3u << (pair * 2));
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(ready_bar(s), Cfg::READY_COUNT);
             mbar_init(empty_bar(s), 1);
+            if constexpr (SHARE == 2) { mbar_init(bpart_bar(s), 1); mbar_init(partner_ready_bar(s), 1); }
         }
         for (int b = 0; b < ACC_BUFS; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 4 * CG * Cfg::EPI_SETS); }
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if constexpr (CG == 2) cluster_sync_all();         // both CTAs are resident before the pair allocates
+    if constexpr (Cfg::CLUSTER > 1) cluster_sync_all();   // every CTA of the cluster is resident before a pair allocates
     if (warp == 2) {
         if constexpr (CG == 2) { tmem_alloc_pair(base + slot_off, Cfg::TMEM_COLS); tmem_relinquish_pair(); }
         else { tmem_alloc(base + slot_off, Cfg::TMEM_COLS); tmem_relinquish(); }
@@ -151,12 +168,12 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         prefetch_tensormap(&out.m[0]);
     }
     tc_fence_before_sync();
-    if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();   // barriers of every CTA are initialised
+    if constexpr (Cfg::CLUSTER > 1) cluster_sync_all(); else __syncthreads();   // barriers of every CTA are initialised
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
     const int total_tiles = p.m_tiles * p.n_tiles;
-    const int group = blockIdx.x / CG, num_groups = gridDim.x / CG;
+    const int group = blockIdx.x / Cfg::CLUSTER, num_groups = gridDim.x / Cfg::CLUSTER;   // a cluster walks tiles of (128*CG*SHARE) x BN
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (every CTA)
@@ -168,8 +185,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
                 int m_tile, n_tile;
                 tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_tile, n_tile);
-                const int a_row = (m_tile * CG + static_cast<int>(rank)) * 128;
-                const int b_row = n_tile * BN + static_cast<int>(rank) * static_cast<int>(Cfg::B_ROWS);
+                const int a_row = ((m_tile * SHARE + static_cast<int>(pair)) * CG + static_cast<int>(prank)) * 128;
+                const int b_row = n_tile * BN + static_cast<int>(prank) * static_cast<int>(Cfg::B_ROWS) + static_cast<int>(pair) * static_cast<int>(Cfg::B_LOAD_ROWS);
                 for (int ks = 0; ks < p.k_stages; ++ks) {
                     [[maybe_unused]] const long long te = BLZ_T_NOW();
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
@@ -178,13 +195,21 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     BLZ_T_ADD(t_wait_empty, te);
                     const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
-                    mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+                    if constexpr (SHARE == 2) {
+                        // everything but my own part of B completes on full_bar: A, scale factors and
+                        // the part the partner forwards; my own part has its own barrier so that the
+                        // forwarder can pass it on the moment it lands
+                        mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES - Cfg::B_LOAD_BYTES);
+                        mbar_arrive_cluster(partner_ready_bar(stage), partner);    // my stage is free and armed: send
+                    } else {
+                        mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+                    }
                     if constexpr (Cfg::HAS_SF) {
                         // the small scale-factor copies go first: the helper warps need them before the MMA needs the tiles
                         const uint32_t ssfa = sb + Cfg::B_BYTES;
                         const uint32_t ssfb = ssfa + Cfg::SFA_BYTES;
                         const size_t katom = static_cast<size_t>(ks) * 4;
-                        const size_t a_blk = static_cast<size_t>(m_tile) * CG + rank;
+                        const size_t a_blk = (static_cast<size_t>(m_tile) * SHARE + pair) * CG + prank;
                         bulk_load_1d(ssfa, p.sfa + (a_blk * p.sf_katoms + katom) * 512, Cfg::SF_BLOCK_BYTES, full_bar(stage));
 #pragma unroll
                         for (int blk = 0; blk < static_cast<int>(Cfg::SFB_BLOCKS); ++blk) {
@@ -193,7 +218,17 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         }
                     }
                     tma_load_2d(sa, &tm_a, ks * 128, a_row, full_bar(stage));
-                    tma_load_2d(sb, &tm_b, ks * 128, b_row, full_bar(stage));
+                    if constexpr (SHARE == 2) {
+                        // The partner's "ready" for this round also says that it has consumed what I
+                        // forwarded last round, so my part of the stage may be overwritten now.
+                        if (!mbar_wait(partner_ready_bar(stage), phase, abort_flag)) {
+                            atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_PRODUCER); *abort_flag = 1; ok = false; break;
+                        }
+                        mbar_arrive_expect_tx(bpart_bar(stage), Cfg::B_LOAD_BYTES);
+                        tma_load_2d(sb + pair * Cfg::B_LOAD_BYTES, &tm_b, ks * 128, b_row, bpart_bar(stage));
+                    } else {
+                        tma_load_2d(sb, &tm_b, ks * 128, b_row, full_bar(stage));
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -243,11 +278,11 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                             else umma_nvf4_pair(d_tmem, ad, bd, p.idesc, sf_cols + 4 * k, sf_cols + 16 + k * (BN / 32), accumulate);
                         }
                     }
-                    if constexpr (CG == 1) tc_commit(empty_bar(stage)); else tc_commit_pair(empty_bar(stage), 0x3);
+                    if constexpr (CG == 1) tc_commit(empty_bar(stage)); else tc_commit_pair(empty_bar(stage), commit_mask);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (ok) {
-                    if constexpr (CG == 1) tc_commit(acc_full_bar(buf)); else tc_commit_pair(acc_full_bar(buf), 0x3);
+                    if constexpr (CG == 1) tc_commit(acc_full_bar(buf)); else tc_commit_pair(acc_full_bar(buf), commit_mask);
                 }
             }
             BLZ_T_STORE(2, t_wait_ready); BLZ_T_STORE(3, t_wait_acc); BLZ_T_STORE(4, BLZ_T_NOW() - t_begin); BLZ_T_STORE(8, it);
@@ -261,10 +296,33 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 bool ok = true;
                 for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
                     for (int ks = 0; ks < p.k_stages; ++ks) {
-                        if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+                        bool landed = mbar_wait(full_bar(stage), phase, abort_flag);
+                        if constexpr (SHARE == 2) landed = landed && mbar_wait(bpart_bar(stage), phase, abort_flag);
+                        if (!landed) {
                             atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
                         }
-                        if constexpr (CG == 1) mbar_arrive(ready_bar(stage)); else mbar_arrive_cluster(ready_bar(stage), 0);
+                        if constexpr (CG == 1) mbar_arrive(ready_bar(stage)); else mbar_arrive_cluster(ready_bar(stage), leader_rank);
+                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    }
+                }
+            }
+            __syncwarp();
+        }
+    } else if (warp == 3) {
+        // ------------------- B sharing: pass my part of every B stage on to the other pair's CTA
+        if constexpr (SHARE == 2) {
+            if (lane == 0) {
+                int stage = 0; uint32_t phase = 0;
+                bool ok = true;
+                for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
+                    for (int ks = 0; ks < p.k_stages; ++ks) {
+                        if (!mbar_wait(bpart_bar(stage), phase, abort_flag)) {
+                            atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_PRODUCER); *abort_flag = 1; ok = false; break;
+                        }
+                        // The partner announced that its stage is free and armed before my producer
+                        // even requested this part (it waited for partner_ready first).
+                        const uint32_t part = base + stage * Cfg::STAGE_BYTES + Cfg::A_BYTES + pair * Cfg::B_LOAD_BYTES;
+                        dsmem_copy(part, part, Cfg::B_LOAD_BYTES, full_bar(stage), partner);
                         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                     }
                 }
@@ -298,7 +356,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             // After a give-up the warps still walk the same named-barrier sequence (without touching
             // tensor memory or C) so that no epilogue warp is left waiting for another.
             tc_fence_after_sync();
-            const int row0 = (m_tile * CG + static_cast<int>(rank)) * 128;
+            const int row0 = ((m_tile * SHARE + static_cast<int>(pair)) * CG + static_cast<int>(prank)) * 128;
             const int r_local = q * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
             if (p.use_tma_store) {
@@ -359,7 +417,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             tc_fence_before_sync();
             __syncwarp();
             if (ok && lane == 0) {
-                if constexpr (CG == 1) mbar_arrive(acc_empty_bar(buf)); else mbar_arrive_cluster(acc_empty_bar(buf), 0);
+                if constexpr (CG == 1) mbar_arrive(acc_empty_bar(buf)); else mbar_arrive_cluster(acc_empty_bar(buf), leader_rank);
             }
             BLZ_T_ADD(t_work, tk);
         }
@@ -409,9 +467,14 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     }
                     tmem_st_wait();
                     tc_fence_before_sync();
+                    if constexpr (SHARE == 2) {
+                        if (!mbar_wait(bpart_bar(stage), phase, abort_flag)) {
+                            atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
+                        }
+                    }
                     __syncwarp();
                     if (lane == 0) {
-                        if constexpr (CG == 1) mbar_arrive(ready_bar(stage)); else mbar_arrive_cluster(ready_bar(stage), 0);
+                        if constexpr (CG == 1) mbar_arrive(ready_bar(stage)); else mbar_arrive_cluster(ready_bar(stage), leader_rank);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -421,12 +484,12 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
     // ---------------------------------------------------------------- teardown
     tc_fence_before_sync();
-    if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
+    if constexpr (Cfg::CLUSTER > 1) cluster_sync_all(); else __syncthreads();
     if (*abort_flag != 0) {
         const uint64_t t0 = global_timer_ns();
         while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
     }
-    if constexpr (CG == 2) cluster_sync_all(); else __syncthreads();
+    if constexpr (Cfg::CLUSTER > 1) cluster_sync_all(); else __syncthreads();
     if (warp == 2) {
         tc_fence_after_sync();
         if constexpr (CG == 2) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS); else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);

@@ -127,6 +127,17 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar) : "memory");
 }
+// Bulk copy from this CTA's shared memory into the shared memory of CTA `cta` of the cluster (same
+// offsets), completion counted in bytes on that CTA's barrier.  Not a multicast: one source, one
+// destination, over the SM-to-SM network instead of L2.
+__device__ __forceinline__ void dsmem_copy(uint32_t dst_offset, uint32_t src, uint32_t bytes, uint32_t bar_offset, uint32_t cta) {
+    asm volatile(
+        "{\n\t.reg .b32 rd, rb;\n\t"
+        "mapa.shared::cluster.u32 rd, %0, %4;\n\t"
+        "mapa.shared::cluster.u32 rb, %3, %4;\n\t"
+        "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [rd], [%1], %2, [rb];\n\t}"
+        ::"r"(dst_offset), "r"(src), "r"(bytes), "r"(bar_offset), "r"(cta) : "memory");
+}
 // 2-D tiled store shared -> global (rows/columns outside the tensor are clipped by the hardware).
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int c0, int c1) {
     asm volatile(

@@ -64,6 +64,9 @@ def _dense_inputs(oracle, kind, M, N, K, scale=1.0):
     ("f16", "f32", "256x256", (300, 520, 136)),      # CTA pair, ragged in M, N and K
     ("f16", "f16", "256x256", (2048, 2304, 1024)),   # CTA pair, several tiles per pair
     ("bf16", "bf16", "128x128", (2048, 1152, 512)),
+    ("bf16", "bf16", "512x256", (512, 256, 64)),     # two pairs sharing B, one tile, one K stage
+    ("bf16", "f32", "512x256", (700, 520, 392)),     # ragged; the second pair partly outside M
+    ("f16", "f16", "512x256", (2048, 2304, 1024)),
 ])
 def test_dense16(oracle, cuda_device, kind, out_dtype, variant, shape):
     from blaze_b200 import GemmPlan
@@ -137,6 +140,9 @@ def _fp8_inputs(oracle, M, N, K):
     ("256x256", (512, 768, 512)),
     ("256x256", (200, 328, 144)),
     ("256x256", (1024, 2048, 2048)),
+    ("512x256", (512, 256, 128)),
+    ("512x256", (1024, 2048, 2048)),
+    ("512x256", (300, 328, 144)),
 ])
 def test_fp8(oracle, cuda_device, variant, shape):
     from blaze_b200 import GemmPlan
@@ -214,6 +220,11 @@ def _nvfp4_ref(oracle, qa, qb, out_dtype="bf16", **epi):
     ("256x256", (129, 520, 96)),
     ("256x256", (2048, 2304, 1024)),   # several tiles per pair
     ("128x128", (2048, 1152, 1024)),
+    ("512x256", (512, 256, 256)),      # two pairs sharing B: one tile, one K stage
+    ("512x256", (512, 256, 2048)),     # ... the stage ring wraps
+    ("512x256", (1024, 768, 1536)),
+    ("512x256", (700, 328, 160)),      # ragged
+    ("512x256", (2048, 2304, 1024)),
     ("decode", (16, 512, 1024)),
     ("decode", (1, 128, 256)),
     ("decode", (7, 200, 160)),
