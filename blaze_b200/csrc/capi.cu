@@ -161,7 +161,7 @@ struct blz_gemm_plan {
     int out_n = 0;
     // decode-kernel launch
     DecodeStreamParams dp{};
-    int decode_smem = 0, decode_stages = 0, decode_split = 1, decode_mma_n = 0, decode_tmem = 0;
+    int decode_smem = 0, decode_stages = 0, decode_split = 1, decode_mma_n = 0, decode_tmem = 0, decode_threads = 0;
     const void* decode_fn = nullptr;
     int launches = 1;
 };
@@ -332,14 +332,37 @@ void fill_epilogue(const blz_gemm_plan* p, void* C, EpilogueParams& e) {
     e.vec_ok = vec ? 1 : 0;
 }
 
-// ---- decode variant (NVFP4, M <= 64)
+// ---- decode variant (M <= 64, every kind)
 
-struct DecodeChoice { const void* fn; int mma_n, stages, smem; };
+struct DecodeChoice { const void* fn; int mma_n, stages, smem, threads, max_split, tmem_cols; };
 
-template <int MMA_N, int STAGES>
+template <int KIND, int MMA_N, int STAGES>
 DecodeChoice decode_choice() {
-    return DecodeChoice{reinterpret_cast<const void*>(&decode_stream_kernel<MMA_N, STAGES>), MMA_N, STAGES,
-                        static_cast<int>(DecodeStreamConfig<MMA_N, STAGES>::SMEM_BYTES)};
+    using Cfg = DecodeStreamConfig<KIND, MMA_N, STAGES>;
+    return DecodeChoice{reinterpret_cast<const void*>(&decode_stream_kernel<KIND, MMA_N, STAGES>), MMA_N, STAGES, static_cast<int>(Cfg::SMEM_BYTES),
+                        Cfg::THREADS, Cfg::MAX_SPLIT, static_cast<int>(Cfg::TMEM_COLS)};
+}
+template <bool BF16, int MMA_N, int LSTAGES, int OSTAGES>
+DecodeChoice decode_choice_w4a16() {
+    using Cfg = DecodeW4A16Config<MMA_N, LSTAGES, OSTAGES>;
+    return DecodeChoice{reinterpret_cast<const void*>(&decode_w4a16_kernel<BF16, MMA_N, LSTAGES, OSTAGES>), MMA_N, LSTAGES, static_cast<int>(Cfg::SMEM_BYTES),
+                        Cfg::THREADS, Cfg::MAX_SPLIT, static_cast<int>(Cfg::TMEM_COLS)};
+}
+template <int KIND>
+DecodeChoice decode_choice_for(int M) {
+    return M <= 16 ? decode_choice<KIND, 16, 5>() : M <= 32 ? decode_choice<KIND, 32, 4>() : decode_choice<KIND, 64, 3>();
+}
+template <bool BF16>
+DecodeChoice decode_choice_w4a16_for(int M) {
+    return M <= 16 ? decode_choice_w4a16<BF16, 16, 12, 3>() : M <= 32 ? decode_choice_w4a16<BF16, 32, 10, 3>() : decode_choice_w4a16<BF16, 64, 8, 3>();
+}
+DecodeChoice pick_decode_kernel(int mma_kind, bool w4a16, bool bf16, int M) {
+    if (w4a16) return bf16 ? decode_choice_w4a16_for<true>(M) : decode_choice_w4a16_for<false>(M);
+    switch (mma_kind) {
+        case MMA_F16: return decode_choice_for<MMA_F16>(M);
+        case MMA_F8: return decode_choice_for<MMA_F8>(M);
+        default: return decode_choice_for<MMA_NVF4>(M);
+    }
 }
 
 int env_int(const char* name, int fallback) {
@@ -348,31 +371,47 @@ int env_int(const char* name, int fallback) {
     return atoi(v);
 }
 
+bool is_w4a16(const blz_gemm_desc& d) { return d.kind == BLZ_GEMM_W4A16_F16 || d.kind == BLZ_GEMM_W4A16_BF16; }
+
 blz_status decode_encode_x(blz_gemm_plan* p) {
     const blz_gemm_desc& d = p->desc;
-    const int64_t rb = d.K / 2;
+    const int64_t rb = row_bytes(p->mma_kind, d.K);      // W4A16 plans carry MMA_F16: 16-bit activations
     return encode_map(&p->tm_a, p->a_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.M), static_cast<uint64_t>(rb), 128,
                       static_cast<uint32_t>(p->decode_mma_n), CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 blz_status decode_setup(blz_gemm_plan* p) {
     const blz_gemm_desc& d = p->desc;
-    const DecodeChoice dc = d.M <= 16 ? decode_choice<16, 5>() : d.M <= 32 ? decode_choice<32, 4>() : decode_choice<64, 3>();
+    const bool w4 = is_w4a16(d);
+    const DecodeChoice dc = pick_decode_kernel(p->mma_kind, w4, d.kind == BLZ_GEMM_W4A16_BF16, d.M);
     p->decode_fn = dc.fn; p->decode_mma_n = dc.mma_n; p->decode_stages = dc.stages; p->decode_smem = dc.smem;
-    p->decode_tmem = 256;
+    p->decode_tmem = dc.tmem_cols; p->decode_threads = dc.threads;
     BLZ_CUDA(cudaFuncSetAttribute(dc.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, dc.smem));
-    const int64_t rb = d.K / 2;
-    blz_status s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rb), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    blz_status s;
+    DecodeStreamParams& dp = p->dp;
+    if (w4) {
+        // packed weights: 32 bytes (64 values) x 128 rows per stage, no swizzle -- the expansion warps read them
+        const int64_t rbw = d.K / 2;
+        s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rbw), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rbw), 32, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
+        dp.k_stages_total = static_cast<int>(ceil_div(d.K, 64));
+    } else {
+        const int64_t rb = row_bytes(p->mma_kind, d.K);
+        s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rb), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+        dp.k_stages_total = static_cast<int>(ceil_div(rb, 128));
+    }
     if (s) return s;
     if ((s = decode_encode_x(p))) return s;
 
-    DecodeStreamParams& dp = p->dp;
     dp.M = d.M; dp.N = d.N;
     dp.n_tiles = static_cast<int>(ceil_div(d.N, 128));
-    dp.k_stages_total = static_cast<int>(ceil_div(rb, 128));
-    dp.split = decode_pick_split(dp.n_tiles, dp.k_stages_total, p->num_sms, decode_max_split(dc.mma_n), env_int("BLZ_DECODE_SPLIT", 0));
+    const int max_split = decode_max_split(dc.mma_n) < dc.max_split ? decode_max_split(dc.mma_n) : dc.max_split;
+    dp.split = decode_pick_split(dp.n_tiles, dp.k_stages_total, p->num_sms, max_split, env_int("BLZ_DECODE_SPLIT", 0));
     dp.stages_per_split = static_cast<int>(ceil_div(dp.k_stages_total, dp.split));
-    dp.idesc = make_idesc_nvf4(128, static_cast<uint32_t>(dc.mma_n));
+    const uint32_t fmt16 = d.kind == BLZ_GEMM_BF16 || d.kind == BLZ_GEMM_W4A16_BF16 ? 1u : 0u;
+    // operands are swapped: the instruction's A is the weight tile, its B the activations
+    dp.idesc = p->mma_kind == MMA_NVF4 ? make_idesc_nvf4(128, static_cast<uint32_t>(dc.mma_n))
+             : p->mma_kind == MMA_F8 ? make_idesc(0, 0, 128, static_cast<uint32_t>(dc.mma_n))
+                                     : make_idesc(fmt16, fmt16, 128, static_cast<uint32_t>(dc.mma_n));
     dp.sfw = p->sfb_used; dp.sfx = p->sfa_used;
     dp.sf_katoms = static_cast<int>(sf_katoms(d.K));
     dp.status = p->status;
@@ -391,7 +430,7 @@ blz_status decode_launch(blz_gemm_plan* p, void* C, cudaStream_t stream) {
     fill_epilogue(p, C, dp.epi);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(p->grid));
-    cfg.blockDim = dim3(384);
+    cfg.blockDim = dim3(static_cast<unsigned>(p->decode_threads));
     cfg.dynamicSmemBytes = static_cast<size_t>(p->decode_smem);
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -526,17 +565,17 @@ blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_p
     if ((s = prepare_b(p))) return fail(s);
     if ((s = prepare_a_scales(p))) return fail(s);
 
-    if (w4a16) {
-        // The tensor core consumes 16-bit weights: every execute expands the packed weights into
+    // Skinny activations stream the weights once through the decode kernels (every kind).
+    const bool want_decode = desc->variant == BLZ_VARIANT_DECODE || (desc->variant == BLZ_VARIANT_AUTO && desc->M <= 64);
+    if (w4a16 && !want_decode) {
+        // The tiled kernels consume 16-bit weights: every execute expands the packed weights into
         // this buffer (q * block scale, exact in 16 bits); the fp32 tensor scale goes into alpha.
         if ((s = dev_alloc(p, &p->own_w16, static_cast<int64_t>(desc->N) * desc->K * 2, false))) return fail(s);
         p->launches = 2;
     }
 
-    const bool want_decode = desc->variant == BLZ_VARIANT_DECODE ||
-                             (desc->variant == BLZ_VARIANT_AUTO && desc->kind == BLZ_GEMM_NVFP4 && desc->M <= 64);
     if (want_decode) {
-        if (desc->kind != BLZ_GEMM_NVFP4 || desc->M > 64) return fail(BLZ_ERR_UNSUPPORTED);
+        if (desc->M > 64) return fail(BLZ_ERR_UNSUPPORTED);
         p->variant = BLZ_VARIANT_DECODE;
         if ((s = decode_setup(p))) return fail(s);
     } else {

@@ -285,6 +285,41 @@ __host__ __device__ constexpr uint32_t make_idesc_nvf4(uint32_t mma_m, uint32_t 
     return (1u << 7) | (1u << 10) | ((mma_n >> 3) << 17) | ((mma_m >> 4) << 24);
 }
 
+
+// ------------------------------------------------------------- narrow-format conversions
+// Two E2M1 values (one byte, first value in the low nibble) -> two fp16 values.
+__device__ __forceinline__ uint32_t cvt_e2m1x2_to_f16x2(uint32_t byte) {
+    uint32_t r;
+    asm("{\n\t.reg .b8 lo, hi;\n\t.reg .b16 h;\n\t"
+        "cvt.u16.u32 h, %1;\n\t"
+        "mov.b16 {lo, hi}, h;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, lo;\n\t}"
+        : "=r"(r) : "r"(byte));
+    return r;
+}
+// Two E4M3 values (first in the low byte) -> two fp16 values.
+__device__ __forceinline__ uint32_t cvt_e4m3x2_to_f16x2(uint16_t two) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(two));
+    return r;
+}
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+// two floats -> packed bf16 (lo in the low half), round to nearest even
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ uint32_t mul_f16x2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
 // ---------------------------------------------------------------------- MMA
 // All issued by one thread.  `accumulate` = 0 overwrites the accumulator, 1 adds to it.
 

@@ -67,6 +67,11 @@ def _dense_inputs(oracle, kind, M, N, K, scale=1.0):
     ("bf16", "bf16", "512x256", (512, 256, 64)),     # two pairs sharing B, one tile, one K stage
     ("bf16", "f32", "512x256", (700, 520, 392)),     # ragged; the second pair partly outside M
     ("f16", "f16", "512x256", (2048, 2304, 1024)),
+    ("f16", "f32", "decode", (1, 128, 64)),          # skinny-M weight stream: one tile, one K stage
+    ("bf16", "bf16", "decode", (16, 384, 520)),      # ragged K stage
+    ("f16", "f16", "decode", (33, 1000, 1032)),      # 64-row instruction, ragged N
+    ("bf16", "f32", "decode", (64, 4096, 4096)),     # K split across a cluster
+    ("bf16", "bf16", "decode", (5, 512, 8192)),      # deep K split, ring wraps
 ])
 def test_dense16(oracle, cuda_device, kind, out_dtype, variant, shape):
     from blaze_b200 import GemmPlan
@@ -143,6 +148,11 @@ def _fp8_inputs(oracle, M, N, K):
     ("512x256", (512, 256, 128)),
     ("512x256", (1024, 2048, 2048)),
     ("512x256", (300, 328, 144)),
+    ("decode", (1, 256, 128)),
+    ("decode", (32, 4096, 1024)),
+    ("decode", (48, 1000, 1136)),
+    ("decode", (7, 4096, 11008)),
+    ("decode", (64, 12288, 4096)),
 ])
 def test_fp8(oracle, cuda_device, variant, shape):
     from blaze_b200 import GemmPlan
@@ -369,7 +379,12 @@ def test_nvfp4_config5_sampled(oracle, cuda_device):
 
 # ------------------------------------------------------------------------------------- W4A16
 
-@pytest.mark.parametrize("kind,shape", [("w4a16_bf16", (128, 256, 512)), ("w4a16_f16", (200, 328, 160)), ("w4a16_bf16", (512, 1024, 2048))])
+@pytest.mark.parametrize("kind,shape", [
+    ("w4a16_bf16", (128, 256, 512)), ("w4a16_f16", (200, 328, 160)), ("w4a16_bf16", (512, 1024, 2048)),
+    # M <= 64: the weight-stream kernel that expands the packed weights in shared memory
+    ("w4a16_f16", (1, 128, 64)), ("w4a16_bf16", (1, 256, 512)), ("w4a16_f16", (16, 328, 160)), ("w4a16_bf16", (40, 1000, 1056)),
+    ("w4a16_bf16", (64, 4096, 4096)), ("w4a16_f16", (8, 4096, 11008)), ("w4a16_bf16", (32, 12288, 4096)),
+])
 def test_w4a16(oracle, cuda_device, kind, shape):
     from blaze_b200 import GemmPlan
     M, N, K = shape
@@ -382,6 +397,8 @@ def test_w4a16(oracle, cuda_device, kind, shape):
     want = oracle.widen(oracle.narrow(oracle.epilogue(acc, alpha), act), act)
     C = _out_tensor(M, N, act, cuda_device)
     plan = GemmPlan(kind, M, N, K, bits16_to_torch(A, act, cuda_device), _u8(bd, cuda_device), B_sf=_u8(bsf, cuda_device), b_scale=gb, out_dtype=act)
+    if M <= 64:
+        assert plan.info()["variant"] == 3 and plan.info()["launches"] == 1    # one kernel, no expanded copy of the weights
     _run(plan, C)
     assert_close(torch_to_f32(C, oracle, act), want, "w4a16 %s %s" % (kind, shape))
     plan.destroy()
