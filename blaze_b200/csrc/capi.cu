@@ -342,10 +342,13 @@ DecodeChoice decode_choice() {
     return DecodeChoice{reinterpret_cast<const void*>(&decode_stream_kernel<KIND, MMA_N, STAGES>), MMA_N, STAGES, static_cast<int>(Cfg::SMEM_BYTES),
                         Cfg::THREADS, Cfg::MAX_SPLIT, static_cast<int>(Cfg::TMEM_COLS)};
 }
-template <bool BF16, int MMA_N, int LSTAGES, int OSTAGES>
+#ifndef BLZ_W4_L16
+#define BLZ_W4_L16 6
+#endif
+template <bool BF16, int MMA_N, int LSTAGES>
 DecodeChoice decode_choice_w4a16() {
-    using Cfg = DecodeW4A16Config<MMA_N, LSTAGES, OSTAGES>;
-    return DecodeChoice{reinterpret_cast<const void*>(&decode_w4a16_kernel<BF16, MMA_N, LSTAGES, OSTAGES>), MMA_N, LSTAGES, static_cast<int>(Cfg::SMEM_BYTES),
+    using Cfg = DecodeW4A16Config<MMA_N, LSTAGES>;
+    return DecodeChoice{reinterpret_cast<const void*>(&decode_w4a16_kernel<BF16, MMA_N, LSTAGES>), MMA_N, LSTAGES, static_cast<int>(Cfg::SMEM_BYTES),
                         Cfg::THREADS, Cfg::MAX_SPLIT, static_cast<int>(Cfg::TMEM_COLS)};
 }
 template <int KIND>
@@ -354,7 +357,7 @@ DecodeChoice decode_choice_for(int M) {
 }
 template <bool BF16>
 DecodeChoice decode_choice_w4a16_for(int M) {
-    return M <= 16 ? decode_choice_w4a16<BF16, 16, 12, 3>() : M <= 32 ? decode_choice_w4a16<BF16, 32, 10, 3>() : decode_choice_w4a16<BF16, 64, 8, 3>();
+    return M <= 16 ? decode_choice_w4a16<BF16, 16, BLZ_W4_L16>() : M <= 32 ? decode_choice_w4a16<BF16, 32, 6>() : decode_choice_w4a16<BF16, 64, 3>();
 }
 DecodeChoice pick_decode_kernel(int mma_kind, bool w4a16, bool bf16, int M) {
     if (w4a16) return bf16 ? decode_choice_w4a16_for<true>(M) : decode_choice_w4a16_for<false>(M);
@@ -390,10 +393,10 @@ blz_status decode_setup(blz_gemm_plan* p) {
     blz_status s;
     DecodeStreamParams& dp = p->dp;
     if (w4) {
-        // packed weights: 32 bytes (64 values) x 128 rows per stage, no swizzle -- the expansion warps read them
+        // packed weights: 128 bytes (256 values) x 128 rows per load stage; the expansion warps undo the swizzle
         const int64_t rbw = d.K / 2;
-        s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rbw), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rbw), 32, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
-        dp.k_stages_total = static_cast<int>(ceil_div(d.K, 64));
+        s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rbw), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rbw), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+        dp.k_stages_total = static_cast<int>(ceil_div(rbw, 128));
     } else {
         const int64_t rb = row_bytes(p->mma_kind, d.K);
         s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rb), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -689,7 +692,7 @@ blz_status blz_gemm_launch(const blz_gemm_desc* desc, void* C, void* stream) {
     return s;
 }
 
-#ifdef BLZ_KERNEL_TIMING
+#if defined(BLZ_KERNEL_TIMING) || defined(BLZ_W4_TIMELINE)
 // Tuning builds only: copies the per-CTA cycle counters of the last tiled-kernel launch to the host.
 blz_status blz_debug_read_timing(unsigned long long* out, int n_words) {
     BLZ_CUDA(cudaDeviceSynchronize());

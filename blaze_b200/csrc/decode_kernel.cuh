@@ -114,7 +114,7 @@ decode_nvf4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 #endif
 
     if (warp == 0) {
-        if (lane == 0) {
+        if (elect_one()) {
             BLZ_T_DECL(t_wait);
             const uint64_t pol_stream = l2_policy_evict_first();   // weights are read once
             const uint64_t pol_keep = l2_policy_evict_last();      // activations are shared by every CTA
@@ -141,7 +141,7 @@ decode_nvf4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0) {
+        if (elect_one()) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             BLZ_T_DECL(t_wait_full);

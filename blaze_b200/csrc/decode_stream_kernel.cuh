@@ -31,7 +31,7 @@ namespace blz {
 struct DecodeStreamParams {
     int M, N;
     int n_tiles;             // ceil(N / 128)
-    int k_stages_total;      // ceil(bytes of one operand row / 128); W4A16: ceil(K / 64)
+    int k_stages_total;      // ceil(bytes of one weight row / 128)
     int stages_per_split;
     int split;               // = cluster size: 1, 2, 4 or 8
     uint32_t idesc;
@@ -59,7 +59,7 @@ __device__ __forceinline__ void st_shared_cluster_f32(uint32_t addr, uint32_t ct
 // a K split every thread of every CTA of the cluster meets at two cluster barriers around the
 // reduction through the leader's shared memory (at `base`, free once the main loops are over);
 // the leader applies the epilogue and writes C.
-template <int MMA_N>
+template <int MMA_N, bool SLEEPY = false, int NACC = 1>
 __device__ __forceinline__ void decode_epilogue(const DecodeStreamParams& p, uint32_t base, uint8_t* gen_base, uint32_t tmem_base,
                                                 uint32_t acc_full_bar, volatile int* abort_flag, int n_tile, int split_idx,
                                                 int warp, int lane, [[maybe_unused]] long long t_entry) {
@@ -81,7 +81,7 @@ __device__ __forceinline__ void decode_epilogue(const DecodeStreamParams& p, uin
     const void* const e_res = p.epi.residual;
     asm volatile("" ::"f"(e_alpha), "r"(e_mode), "r"(e_out), "r"(e_vec), "r"(p_M), "r"(p_N), "r"(p_split), "l"(e_ldc), "l"(e_ldr), "l"(e_C), "l"(e_bias), "l"(e_res));
     if (is_epi) {
-        epi_ok = mbar_wait(acc_full_bar, 0u, abort_flag);
+        epi_ok = SLEEPY ? mbar_wait_sleepy(acc_full_bar, 0u, abort_flag) : mbar_wait(acc_full_bar, 0u, abort_flag);
 #ifdef BLZ_KERNEL_TIMING
         if (threadIdx.x == 128) BLZ_T_STORE(5, clock64() - t_entry);
 #endif
@@ -91,12 +91,19 @@ __device__ __forceinline__ void decode_epilogue(const DecodeStreamParams& p, uin
         if (epi_ok) {
             tc_fence_after_sync();
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+            // NACC > 1: the kernel kept NACC independent partial accumulators 64 columns apart
+            // (consecutive tcgen05.mma into one accumulator wait for each other); they are added
+            // here in a fixed order.
 #pragma unroll
-            for (int c = 0; c < MMA_N; c += 16) {
-                uint32_t r[16];
-                tmem_ld16(t_row + c, r);
+            for (int a = 0; a < NACC; ++a) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) acc[c + j] = __uint_as_float(r[j]);
+                for (int c = 0; c < MMA_N; c += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(t_row + a * 64 + c, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc[c + j] = a == 0 ? __uint_as_float(r[j]) : acc[c + j] + __uint_as_float(r[j]);
+                }
             }
             tmem_ld_wait();
             tc_fence_before_sync();
@@ -298,7 +305,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
 #endif
 
     if (warp == 0) {
-        if (lane == 0) {
+        if (elect_one()) {
             const uint64_t pol_stream = l2_policy_evict_first();   // weights are read once
             const uint64_t pol_keep = l2_policy_evict_last();      // activations are shared by every CTA
             int stage = 0; uint32_t phase = 0;
@@ -342,7 +349,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0) {
+        if (elect_one()) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             for (int ks = ks_begin; ks < ks_end; ++ks) {
@@ -408,49 +415,76 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
 // 16-bit activations x NVFP4 weights.
 //
 // The tensor core has no instruction that takes one 4-bit and one 16-bit operand, so the packed
-// weights are expanded on the way: eight helper warps turn every stage of packed weights (128 rows
-// x 64 K values = 4 KB, plus one 512-byte atom of block scales) into the fp16 operand tile
-// in the activations' 16-bit format (q * block scale: at most six significant bits, exact in fp16
-// and in bf16), 128-byte swizzled like a TMA load would have left it.  Both operands of a
-// kind::f16 instruction must have the same format -- an fp16 A with a bf16 B is rejected by the
-// hardware as an illegal instruction -- so bf16 activations need bf16 weights, which cost three
-// more integer instructions per pair of values than fp16 (there is no E2M1 -> bf16 conversion).
-// HBM only ever sees the 4.5 bits per weight.
+// weights are expanded on the way, in the activations' 16-bit format (q * block scale: at most six
+// significant bits, exact in fp16 and in bf16).  Both operands of a kind::f16 instruction must
+// have the same format -- an fp16 A with a bf16 B is rejected by the hardware as an illegal
+// instruction -- so bf16 activations need bf16 weights, which cost three more integer
+// instructions per pair of values than fp16 (there is no E2M1 -> bf16 conversion).
 //
-// Two rings: a deep one of small load stages (packed weights, scales, activation tile) so that
-// enough bytes are in flight to cover HBM latency, and a short one of expanded 16 KB operand tiles.
+// The expanded weights never touch shared memory: they are the instruction's A operand (128 weight
+// rows = 128 tensor-memory lanes), and tcgen05.mma can read A from tensor memory.  Sixteen helper
+// warps in four groups expand one sub-stage each (64 K values = 32 columns of packed 16-bit
+// pairs) straight from the packed bytes in shared memory into registers and tcgen05.st them into
+// a ring of operand slots next to the accumulator.  Measured on B200, the alternative -- writing a
+// 16 KB swizzled operand tile per 64 K values to shared memory for the tensor core to read back --
+// is bound by shared-memory bandwidth (a 128 x 16 x 16 MMA already spends 48 cycles reading its A
+// tile from shared memory) and runs three times slower.  HBM only sees the 4.5 bits per weight.
 //
-// Warps: 0 TMA producer, 1 MMA issuer, 2 tensor-memory alloc, 4-7 epilogue, 8-15 expansion.
+// A load stage is what the NVFP4 kernel loads too: 128 weight rows x 128 packed bytes (256 K
+// values; full 128-byte lines), their four 512-byte scale atoms, and the four activation tiles of
+// those 256 K values.  It is consumed in four sub-stages of 64 K values, one group of four
+// tcgen05.mma (K = 16 each) per sub-stage; expansion group g always takes sub-stage g.
+//
+// The tensor pipe is the bound.  Measured on B200: consecutive tcgen05.mma into the same
+// accumulator wait for each other (~100 cycles apiece for a 128 x 16 x 16 instruction whose
+// arithmetic is worth 8), so the four K = 16 slices of a sub-stage go to four independent
+// accumulators that the epilogue adds; a tcgen05.commit costs ~45 cycles of the pipe, so the
+// operand slots are handed back in groups of four (one commit per load stage, plus the one that
+// frees the load stage) instead of one by one.
+//
+// Warps: 0 TMA producer, 1 MMA issuer, 2 tensor-memory alloc, 4-7 epilogue, 8-23 expansion
+// (group = (warp - 8) / 4 = the sub-stage it takes; warp % 4 selects its 32 lanes).
 
-template <int MMA_N, int LSTAGES, int OSTAGES>
+template <int MMA_N, int LSTAGES>
 struct DecodeW4A16Config {
-    static constexpr int THREADS = 512;
-    static constexpr int EXPAND_WARPS = 8;
-    static constexpr uint32_t OP_BYTES = 128 * 128;          // expanded weight tile: 128 rows x 64 values x 2 bytes
-    static constexpr uint32_t X_BYTES = MMA_N * 128;
+    static constexpr int EXPAND_GROUPS = 4;                  // groups of four warps (one per 32 lanes)
+    static constexpr int THREADS = 256 + 128 * EXPAND_GROUPS;
+    static constexpr int SUBS = 4;                           // sub-stages (64 K values) per load stage
+#ifndef BLZ_W4_OGROUPS
+#define BLZ_W4_OGROUPS 2
+#endif
+    static constexpr int OGROUPS = BLZ_W4_OGROUPS;           // operand slot groups in tensor memory, one per load stage in flight
+    static constexpr int OSLOTS = OGROUPS * SUBS;
+    static constexpr uint32_t X_BYTES = MMA_N * 128;         // one activation tile (64 K values)
     static constexpr uint32_t X_REGION = X_BYTES < 1024 ? 1024 : X_BYTES;
-    static constexpr uint32_t PK_BYTES = 128 * 32;           // packed weights of one stage
-    static constexpr uint32_t SF_BYTES = 512;                // one atom: 128 rows x 4 block scales
-    static constexpr uint32_t TX_BYTES = PK_BYTES + SF_BYTES + X_BYTES;
-    static constexpr uint32_t OP_OFF = 0;
-    static constexpr uint32_t X_OFF = OSTAGES * OP_BYTES;
-    static constexpr uint32_t PK_OFF = X_OFF + LSTAGES * X_REGION;
-    static constexpr uint32_t SF_OFF = PK_OFF + LSTAGES * PK_BYTES;
+    static constexpr uint32_t PK_BYTES = 128 * 128;          // packed weights of one load stage
+    static constexpr uint32_t SF_BYTES = SUBS * 512;         // four atoms: 128 rows x 4 block scales each
+    static constexpr uint32_t TX_BYTES = PK_BYTES + SF_BYTES + SUBS * X_BYTES;
+    static constexpr uint32_t PK_OFF = 0;
+    static constexpr uint32_t X_OFF = PK_OFF + LSTAGES * PK_BYTES;
+    static constexpr uint32_t SF_OFF = X_OFF + LSTAGES * SUBS * X_REGION;
     static constexpr uint32_t RING_BYTES = SF_OFF + LSTAGES * SF_BYTES;
-    static constexpr uint32_t TMEM_COLS = 64;
-    static constexpr uint32_t NUM_BARS = 2 * LSTAGES + 2 * OSTAGES + 1;
+    static constexpr int NACC = 4;                           // independent accumulators, one per K = 16 slice of a sub-stage, 64 columns apart
+    static constexpr uint32_t OP_COL0 = 64 * NACC;
+    static constexpr uint32_t OP_COLS = 32;                  // 64 K values x 16 bit per lane
+    static constexpr uint32_t TMEM_COLS = 512;               // the whole tensor memory: one CTA per SM (see SMEM_BYTES)
+    static constexpr uint32_t NUM_BARS = 2 * LSTAGES + OSLOTS + OGROUPS + 1;
     static constexpr uint32_t BAR_BYTES = 8 * NUM_BARS + 16;
     static constexpr uint32_t SMEM_BYTES = RING_BYTES + BAR_BYTES + 1024;
     static constexpr int MAX_SPLIT = RING_BYTES / (MMA_N * 128 * 4) + 1 < 8 ? RING_BYTES / (MMA_N * 128 * 4) + 1 : 8;
     static_assert(MMA_N % 16 == 0 && MMA_N >= 16 && MMA_N <= 64, "activation rows per instruction");
+    static_assert(OP_COL0 + OSLOTS * OP_COLS <= TMEM_COLS, "operand slots exceed the allocation");
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared-memory limit");
     static_assert(MMA_N * 128 * 4 <= RING_BYTES, "fp32 output staging must fit the rings");
+    static_assert(SMEM_BYTES > 116 * 1024, "two CTAs on one SM would wait for each other's tensor memory");
+    static_assert(EXPAND_GROUPS == SUBS, "one expansion group per sub-stage");
 };
 
-// Expands one stage: thread t of 256 takes half a row (32 values = 16 packed bytes, two block
-// scales).  packed: [128][32] bytes, even k in the low nibble; sf_atom: the tiled scale layout,
-// row r at byte (r % 32) * 16 + (r / 32) * 4; dst: shared-memory address of the operand tile
-// (1024-byte aligned), 16-byte unit j of row r at unit j ^ (r % 8).
+// One thread expands the 64 K values of its weight row for one sub-stage into 32 registers of
+// packed 16-bit pairs (lower k in the low half), the tensor-memory layout of a K-major A operand.
+// packed_row: the row's 128 packed bytes of the load stage as a 128-byte-swizzled TMA load left
+// them (16-byte unit u at unit u ^ (row % 8)), even k in the low nibble; sf4: the row's four
+// block scales of this sub-stage (E4M3, lowest k first).
 //
 // fp16: cvt.e2m1x2 -> f16x2, one packed multiply by the block scale.
 // bf16: the fp16 bit pattern of an E2M1 value, shifted right by three with the sign put back,
@@ -459,41 +493,38 @@ struct DecodeW4A16Config {
 // therefore prepared as bf16(scale * 2^112) (at most 2^121, in range) and one packed bf16
 // multiply gives value * scale exactly.
 template <bool BF16>
-__device__ __forceinline__ void expand_w4_stage(const uint8_t* packed, const uint8_t* sf_atom, uint32_t dst, int t) {
-    const int row = t >> 1, half = t & 1;
-    const uint4 w = *reinterpret_cast<const uint4*>(packed + row * 32 + half * 16);
-    const uint32_t sf4 = *reinterpret_cast<const uint32_t*>(sf_atom + (row & 31) * 16 + (row >> 5) * 4);
-    const uint32_t s01 = cvt_e4m3x2_to_f16x2(static_cast<uint16_t>(sf4 >> (16 * half)));
-    uint32_t s_lo, s_hi;
+__device__ __forceinline__ void expand_w4_row(const uint8_t* packed_row, int row, int sub, uint32_t sf4, uint32_t (&r)[32]) {
+    const uint4 w0 = *reinterpret_cast<const uint4*>(packed_row + (((sub * 2) ^ (row & 7)) << 4));
+    const uint4 w1 = *reinterpret_cast<const uint4*>(packed_row + (((sub * 2 + 1) ^ (row & 7)) << 4));
+    const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    const uint32_t s01 = cvt_e4m3x2_to_f16x2(static_cast<uint16_t>(sf4)), s23 = cvt_e4m3x2_to_f16x2(static_cast<uint16_t>(sf4 >> 16));
+    uint32_t s[4];
     if constexpr (BF16) {
-        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&s01));
+        const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&s01)), f23 = __half22float2(*reinterpret_cast<const __half2*>(&s23));
         const float big = __uint_as_float(0x77800000u);                    // 2^112
-        s_lo = pack_bf16x2(f.x * big, f.x * big);
-        s_hi = pack_bf16x2(f.y * big, f.y * big);
+        s[0] = pack_bf16x2(f01.x * big, f01.x * big); s[1] = pack_bf16x2(f01.y * big, f01.y * big);
+        s[2] = pack_bf16x2(f23.x * big, f23.x * big); s[3] = pack_bf16x2(f23.y * big, f23.y * big);
     } else {
-        s_lo = __byte_perm(s01, 0, 0x1010); s_hi = __byte_perm(s01, 0, 0x3232);
+        s[0] = __byte_perm(s01, 0, 0x1010); s[1] = __byte_perm(s01, 0, 0x3232);
+        s[2] = __byte_perm(s23, 0, 0x1010); s[3] = __byte_perm(s23, 0, 0x3232);
     }
-    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
-    const uint32_t drow = dst + row * 128;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        const uint32_t s = c < 2 ? s_lo : s_hi;
-        uint32_t o[4];
+    for (int wd = 0; wd < 8; ++wd) {
+        uint32_t h[4];
+        cvt_e2m1x8_to_f16x2x4(words[wd], h);
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-            const uint32_t h2 = cvt_e2m1x2_to_f16x2((words[c] >> (8 * b)) & 0xFFu);
-            if constexpr (BF16) o[b] = mul_bf16x2(((h2 >> 3) & 0x0FFF0FFFu) | (h2 & 0x80008000u), s);
-            else o[b] = mul_f16x2(h2, s);
+            if constexpr (BF16) r[4 * wd + b] = mul_bf16x2(((h[b] >> 3) & 0x0FFF0FFFu) | (h[b] & 0x80008000u), s[wd >> 1]);
+            else r[4 * wd + b] = mul_f16x2(h[b], s[wd >> 1]);
         }
-        const uint32_t addr = drow + (static_cast<uint32_t>((half * 4 + c) ^ (row & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
     }
 }
 
-template <bool BF16, int MMA_N, int LSTAGES, int OSTAGES>
-__global__ void __launch_bounds__(512, 1)
+template <bool BF16, int MMA_N, int LSTAGES>
+__global__ void __launch_bounds__((DecodeW4A16Config<MMA_N, LSTAGES>::THREADS), 1)
 decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const DecodeStreamParams p) {
-    using Cfg = DecodeW4A16Config<MMA_N, LSTAGES, OSTAGES>;
+    using Cfg = DecodeW4A16Config<MMA_N, LSTAGES>;
+    constexpr int SUBS = Cfg::SUBS, OSLOTS = Cfg::OSLOTS;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -503,8 +534,8 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     auto load_full = [&](int s) { return bar_base + 8u * s; };
     auto load_empty = [&](int s) { return bar_base + 8u * (LSTAGES + s); };
     auto op_ready = [&](int s) { return bar_base + 8u * (2 * LSTAGES + s); };
-    auto op_empty = [&](int s) { return bar_base + 8u * (2 * LSTAGES + OSTAGES + s); };
-    const uint32_t acc_full_bar = bar_base + 8u * (2 * LSTAGES + 2 * OSTAGES);
+    auto og_empty = [&](int g) { return bar_base + 8u * (2 * LSTAGES + OSLOTS + g); };
+    const uint32_t acc_full_bar = bar_base + 8u * (2 * LSTAGES + OSLOTS + Cfg::OGROUPS);
     const uint32_t slot_off = Cfg::RING_BYTES + 8u * Cfg::NUM_BARS;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + slot_off);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + slot_off + 4);
@@ -518,7 +549,8 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < LSTAGES; ++s) { mbar_init(load_full(s), 1); mbar_init(load_empty(s), 1); }
-        for (int s = 0; s < OSTAGES; ++s) { mbar_init(op_ready(s), Cfg::EXPAND_WARPS); mbar_init(op_empty(s), 1); }
+        for (int s = 0; s < OSLOTS; ++s) mbar_init(op_ready(s), 4);
+        for (int g = 0; g < Cfg::OGROUPS; ++g) mbar_init(og_empty(g), 1);
         mbar_init(acc_full_bar, 1);
         *abort_flag = 0;
         fence_mbar_init();
@@ -538,13 +570,21 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     griddep_launch_dependents();
 
     if (warp == 0) {
-        if (lane == 0) {
+        if (elect_one()) {
             const uint64_t pol_stream = l2_policy_evict_first();
             const uint64_t pol_keep = l2_policy_evict_last();
             auto load_weights = [&](int ks, int stage) {
+#ifdef BLZ_W4_NO_W
+                mbar_arrive_expect_tx(load_full(stage), Cfg::TX_BYTES - Cfg::PK_BYTES);
+                if (ks < 0)
+#elif defined(BLZ_W4_ONE_X)
+                mbar_arrive_expect_tx(load_full(stage), Cfg::TX_BYTES - 3 * Cfg::X_BYTES);
+#else
                 mbar_arrive_expect_tx(load_full(stage), Cfg::TX_BYTES);
-                tma_load_2d_hint(base + Cfg::PK_OFF + stage * Cfg::PK_BYTES, &tm_w, ks * 32, n_tile * 128, load_full(stage), pol_stream);
-                bulk_load_1d(base + Cfg::SF_OFF + stage * Cfg::SF_BYTES, p.sfw + (static_cast<size_t>(n_tile) * p.sf_katoms + ks) * 512, Cfg::SF_BYTES, load_full(stage));
+#endif
+                tma_load_2d_hint(base + Cfg::PK_OFF + stage * Cfg::PK_BYTES, &tm_w, ks * 128, n_tile * 128, load_full(stage), pol_stream);
+                bulk_load_1d(base + Cfg::SF_OFF + stage * Cfg::SF_BYTES, p.sfw + (static_cast<size_t>(n_tile) * p.sf_katoms + static_cast<size_t>(ks) * SUBS) * 512,
+                             Cfg::SF_BYTES, load_full(stage));
             };
             // packed weights and their scales of the first ring do not depend on earlier kernels
             const int n_pre = min(ks_end - ks_begin, LSTAGES);
@@ -557,55 +597,120 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                         atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_PRODUCER); *abort_flag = 1; break;
                     }
                     load_weights(ks, stage);
+                    if (ks - ks_begin == 8) BLZ_TL_STORE(0, clock64());
                 }
-                tma_load_2d_hint(base + Cfg::X_OFF + stage * Cfg::X_REGION, &tm_x, ks * 128, 0, load_full(stage), pol_keep);
+#ifdef BLZ_W4_ONE_X
+                for (int j = 0; j < 1; ++j)
+#else
+#pragma unroll
+                for (int j = 0; j < SUBS; ++j)
+#endif
+                    tma_load_2d_hint(base + Cfg::X_OFF + (stage * SUBS + j) * Cfg::X_REGION, &tm_x, (ks * SUBS + j) * 128, 0, load_full(stage), pol_keep);
                 if (++stage == LSTAGES) { stage = 0; phase ^= 1u; }
             }
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0) {
-            int ls = 0, os = 0; uint32_t ophase = 0;
+        if (elect_one()) {
+            // This thread shares its scheduler with expansion warps, so its instruction count is on the
+            // critical path: the loop is unrolled over one full period of both rings, which turns every
+            // descriptor, tensor-memory address, barrier address and phase into "base + constant".
+            constexpr int OGROUPS = Cfg::OGROUPS;
+            constexpr int LPERIOD = (LSTAGES % (2 * OGROUPS) == 0) ? LSTAGES : (LSTAGES % 2 == 0 ? LSTAGES * OGROUPS : LSTAGES * 2 * OGROUPS);
+            static_assert(LPERIOD % LSTAGES == 0 && LPERIOD % (2 * OGROUPS) == 0, "unroll period (load stages): rings and phases repeat");
+            const uint64_t dx0 = make_desc_k_sw128(base + Cfg::X_OFF);
+            const uint32_t a0 = tmem_base + Cfg::OP_COL0;
+            const int n_load = ks_end - ks_begin;
             bool ok = true;
-            for (int ks = ks_begin; ks < ks_end; ++ks) {
-                // "expanded" implies "landed": the expansion warps waited for the stage's loads
-                if (!mbar_wait(op_ready(os), ophase, abort_flag)) {
-                    atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
-                }
-                tc_fence_after_sync();
-                const uint32_t sw = base + Cfg::OP_OFF + os * Cfg::OP_BYTES;
-                const uint32_t sx = base + Cfg::X_OFF + ls * Cfg::X_REGION;
+            BLZ_T_DECL(t_ready);
+            for (int l0 = 0; ok && l0 < n_load; l0 += LPERIOD) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint32_t accumulate = (ks != ks_begin || k != 0) ? 1u : 0u;
-                    umma_f16(tmem_base, make_desc_k_sw128(sw + k * 32), make_desc_k_sw128(sx + k * 32), p.idesc, accumulate);
+                for (int ul = 0; ul < LPERIOD; ++ul) {
+                    if (l0 + ul >= n_load) break;
+                    const int ls = ul % LSTAGES, og = ul % OGROUPS;
+                    const uint32_t ophase = static_cast<uint32_t>(ul / OGROUPS) & 1u;
+#pragma unroll
+                    for (int j = 0; j < SUBS; ++j) {
+                        const int os = og * SUBS + j;
+                        [[maybe_unused]] const long long tr = BLZ_T_NOW();
+                        // "expanded" implies "landed": the expansion warps waited for the stage's loads
+                        if (!mbar_wait(op_ready(os), ophase, abort_flag)) {
+                            atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
+                        }
+                        BLZ_T_ADD(t_ready, tr);
+                        if (l0 + ul == 8 && j == 0) BLZ_TL_STORE(13, clock64());
+                        if (l0 + ul == 8 && j == 3) BLZ_TL_STORE(14, clock64());
+                        tc_fence_after_sync();
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const uint32_t accumulate = (ul | j) != 0 ? 1u : (l0 != 0 ? 1u : 0u);
+                            // A: 16 K values = 8 columns of this slot; B: 32 bytes further into the activation tile
+#ifndef BLZ_W4_SKIP_MMA
+                            umma_f16_ts(tmem_base + 64 * k, a0 + os * Cfg::OP_COLS + k * 8, dx0 + (((ls * SUBS + j) * Cfg::X_REGION + k * 32) >> 4), p.idesc, accumulate);
+#else
+                            if (k == 0 && j == 0) umma_f16_ts(tmem_base, a0 + os * Cfg::OP_COLS + k * 8, dx0 + (((ls * SUBS + j) * Cfg::X_REGION + k * 32) >> 4), p.idesc, accumulate);
+#endif
+                        }
+                    }
+                    if (!ok) break;
+                    tc_commit(og_empty(og));        // the four operand slots of this load stage
+                    tc_commit(load_empty(ls));      // its packed bytes were expanded before the MMAs, its activation tiles are read by them
+                    if (l0 + ul == 8) BLZ_TL_STORE(15, clock64());
                 }
-                tc_commit(op_empty(os));
-                tc_commit(load_empty(ls));
-                if (++ls == LSTAGES) ls = 0;
-                if (++os == OSTAGES) { os = 0; ophase ^= 1u; }
             }
             if (ok) tc_commit(acc_full_bar);
+            BLZ_T_STORE(8, t_ready); BLZ_T_STORE(9, BLZ_T_NOW() - t_entry);
         }
         __syncwarp();
     } else if (warp >= 8) {
-        const int t = threadIdx.x - 256;
-        int ls = 0, os = 0; uint32_t lphase = 0, ophase = 0;
-        for (int ks = ks_begin; ks < ks_end; ++ks) {
-            if (!mbar_wait(load_full(ls), lphase, abort_flag) || !mbar_wait(op_empty(os), ophase ^ 1u, abort_flag)) {
+        const int j = (warp - 8) >> 2, q = warp & 3;               // group = the sub-stage it takes; which 32 tensor-memory lanes
+        const int row = q * 32 + lane;
+        const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::OP_COL0;
+        const int n_load = ks_end - ks_begin;
+        BLZ_T_DECL(t_load); BLZ_T_DECL(t_slot); BLZ_T_DECL(t_expand); BLZ_T_DECL(t_sync);
+        for (int li = 0; li < n_load; ++li) {
+            const int ls = li % LSTAGES, og = li % Cfg::OGROUPS, os = og * SUBS + j;
+            const uint32_t lphase = static_cast<uint32_t>(li / LSTAGES) & 1u, ophase = static_cast<uint32_t>(li / Cfg::OGROUPS) & 1u;
+            [[maybe_unused]] const long long t0 = BLZ_T_NOW();
+            if (!mbar_wait_warp(load_full(ls), lphase, abort_flag)) {
                 atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; break;
             }
-            expand_w4_stage<BF16>(gen_base + Cfg::PK_OFF + ls * Cfg::PK_BYTES, gen_base + Cfg::SF_OFF + ls * Cfg::SF_BYTES,
-                            base + Cfg::OP_OFF + os * Cfg::OP_BYTES, t);
-            fence_proxy_async_smem();        // the tensor core reads the tile through the async proxy
+            [[maybe_unused]] const long long t1 = BLZ_T_NOW();
+            if (li == 8 && q == 0 && lane == 0) BLZ_TL_STORE(1 + j, clock64());
+            uint32_t r[32];
+            const uint32_t sf4 = *reinterpret_cast<const uint32_t*>(gen_base + Cfg::SF_OFF + ls * Cfg::SF_BYTES + j * 512 + lane * 16 + q * 4);
+#ifndef BLZ_W4_SKIP_EXPAND
+            expand_w4_row<BF16>(gen_base + Cfg::PK_OFF + ls * Cfg::PK_BYTES + row * 128, row, j, sf4, r);
+#else
+#pragma unroll
+            for (int z = 0; z < 32; ++z) r[z] = sf4 + z;
+#endif
+            [[maybe_unused]] const long long t2 = BLZ_T_NOW();
+            // the slot group is free once the MMAs of the load stage that used it last have completed
+            if (!mbar_wait_warp(og_empty(og), ophase ^ 1u, abort_flag)) {
+                atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; break;
+            }
+            tc_fence_after_sync();
+            [[maybe_unused]] const long long t3 = BLZ_T_NOW();
+            if (li == 8 && q == 0 && lane == 0) BLZ_TL_STORE(5 + j, clock64());
+            tmem_st32(t_lane + os * Cfg::OP_COLS, r);
+            tmem_st_wait();
+            tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(op_ready(os));
-            if (++ls == LSTAGES) { ls = 0; lphase ^= 1u; }
-            if (++os == OSTAGES) { os = 0; ophase ^= 1u; }
+            if (li == 8 && q == 0 && lane == 0) BLZ_TL_STORE(9 + j, clock64());
+#ifdef BLZ_KERNEL_TIMING
+            t_load += t1 - t0; t_expand += t2 - t1; t_slot += t3 - t2; t_sync += clock64() - t3;
+#endif
         }
+#ifdef BLZ_KERNEL_TIMING
+        if (lane == 0 && q == 0 && j == 0) { BLZ_T_STORE(0, t_load); BLZ_T_STORE(3, t_slot); BLZ_T_STORE(4, t_expand); BLZ_T_STORE(11, t_sync); }
+        if (lane == 0 && q == 0 && j == 1) { BLZ_T_STORE(12, t_load); BLZ_T_STORE(13, t_slot); BLZ_T_STORE(14, t_expand); BLZ_T_STORE(15, t_sync); }
+#endif
     }
 
-    decode_epilogue<MMA_N>(p, base, gen_base, tmem_base, acc_full_bar, abort_flag, n_tile, split_idx, warp, lane, t_entry);
+    // the epilogue warps sleep between polls: the expansion warps need every issue slot
+    decode_epilogue<MMA_N, true, Cfg::NACC>(p, base, gen_base, tmem_base, acc_full_bar, abort_flag, n_tile, split_idx, warp, lane, t_entry);
     decode_teardown(tmem_base, Cfg::TMEM_COLS, abort_flag, warp);
 }
 

@@ -177,7 +177,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (every CTA)
-        if (lane == 0) {
+        if (elect_one()) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             BLZ_T_DECL(t_wait_empty);
@@ -237,7 +237,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         __syncwarp();
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer (leader CTA)
-        if (leader && lane == 0) {
+        if (leader && elect_one()) {
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             bool ok = true;
@@ -311,7 +311,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     } else if (warp == 3) {
         // ------------------- B sharing: pass my part of every B stage on to the other pair's CTA
         if constexpr (SHARE == 2) {
-            if (lane == 0) {
+            if (elect_one()) {
                 int stage = 0; uint32_t phase = 0;
                 bool ok = true;
                 for (int tile = group; ok && tile < total_tiles; tile += num_groups) {

@@ -41,6 +41,19 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     return t;
 }
 
+// ---------------------------------------------------------------- single-thread roles
+// True in exactly one lane of a converged warp (all 32 lanes must execute it).  Roles that issue
+// TMA copies and tcgen05.mma / tcgen05.commit are entered through this, not through `lane == 0`:
+// those instructions take their operands from the uniform datapath, and only after elect.sync
+// does the compiler keep a role's address arithmetic there.  Measured on B200 with 1024
+// back-to-back 128 x 16 x 16 MMAs (A in tensor memory): 20 cycles per instruction behind
+// elect.sync, 94 behind `threadIdx.x == 0`.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
 // ---------------------------------------------------------------- mbarrier
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -102,6 +115,29 @@ __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, c
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
     return mbar_wait_limit(bar, parity, abort_flag, BLZ_WAIT_LIMIT_NS);
+}
+// The same bounded wait for a whole warp (all 32 lanes must call it): lane 0 polls, the others
+// wait at the warp barrier without issuing shared-memory traffic.  Many warps polling one barrier
+// with every lane load the shared-memory pipe that TMA completions and tcgen05.commit arrivals
+// also go through.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait_limit(bar, parity, abort_flag, BLZ_WAIT_LIMIT_NS);
+    return __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
+}
+// The same bounded wait for warps that wait long while other warps of the SM need the issue slots:
+// sleeps between polls (the wake-up may come up to ~0.2 us late).
+__device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+    for (int i = 0;; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(200);
+        if ((i & 63) == 63) {
+            if (*abort_flag != 0) return false;
+            if (global_timer_ns() - t0 > BLZ_WAIT_LIMIT_NS) return false;
+        }
+    }
 }
 
 // ---------------------------------------------------------------------- TMA
@@ -297,6 +333,16 @@ __device__ __forceinline__ uint32_t cvt_e2m1x2_to_f16x2(uint32_t byte) {
         : "=r"(r) : "r"(byte));
     return r;
 }
+// Eight E2M1 values (one 32-bit word, lowest nibble first) -> four packed fp16 pairs.
+__device__ __forceinline__ void cvt_e2m1x8_to_f16x2x4(uint32_t word, uint32_t (&h)[4]) {
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "r"(word));
+}
 // Two E4M3 values (first in the low byte) -> two fp16 values.
 __device__ __forceinline__ uint32_t cvt_e4m3x2_to_f16x2(uint16_t two) {
     uint32_t r;
@@ -328,6 +374,13 @@ __device__ __forceinline__ void umma_f16(uint32_t d, uint64_t a, uint64_t b, uin
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// A from tensor memory (128 lanes x 8 columns of packed 16-bit pairs per K = 16), B from shared memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_f8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
