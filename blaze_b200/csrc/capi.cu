@@ -342,9 +342,6 @@ DecodeChoice decode_choice() {
     return DecodeChoice{reinterpret_cast<const void*>(&decode_stream_kernel<KIND, MMA_N, STAGES>), MMA_N, STAGES, static_cast<int>(Cfg::SMEM_BYTES),
                         Cfg::THREADS, Cfg::MAX_SPLIT, static_cast<int>(Cfg::TMEM_COLS)};
 }
-#ifndef BLZ_W4_L16
-#define BLZ_W4_L16 6
-#endif
 template <bool BF16, int MMA_N, int LSTAGES>
 DecodeChoice decode_choice_w4a16() {
     using Cfg = DecodeW4A16Config<MMA_N, LSTAGES>;
@@ -357,7 +354,7 @@ DecodeChoice decode_choice_for(int M) {
 }
 template <bool BF16>
 DecodeChoice decode_choice_w4a16_for(int M) {
-    return M <= 16 ? decode_choice_w4a16<BF16, 16, BLZ_W4_L16>() : M <= 32 ? decode_choice_w4a16<BF16, 32, 6>() : decode_choice_w4a16<BF16, 64, 3>();
+    return M <= 16 ? decode_choice_w4a16<BF16, 16, 6>() : M <= 32 ? decode_choice_w4a16<BF16, 32, 6>() : decode_choice_w4a16<BF16, 64, 3>();
 }
 DecodeChoice pick_decode_kernel(int mma_kind, bool w4a16, bool bf16, int M) {
     if (w4a16) return bf16 ? decode_choice_w4a16_for<true>(M) : decode_choice_w4a16_for<false>(M);
@@ -692,7 +689,7 @@ blz_status blz_gemm_launch(const blz_gemm_desc* desc, void* C, void* stream) {
     return s;
 }
 
-#if defined(BLZ_KERNEL_TIMING) || defined(BLZ_W4_TIMELINE)
+#ifdef BLZ_KERNEL_TIMING
 // Tuning builds only: copies the per-CTA cycle counters of the last tiled-kernel launch to the host.
 blz_status blz_debug_read_timing(unsigned long long* out, int n_words) {
     BLZ_CUDA(cudaDeviceSynchronize());

@@ -31,18 +31,11 @@ struct EpilogueParams {
 // 3 mma wait-accumulator, 4 mma total, 5 epilogue wait-full, 6 epilogue work, 7 epilogue total, 8 tiles.
 #ifdef BLZ_KERNEL_TIMING
 __device__ unsigned long long g_blz_timing[1024 * 16];
-#define BLZ_TL_STORE(slot, v)
 #define BLZ_T_DECL(name) long long name = 0
 #define BLZ_T_NOW() clock64()
 #define BLZ_T_ADD(acc, t0) acc += clock64() - (t0)
 #define BLZ_T_STORE(slot, v) g_blz_timing[(blockIdx.x & 1023) * 16 + (slot)] = static_cast<unsigned long long>(v)
 #else
-#ifdef BLZ_W4_TIMELINE
-__device__ unsigned long long g_blz_timing[1024 * 16];
-#define BLZ_TL_STORE(slot, v) g_blz_timing[(blockIdx.x & 1023) * 16 + (slot)] = static_cast<unsigned long long>(v)
-#else
-#define BLZ_TL_STORE(slot, v)
-#endif
 #define BLZ_T_DECL(name)
 #define BLZ_T_NOW() 0
 #define BLZ_T_ADD(acc, t0)

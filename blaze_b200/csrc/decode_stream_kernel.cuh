@@ -450,10 +450,7 @@ struct DecodeW4A16Config {
     static constexpr int EXPAND_GROUPS = 4;                  // groups of four warps (one per 32 lanes)
     static constexpr int THREADS = 256 + 128 * EXPAND_GROUPS;
     static constexpr int SUBS = 4;                           // sub-stages (64 K values) per load stage
-#ifndef BLZ_W4_OGROUPS
-#define BLZ_W4_OGROUPS 2
-#endif
-    static constexpr int OGROUPS = BLZ_W4_OGROUPS;           // operand slot groups in tensor memory, one per load stage in flight
+    static constexpr int OGROUPS = 2;                        // operand slot groups in tensor memory, one per load stage in flight
     static constexpr int OSLOTS = OGROUPS * SUBS;
     static constexpr uint32_t X_BYTES = MMA_N * 128;         // one activation tile (64 K values)
     static constexpr uint32_t X_REGION = X_BYTES < 1024 ? 1024 : X_BYTES;
@@ -468,7 +465,7 @@ struct DecodeW4A16Config {
     static constexpr uint32_t OP_COL0 = 64 * NACC;
     static constexpr uint32_t OP_COLS = 32;                  // 64 K values x 16 bit per lane
     static constexpr uint32_t TMEM_COLS = 512;               // the whole tensor memory: one CTA per SM (see SMEM_BYTES)
-    static constexpr uint32_t NUM_BARS = 2 * LSTAGES + OSLOTS + OGROUPS + 1;
+    static constexpr uint32_t NUM_BARS = 2 * LSTAGES + 2 * OGROUPS + 1;
     static constexpr uint32_t BAR_BYTES = 8 * NUM_BARS + 16;
     static constexpr uint32_t SMEM_BYTES = RING_BYTES + BAR_BYTES + 1024;
     static constexpr int MAX_SPLIT = RING_BYTES / (MMA_N * 128 * 4) + 1 < 8 ? RING_BYTES / (MMA_N * 128 * 4) + 1 : 8;
@@ -533,9 +530,9 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const uint32_t bar_base = base + Cfg::RING_BYTES;
     auto load_full = [&](int s) { return bar_base + 8u * s; };
     auto load_empty = [&](int s) { return bar_base + 8u * (LSTAGES + s); };
-    auto op_ready = [&](int s) { return bar_base + 8u * (2 * LSTAGES + s); };
-    auto og_empty = [&](int g) { return bar_base + 8u * (2 * LSTAGES + OSLOTS + g); };
-    const uint32_t acc_full_bar = bar_base + 8u * (2 * LSTAGES + OSLOTS + Cfg::OGROUPS);
+    auto og_ready = [&](int g) { return bar_base + 8u * (2 * LSTAGES + g); };
+    auto og_empty = [&](int g) { return bar_base + 8u * (2 * LSTAGES + Cfg::OGROUPS + g); };
+    const uint32_t acc_full_bar = bar_base + 8u * (2 * LSTAGES + 2 * Cfg::OGROUPS);
     const uint32_t slot_off = Cfg::RING_BYTES + 8u * Cfg::NUM_BARS;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + slot_off);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + slot_off + 4);
@@ -549,8 +546,7 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < LSTAGES; ++s) { mbar_init(load_full(s), 1); mbar_init(load_empty(s), 1); }
-        for (int s = 0; s < OSLOTS; ++s) mbar_init(op_ready(s), 4);
-        for (int g = 0; g < Cfg::OGROUPS; ++g) mbar_init(og_empty(g), 1);
+        for (int g = 0; g < Cfg::OGROUPS; ++g) { mbar_init(og_ready(g), 4 * Cfg::EXPAND_GROUPS); mbar_init(og_empty(g), 1); }
         mbar_init(acc_full_bar, 1);
         *abort_flag = 0;
         fence_mbar_init();
@@ -574,14 +570,7 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             const uint64_t pol_stream = l2_policy_evict_first();
             const uint64_t pol_keep = l2_policy_evict_last();
             auto load_weights = [&](int ks, int stage) {
-#ifdef BLZ_W4_NO_W
-                mbar_arrive_expect_tx(load_full(stage), Cfg::TX_BYTES - Cfg::PK_BYTES);
-                if (ks < 0)
-#elif defined(BLZ_W4_ONE_X)
-                mbar_arrive_expect_tx(load_full(stage), Cfg::TX_BYTES - 3 * Cfg::X_BYTES);
-#else
                 mbar_arrive_expect_tx(load_full(stage), Cfg::TX_BYTES);
-#endif
                 tma_load_2d_hint(base + Cfg::PK_OFF + stage * Cfg::PK_BYTES, &tm_w, ks * 128, n_tile * 128, load_full(stage), pol_stream);
                 bulk_load_1d(base + Cfg::SF_OFF + stage * Cfg::SF_BYTES, p.sfw + (static_cast<size_t>(n_tile) * p.sf_katoms + static_cast<size_t>(ks) * SUBS) * 512,
                              Cfg::SF_BYTES, load_full(stage));
@@ -597,14 +586,9 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                         atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_PRODUCER); *abort_flag = 1; break;
                     }
                     load_weights(ks, stage);
-                    if (ks - ks_begin == 8) BLZ_TL_STORE(0, clock64());
                 }
-#ifdef BLZ_W4_ONE_X
-                for (int j = 0; j < 1; ++j)
-#else
 #pragma unroll
                 for (int j = 0; j < SUBS; ++j)
-#endif
                     tma_load_2d_hint(base + Cfg::X_OFF + (stage * SUBS + j) * Cfg::X_REGION, &tm_x, (ks * SUBS + j) * 128, 0, load_full(stage), pol_keep);
                 if (++stage == LSTAGES) { stage = 0; phase ^= 1u; }
             }
@@ -629,33 +613,28 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                     if (l0 + ul >= n_load) break;
                     const int ls = ul % LSTAGES, og = ul % OGROUPS;
                     const uint32_t ophase = static_cast<uint32_t>(ul / OGROUPS) & 1u;
+                    // One wait per load stage: polling a barrier costs ~200 cycles even when its phase is
+                    // long complete (measured), as much as issuing eight of these MMAs.
+                    // "expanded" implies "landed": the expansion warps waited for the stage's loads.
+                    [[maybe_unused]] const long long tr = BLZ_T_NOW();
+                    if (!mbar_wait(og_ready(og), ophase, abort_flag)) {
+                        atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
+                    }
+                    BLZ_T_ADD(t_ready, tr);
+                    tc_fence_after_sync();
 #pragma unroll
                     for (int j = 0; j < SUBS; ++j) {
                         const int os = og * SUBS + j;
-                        [[maybe_unused]] const long long tr = BLZ_T_NOW();
-                        // "expanded" implies "landed": the expansion warps waited for the stage's loads
-                        if (!mbar_wait(op_ready(os), ophase, abort_flag)) {
-                            atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
-                        }
-                        BLZ_T_ADD(t_ready, tr);
-                        if (l0 + ul == 8 && j == 0) BLZ_TL_STORE(13, clock64());
-                        if (l0 + ul == 8 && j == 3) BLZ_TL_STORE(14, clock64());
-                        tc_fence_after_sync();
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
                             const uint32_t accumulate = (ul | j) != 0 ? 1u : (l0 != 0 ? 1u : 0u);
                             // A: 16 K values = 8 columns of this slot; B: 32 bytes further into the activation tile
-#ifndef BLZ_W4_SKIP_MMA
                             umma_f16_ts(tmem_base + 64 * k, a0 + os * Cfg::OP_COLS + k * 8, dx0 + (((ls * SUBS + j) * Cfg::X_REGION + k * 32) >> 4), p.idesc, accumulate);
-#else
-                            if (k == 0 && j == 0) umma_f16_ts(tmem_base, a0 + os * Cfg::OP_COLS + k * 8, dx0 + (((ls * SUBS + j) * Cfg::X_REGION + k * 32) >> 4), p.idesc, accumulate);
-#endif
                         }
                     }
                     if (!ok) break;
                     tc_commit(og_empty(og));        // the four operand slots of this load stage
                     tc_commit(load_empty(ls));      // its packed bytes were expanded before the MMAs, its activation tiles are read by them
-                    if (l0 + ul == 8) BLZ_TL_STORE(15, clock64());
                 }
             }
             if (ok) tc_commit(acc_full_bar);
@@ -676,15 +655,9 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                 atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; break;
             }
             [[maybe_unused]] const long long t1 = BLZ_T_NOW();
-            if (li == 8 && q == 0 && lane == 0) BLZ_TL_STORE(1 + j, clock64());
             uint32_t r[32];
             const uint32_t sf4 = *reinterpret_cast<const uint32_t*>(gen_base + Cfg::SF_OFF + ls * Cfg::SF_BYTES + j * 512 + lane * 16 + q * 4);
-#ifndef BLZ_W4_SKIP_EXPAND
             expand_w4_row<BF16>(gen_base + Cfg::PK_OFF + ls * Cfg::PK_BYTES + row * 128, row, j, sf4, r);
-#else
-#pragma unroll
-            for (int z = 0; z < 32; ++z) r[z] = sf4 + z;
-#endif
             [[maybe_unused]] const long long t2 = BLZ_T_NOW();
             // the slot group is free once the MMAs of the load stage that used it last have completed
             if (!mbar_wait_warp(og_empty(og), ophase ^ 1u, abort_flag)) {
@@ -692,13 +665,11 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             }
             tc_fence_after_sync();
             [[maybe_unused]] const long long t3 = BLZ_T_NOW();
-            if (li == 8 && q == 0 && lane == 0) BLZ_TL_STORE(5 + j, clock64());
             tmem_st32(t_lane + os * Cfg::OP_COLS, r);
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(op_ready(os));
-            if (li == 8 && q == 0 && lane == 0) BLZ_TL_STORE(9 + j, clock64());
+            if (lane == 0) mbar_arrive(og_ready(og));
 #ifdef BLZ_KERNEL_TIMING
             t_load += t1 - t0; t_expand += t2 - t1; t_slot += t3 - t2; t_sync += clock64() - t3;
 #endif

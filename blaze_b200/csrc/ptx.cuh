@@ -54,6 +54,10 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+#ifndef BLZ_POLL_SLEEP_NS
+#define BLZ_POLL_SLEEP_NS 32
+#endif
+
 // ---------------------------------------------------------------- mbarrier
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -122,7 +126,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const v
 // also go through.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
     bool ok = true;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait_limit(bar, parity, abort_flag, BLZ_WAIT_LIMIT_NS);
+    if ((threadIdx.x & 31) == 0) {
+        // a failed poll backs off: sixteen pollers re-issuing mbarrier.try_wait back to back were
+        // measured to delay every other barrier operation of the CTA by ~200 cycles
+        const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+        for (int i = 0; !mbar_try_wait(bar, parity); ++i) {
+            __nanosleep(BLZ_POLL_SLEEP_NS);
+            if ((i & 255) == 255 && (*abort_flag != 0 || global_timer_ns() - t0 > BLZ_WAIT_LIMIT_NS)) { ok = false; break; }
+        }
+    }
     return __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
 }
 // The same bounded wait for warps that wait long while other warps of the SM need the issue slots:
