@@ -350,10 +350,18 @@ DecodeChoice decode_choice_w4a16() {
 }
 template <int KIND>
 DecodeChoice decode_choice_for(int M) {
+    if constexpr (KIND != MMA_NVF4) { if (M > 64) return decode_choice<KIND, 128, 5>(); }
     return M <= 16 ? decode_choice<KIND, 16, 5>() : M <= 32 ? decode_choice<KIND, 32, 4>() : decode_choice<KIND, 64, 3>();
+}
+template <bool BF16, int WSTAGES, int XSLOTS>
+DecodeChoice decode_choice_w4a16_wide() {
+    using Cfg = DecodeW4A16WideConfig<WSTAGES, XSLOTS>;
+    return DecodeChoice{reinterpret_cast<const void*>(&decode_w4a16_wide_kernel<BF16, WSTAGES, XSLOTS>), Cfg::MMA_N, WSTAGES, static_cast<int>(Cfg::SMEM_BYTES),
+                        Cfg::THREADS, Cfg::MAX_SPLIT, static_cast<int>(Cfg::TMEM_COLS)};
 }
 template <bool BF16>
 DecodeChoice decode_choice_w4a16_for(int M) {
+    if (M > 64) return decode_choice_w4a16_wide<BF16, 3, 4>();
     return M <= 16 ? decode_choice_w4a16<BF16, 16, 6>() : M <= 32 ? decode_choice_w4a16<BF16, 32, 6>() : decode_choice_w4a16<BF16, 64, 3>();
 }
 DecodeChoice pick_decode_kernel(int mma_kind, bool w4a16, bool bf16, int M) {
@@ -460,9 +468,9 @@ blz_status launch_cluster(blz_gemm_plan* p, int n_dst, void* const* dst, int64_t
     if (p->own_w16) {
         const int64_t blocks16 = static_cast<int64_t>(d.N) * (d.K / 16);
         if (d.kind == BLZ_GEMM_W4A16_F16)
-            dequant_nvfp4_kernel<__half><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<__half*>(p->own_w16));
+            dequant_nvfp4_kernel<false><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<uint16_t*>(p->own_w16));
         else
-            dequant_nvfp4_kernel<__nv_bfloat16><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<__nv_bfloat16*>(p->own_w16));
+            dequant_nvfp4_kernel<true><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<uint16_t*>(p->own_w16));
         BLZ_CUDA(cudaGetLastError());
     }
     const int eb = elem_bytes_out(d.out_dtype);
@@ -565,8 +573,13 @@ blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_p
     if ((s = prepare_b(p))) return fail(s);
     if ((s = prepare_a_scales(p))) return fail(s);
 
-    // Skinny activations stream the weights once through the decode kernels (every kind).
-    const bool want_decode = desc->variant == BLZ_VARIANT_DECODE || (desc->variant == BLZ_VARIANT_AUTO && desc->M <= 64);
+    // Skinny activations stream the weights once through the decode kernels (every kind).  Up to 64
+    // rows automatically; W4A16 up to 128 (its alternative is a 16-bit copy of the weights per call).
+    // The 128-row forms of the FP8 and 16-bit kernels exist (explicit variant) but lose to the tiled
+    // kernel: both re-read the activations once per 128 weight rows and are bound by L2 -> SM traffic.
+    const int decode_max_m = desc->kind == BLZ_GEMM_NVFP4 ? 64 : 128;
+    const int decode_auto_m = w4a16 ? 128 : 64;
+    const bool want_decode = desc->variant == BLZ_VARIANT_DECODE || (desc->variant == BLZ_VARIANT_AUTO && desc->M <= decode_auto_m);
     if (w4a16 && !want_decode) {
         // The tiled kernels consume 16-bit weights: every execute expands the packed weights into
         // this buffer (q * block scale, exact in 16 bits); the fp32 tensor scale goes into alpha.
@@ -575,7 +588,7 @@ blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_p
     }
 
     if (want_decode) {
-        if (desc->M > 64) return fail(BLZ_ERR_UNSUPPORTED);
+        if (desc->M > decode_max_m) return fail(BLZ_ERR_UNSUPPORTED);
         p->variant = BLZ_VARIANT_DECODE;
         if ((s = decode_setup(p))) return fail(s);
     } else {

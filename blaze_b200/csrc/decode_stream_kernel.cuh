@@ -54,6 +54,60 @@ __device__ __forceinline__ void st_shared_cluster_f32(uint32_t addr, uint32_t ct
         ::"r"(addr), "r"(cta), "f"(v) : "memory");
 }
 
+// The 128 epilogue threads (threadIdx 128..255) write the staged fp32 sums stag[m][128] to C:
+// alpha, bias / SiLU / residual, narrowing, 16-byte row stores.  Compact on purpose: it runs once.
+__device__ __forceinline__ void decode_store_rows(const float* stag, int p_M, int p_N, int n_tile, float e_alpha, int e_mode, int e_out, int e_vec,
+                                                  long long e_ldc, long long e_ldr, void* e_C, const void* e_bias, const void* e_res) {
+                const int tid = threadIdx.x - 128;
+                const int esize = e_out == OUT_F32 ? 4 : 2;
+                // one item = 8 consecutive columns of one row: 128 / 8 = 16 items per row
+    #pragma unroll 1
+                for (int c = tid; c < p_M * 16; c += 128) {
+                    const int m = c >> 4, j = c & 15;
+                    const int col = n_tile * 128 + j * 8;
+                    if (col >= p_N) continue;
+                    const float4 lo = *reinterpret_cast<const float4*>(stag + m * 128 + j * 8);
+                    const float4 hi = *reinterpret_cast<const float4*>(stag + m * 128 + j * 8 + 4);
+                    float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    #pragma unroll
+                    for (int t = 0; t < 8; ++t) v[t] *= e_alpha;
+                    if (e_mode != EPI_NONE) {
+    #pragma unroll 1
+                        for (int t = 0; t < 8; ++t) {
+                            const int n = col + t;
+                            if (n >= p_N) break;
+                            if ((e_mode == EPI_BIAS || e_mode == EPI_BIAS_SILU) && e_bias != nullptr)
+                                v[t] += e_out == OUT_BF16 ? load_out_elem<OUT_BF16>(e_bias, n) : e_out == OUT_F16 ? load_out_elem<OUT_F16>(e_bias, n) : load_out_elem<OUT_F32>(e_bias, n);
+                            if (e_mode == EPI_SILU || e_mode == EPI_BIAS_SILU) v[t] = silu_f32(v[t]);
+                            if (e_mode == EPI_RESIDUAL && e_res != nullptr) {
+                                const long long roff = static_cast<long long>(m) * e_ldr + n;
+                                v[t] += e_out == OUT_BF16 ? load_out_elem<OUT_BF16>(e_res, roff) : e_out == OUT_F16 ? load_out_elem<OUT_F16>(e_res, roff) : load_out_elem<OUT_F32>(e_res, roff);
+                            }
+                        }
+                    }
+                    uint8_t* dst = reinterpret_cast<uint8_t*>(e_C) + (static_cast<long long>(m) * e_ldc + col) * esize;
+                    const bool whole = e_vec && col + 8 <= p_N;
+                    if (e_out == OUT_F32) {
+                        if (whole) {
+                            reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
+                            reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+                        } else {
+                            for (int t = 0; t < 8 && col + t < p_N; ++t) reinterpret_cast<float*>(dst)[t] = v[t];
+                        }
+                    } else {
+                        uint32_t w[4];
+    #pragma unroll
+                        for (int t = 0; t < 4; ++t) w[t] = pack2_out(e_out, v[2 * t], v[2 * t + 1]);
+                        if (whole) {
+                            *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                        } else {
+                            for (int t = 0; t < 8 && col + t < p_N; ++t)
+                                reinterpret_cast<uint16_t*>(dst)[t] = static_cast<uint16_t>(w[t >> 1] >> (16 * (t & 1)));
+                        }
+                    }
+                }
+}
+
 // Shared by both kernels, called by every thread of the CTA once its main-loop role is done.
 // Warps 4-7 take the fp32 sums out of tensor memory (columns [0, MMA_N), lane = weight row); with
 // a K split every thread of every CTA of the cluster meets at two cluster barriers around the
@@ -152,60 +206,83 @@ __device__ __forceinline__ void decode_epilogue(const DecodeStreamParams& p, uin
         if (threadIdx.x == 128) BLZ_T_STORE(6, clock64() - t_entry);
 #endif
         if (epi_ok) {
-            const int tid = threadIdx.x - 128;
-            const int esize = e_out == OUT_F32 ? 4 : 2;
-            // one item = 8 consecutive columns of one row: 128 / 8 = 16 items per row
-#pragma unroll 1
-            for (int c = tid; c < p_M * 16; c += 128) {
-                const int m = c >> 4, j = c & 15;
-                const int col = n_tile * 128 + j * 8;
-                if (col >= p_N) continue;
-                const float4 lo = *reinterpret_cast<const float4*>(stag + m * 128 + j * 8);
-                const float4 hi = *reinterpret_cast<const float4*>(stag + m * 128 + j * 8 + 4);
-                float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-#pragma unroll
-                for (int t = 0; t < 8; ++t) v[t] *= e_alpha;
-                if (e_mode != EPI_NONE) {
-#pragma unroll 1
-                    for (int t = 0; t < 8; ++t) {
-                        const int n = col + t;
-                        if (n >= p_N) break;
-                        if ((e_mode == EPI_BIAS || e_mode == EPI_BIAS_SILU) && e_bias != nullptr)
-                            v[t] += e_out == OUT_BF16 ? load_out_elem<OUT_BF16>(e_bias, n) : e_out == OUT_F16 ? load_out_elem<OUT_F16>(e_bias, n) : load_out_elem<OUT_F32>(e_bias, n);
-                        if (e_mode == EPI_SILU || e_mode == EPI_BIAS_SILU) v[t] = silu_f32(v[t]);
-                        if (e_mode == EPI_RESIDUAL && e_res != nullptr) {
-                            const long long roff = static_cast<long long>(m) * e_ldr + n;
-                            v[t] += e_out == OUT_BF16 ? load_out_elem<OUT_BF16>(e_res, roff) : e_out == OUT_F16 ? load_out_elem<OUT_F16>(e_res, roff) : load_out_elem<OUT_F32>(e_res, roff);
-                        }
-                    }
-                }
-                uint8_t* dst = reinterpret_cast<uint8_t*>(e_C) + (static_cast<long long>(m) * e_ldc + col) * esize;
-                const bool whole = e_vec && col + 8 <= p_N;
-                if (e_out == OUT_F32) {
-                    if (whole) {
-                        reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
-                        reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
-                    } else {
-                        for (int t = 0; t < 8 && col + t < p_N; ++t) reinterpret_cast<float*>(dst)[t] = v[t];
-                    }
-                } else {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int t = 0; t < 4; ++t) w[t] = pack2_out(e_out, v[2 * t], v[2 * t + 1]);
-                    if (whole) {
-                        *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
-                    } else {
-                        for (int t = 0; t < 8 && col + t < p_N; ++t)
-                            reinterpret_cast<uint16_t*>(dst)[t] = static_cast<uint16_t>(w[t >> 1] >> (16 * (t & 1)));
-                    }
-                }
-            }
+            decode_store_rows(stag, p_M, p_N, n_tile, e_alpha, e_mode, e_out, e_vec, e_ldc, e_ldr, e_C, e_bias, e_res);
         }
     }
 
 #ifdef BLZ_KERNEL_TIMING
     if (threadIdx.x == 128) BLZ_T_STORE(7, clock64() - t_entry);
 #endif
+}
+
+// The same for wide activation tiles (MMA_N = 128): the sums do not fit a thread's registers, so
+// everything goes in chunks of 32 columns (= activation rows).  The NACC accumulators sit MMA_N
+// columns apart.  The leader's staging buffer aliases partial-sum slot 0: every element of that
+// slot is read (as a partial sum) and then overwritten (as the total) by the same thread.
+template <int MMA_N, bool SLEEPY, int NACC>
+__device__ __forceinline__ void decode_epilogue_wide(const DecodeStreamParams& p, uint32_t base, uint8_t* gen_base, uint32_t tmem_base,
+                                                     uint32_t acc_full_bar, volatile int* abort_flag, int n_tile, int split_idx, int warp, int lane) {
+    bool epi_ok = true;
+    const bool is_epi = (warp >= 4 && warp < 8);
+    const int q = warp & 3;
+    const int n_local = q * 32 + lane;
+    const float e_alpha = p.epi.alpha;
+    const int e_mode = p.epi.mode, e_out = p.epi.out_type, e_vec = p.epi.vec_ok, p_M = p.M, p_N = p.N, p_split = p.split;
+    const long long e_ldc = p.epi.ldc, e_ldr = p.epi.ldr;
+    void* const e_C = p.epi.C;
+    const void* const e_bias = p.epi.bias;
+    const void* const e_res = p.epi.residual;
+    if (is_epi) {
+        epi_ok = SLEEPY ? mbar_wait_sleepy(acc_full_bar, 0u, abort_flag) : mbar_wait(acc_full_bar, 0u, abort_flag);
+        if (!epi_ok) { atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_EPILOGUE); *abort_flag = 1; }
+        tc_fence_after_sync();
+    }
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    auto load_chunk = [&](int c, float (&v)[32]) {
+#pragma unroll
+        for (int a = 0; a < NACC; ++a) {
+            uint32_t r[32];
+            tmem_ld32(t_row + a * MMA_N + c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int t = 0; t < 32; ++t) v[t] = a == 0 ? __uint_as_float(r[t]) : v[t] + __uint_as_float(r[t]);
+        }
+    };
+    if (p_split > 1) {
+        cluster_sync_all();                 // every CTA of the tile is past its main loop: the leader's buffers are free
+        if (is_epi && split_idx != 0 && epi_ok) {
+#pragma unroll 1
+            for (int c = 0; c < MMA_N && c < p_M; c += 32) {
+                float v[32];
+                load_chunk(c, v);
+                const uint32_t dst = base + (static_cast<uint32_t>(split_idx - 1) * MMA_N * 128 + c * 128 + n_local) * 4;
+#pragma unroll
+                for (int t = 0; t < 32; ++t)
+                    if (c + t < p_M) st_shared_cluster_f32(dst + t * 512, 0, v[t]);
+            }
+        }
+        cluster_sync_all();                 // partial sums have landed in the leader
+    }
+    if (is_epi && split_idx == 0) {
+        griddep_wait();                      // bias / residual may come from the predecessor; C may be read by it
+        float* stag = reinterpret_cast<float*>(gen_base);
+        if (epi_ok) {
+#pragma unroll 1
+            for (int c = 0; c < MMA_N && c < p_M; c += 32) {
+                float v[32];
+                load_chunk(c, v);
+#pragma unroll
+                for (int t = 0; t < 32; ++t) {
+                    float sum = v[t];
+                    for (int sp = 1; sp < p_split; ++sp) sum += stag[(sp - 1) * MMA_N * 128 + (c + t) * 128 + n_local];
+                    stag[(c + t) * 128 + n_local] = sum;
+                }
+            }
+        }
+        tc_fence_before_sync();
+        named_barrier_sync(1, 128);
+        if (epi_ok) decode_store_rows(stag, p_M, p_N, n_tile, e_alpha, e_mode, e_out, e_vec, e_ldc, e_ldr, e_C, e_bias, e_res);
+    }
 }
 
 // Every thread of the CTA: after a give-up let copies in flight land, then free tensor memory.
@@ -237,15 +314,17 @@ struct DecodeStreamConfig {
     static constexpr uint32_t STAGE_BYTES = W_BYTES + X_REGION + 2 * SF_BYTES;
     static constexpr uint32_t TX_BYTES = W_BYTES + X_BYTES + 2 * SF_BYTES;
     static constexpr uint32_t SF_COLS = 32;                 // per stage: weights 16, activations 16
-    static constexpr uint32_t SF_BASE = 64;                 // accumulator in columns [0, MMA_N)
-    static constexpr uint32_t TMEM_COLS = 256;
+    static constexpr uint32_t SF_BASE = MMA_N <= 64 ? 64 : 128;   // accumulator in columns [0, MMA_N)
+    static constexpr uint32_t TMEM_COLS = HAS_SF ? tmem_cols_pow2(SF_BASE + STAGES * SF_COLS) : (MMA_N <= 64 ? 64 : 128);
     static constexpr uint32_t NUM_BARS = 3 * STAGES + 1;
     static constexpr uint32_t BAR_BYTES = 8 * NUM_BARS + 16;
     static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
     static constexpr int MAX_SPLIT = (STAGES * STAGE_BYTES) / (MMA_N * 128 * 4) + 1 < 8 ? (STAGES * STAGE_BYTES) / (MMA_N * 128 * 4) + 1 : 8;
-    static_assert(MMA_N % 16 == 0 && MMA_N >= 16 && MMA_N <= 64, "activation rows per instruction");
+    static_assert(MMA_N % 16 == 0 && MMA_N >= 16 && MMA_N <= 128, "activation rows per instruction");
     static_assert(!HAS_SF || SF_BASE + STAGES * SF_COLS <= TMEM_COLS, "scale-factor columns exceed the allocation");
-    static_assert(SMEM_BYTES <= 115000, "two CTAs must fit one SM");
+    static_assert(MMA_N > 32 || SMEM_BYTES <= 115000, "two CTAs must fit one SM");
+    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared-memory limit");
+    static_assert(TMEM_COLS <= 256 || SMEM_BYTES > 116 * 1024, "two CTAs on one SM would wait for each other's tensor memory");
     static_assert(MMA_N * 128 * 4 <= STAGES * STAGE_BYTES, "fp32 output staging must fit the stage buffers");
 };
 
@@ -407,7 +486,8 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
         }
     }
 
-    decode_epilogue<MMA_N>(p, base, gen_base, tmem_base, acc_full_bar, abort_flag, n_tile, split_idx, warp, lane, t_entry);
+    if constexpr (MMA_N > 64) decode_epilogue_wide<MMA_N, false, 1>(p, base, gen_base, tmem_base, acc_full_bar, abort_flag, n_tile, split_idx, warp, lane);
+    else decode_epilogue<MMA_N>(p, base, gen_base, tmem_base, acc_full_bar, abort_flag, n_tile, split_idx, warp, lane, t_entry);
     decode_teardown(tmem_base, Cfg::TMEM_COLS, abort_flag, warp);
 }
 
@@ -682,6 +762,196 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
     // the epilogue warps sleep between polls: the expansion warps need every issue slot
     decode_epilogue<MMA_N, true, Cfg::NACC>(p, base, gen_base, tmem_base, acc_full_bar, abort_flag, n_tile, split_idx, warp, lane, t_entry);
+    decode_teardown(tmem_base, Cfg::TMEM_COLS, abort_flag, warp);
+}
+
+// ------------------------------------------------------------------------------------------------
+// The same kernel for 64 < M <= 128: one activation tile of 128 rows (the instruction's N).  The
+// activation tiles are now the bigger part of the traffic into shared memory (16 KB per 64 K values,
+// from L2), so they get a ring of their own, two sub-stages per slot, behind their own barriers;
+// the packed weights keep their load stages.  Two accumulators of 128 columns (even / odd K = 16
+// slice), eight operand slots: all 512 tensor-memory columns.
+
+template <int WSTAGES, int XSLOTS>
+struct DecodeW4A16WideConfig {
+    static constexpr int MMA_N = 128;
+    static constexpr int EXPAND_GROUPS = 4;
+    static constexpr int THREADS = 256 + 128 * EXPAND_GROUPS;
+    static constexpr int SUBS = 4;
+    static constexpr int OGROUPS = 2;
+    static constexpr int NACC = 2;
+    static constexpr uint32_t X_TILE = MMA_N * 128;          // one activation tile (64 K values)
+    static constexpr uint32_t X_SLOT = 2 * X_TILE;           // two sub-stages per slot
+    static constexpr uint32_t PK_BYTES = 128 * 128;
+    static constexpr uint32_t SF_BYTES = SUBS * 512;
+    static constexpr uint32_t W_TX = PK_BYTES + SF_BYTES;
+    static constexpr uint32_t PK_OFF = 0;
+    static constexpr uint32_t X_OFF = PK_OFF + WSTAGES * PK_BYTES;
+    static constexpr uint32_t SF_OFF = X_OFF + XSLOTS * X_SLOT;
+    static constexpr uint32_t RING_BYTES = SF_OFF + WSTAGES * SF_BYTES;
+    static constexpr uint32_t OP_COL0 = NACC * MMA_N;
+    static constexpr uint32_t OP_COLS = 32;
+    static constexpr uint32_t TMEM_COLS = 512;
+    static constexpr uint32_t NUM_BARS = 2 * WSTAGES + 2 * XSLOTS + 2 * OGROUPS + 1;
+    static constexpr uint32_t BAR_BYTES = 8 * NUM_BARS + 16;
+    static constexpr uint32_t SMEM_BYTES = RING_BYTES + BAR_BYTES + 1024;
+    // partial sums of the other splits: (split - 1) slots of MMA_N x 128 fp32 (slot 0 doubles as the staging buffer)
+    static constexpr int MAX_SPLIT = RING_BYTES / (MMA_N * 128 * 4) + 1 < 8 ? RING_BYTES / (MMA_N * 128 * 4) + 1 : 8;
+    static_assert(OP_COL0 + OGROUPS * SUBS * OP_COLS <= TMEM_COLS, "operand slots exceed tensor memory");
+    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared-memory limit");
+    static_assert(SMEM_BYTES > 116 * 1024, "two CTAs on one SM would wait for each other's tensor memory");
+    static_assert(MMA_N * 128 * 4 <= RING_BYTES, "fp32 output staging must fit the rings");
+};
+
+template <bool BF16, int WSTAGES, int XSLOTS>
+__global__ void __launch_bounds__((DecodeW4A16WideConfig<WSTAGES, XSLOTS>::THREADS), 1)
+decode_w4a16_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const DecodeStreamParams p) {
+    using Cfg = DecodeW4A16WideConfig<WSTAGES, XSLOTS>;
+    constexpr int SUBS = Cfg::SUBS, OGROUPS = Cfg::OGROUPS, MMA_N = Cfg::MMA_N;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (base - raw);
+
+    const uint32_t bar_base = base + Cfg::RING_BYTES;
+    auto w_full = [&](int s) { return bar_base + 8u * s; };
+    auto w_empty = [&](int s) { return bar_base + 8u * (WSTAGES + s); };
+    auto x_full = [&](int s) { return bar_base + 8u * (2 * WSTAGES + s); };
+    auto x_empty = [&](int s) { return bar_base + 8u * (2 * WSTAGES + XSLOTS + s); };
+    auto og_ready = [&](int g) { return bar_base + 8u * (2 * WSTAGES + 2 * XSLOTS + g); };
+    auto og_empty = [&](int g) { return bar_base + 8u * (2 * WSTAGES + 2 * XSLOTS + OGROUPS + g); };
+    const uint32_t acc_full_bar = bar_base + 8u * (2 * WSTAGES + 2 * XSLOTS + 2 * OGROUPS);
+    const uint32_t slot_off = Cfg::RING_BYTES + 8u * Cfg::NUM_BARS;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + slot_off);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + slot_off + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tile = blockIdx.x / p.split;
+    const int split_idx = blockIdx.x % p.split;
+    const int ks_begin = split_idx * p.stages_per_split;
+    const int ks_end = min(p.k_stages_total, ks_begin + p.stages_per_split);
+    const int n_load = ks_end - ks_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < WSTAGES; ++s) { mbar_init(w_full(s), 1); mbar_init(w_empty(s), 1); }
+        for (int s = 0; s < XSLOTS; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 1); }
+        for (int g = 0; g < OGROUPS; ++g) { mbar_init(og_ready(g), 4 * Cfg::EXPAND_GROUPS); mbar_init(og_empty(g), 1); }
+        mbar_init(acc_full_bar, 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 2) {
+        tmem_alloc(base + slot_off, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    if (warp == 0 && lane == 0) {
+        prefetch_tensormap(&tm_w);
+        prefetch_tensormap(&tm_x);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    griddep_launch_dependents();
+
+    if (warp == 0) {
+        if (elect_one()) {
+            const uint64_t pol_stream = l2_policy_evict_first();
+            const uint64_t pol_keep = l2_policy_evict_last();
+            auto load_weights = [&](int ks, int stage) {
+                mbar_arrive_expect_tx(w_full(stage), Cfg::W_TX);
+                tma_load_2d_hint(base + Cfg::PK_OFF + stage * Cfg::PK_BYTES, &tm_w, ks * 128, n_tile * 128, w_full(stage), pol_stream);
+                bulk_load_1d(base + Cfg::SF_OFF + stage * Cfg::SF_BYTES, p.sfw + (static_cast<size_t>(n_tile) * p.sf_katoms + static_cast<size_t>(ks) * SUBS) * 512,
+                             Cfg::SF_BYTES, w_full(stage));
+            };
+            const int n_pre = min(n_load, WSTAGES);
+            for (int i = 0; i < n_pre; ++i) load_weights(ks_begin + i, i);
+            griddep_wait();
+            bool ok = true;
+            int xi = 0;
+            for (int li = 0; ok && li < n_load; ++li) {
+                const int ws = li % WSTAGES, ks = ks_begin + li;
+                if (li >= WSTAGES) {
+                    if (!mbar_wait(w_empty(ws), (static_cast<uint32_t>(li / WSTAGES) & 1u) ^ 1u, abort_flag)) {
+                        atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_PRODUCER); *abort_flag = 1; break;
+                    }
+                    load_weights(ks, ws);
+                }
+                for (int h = 0; h < 2; ++h, ++xi) {
+                    const int xs = xi % XSLOTS;
+                    if (xi >= XSLOTS && !mbar_wait(x_empty(xs), (static_cast<uint32_t>(xi / XSLOTS) & 1u) ^ 1u, abort_flag)) {
+                        atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_PRODUCER); *abort_flag = 1; ok = false; break;
+                    }
+                    mbar_arrive_expect_tx(x_full(xs), Cfg::X_SLOT);
+                    tma_load_2d_hint(base + Cfg::X_OFF + xs * Cfg::X_SLOT, &tm_x, (ks * SUBS + 2 * h) * 128, 0, x_full(xs), pol_keep);
+                    tma_load_2d_hint(base + Cfg::X_OFF + xs * Cfg::X_SLOT + Cfg::X_TILE, &tm_x, (ks * SUBS + 2 * h + 1) * 128, 0, x_full(xs), pol_keep);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (elect_one()) {
+            const uint64_t dx0 = make_desc_k_sw128(base + Cfg::X_OFF);
+            const uint32_t a0 = tmem_base + Cfg::OP_COL0;
+            bool ok = true;
+            int xi = 0;
+            for (int li = 0; ok && li < n_load; ++li) {
+                const int ws = li % WSTAGES, og = li % OGROUPS;
+                // "expanded" implies "landed": the expansion warps waited for the stage's weight loads
+                if (!mbar_wait(og_ready(og), static_cast<uint32_t>(li / OGROUPS) & 1u, abort_flag)) {
+                    atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
+                }
+                for (int h = 0; h < 2; ++h, ++xi) {
+                    const int xs = xi % XSLOTS;
+                    if (!mbar_wait(x_full(xs), static_cast<uint32_t>(xi / XSLOTS) & 1u, abort_flag)) {
+                        atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
+                    }
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int jj = 0; jj < 2; ++jj) {
+                        const int os = og * SUBS + 2 * h + jj;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            // even and odd K = 16 slices go to separate accumulators
+                            const uint32_t accumulate = (li | h | jj | (k >> 1)) != 0 ? 1u : 0u;
+                            umma_f16_ts(tmem_base + (k & 1) * MMA_N, a0 + os * Cfg::OP_COLS + k * 8,
+                                        dx0 + ((xs * Cfg::X_SLOT + jj * Cfg::X_TILE + k * 32) >> 4), p.idesc, accumulate);
+                        }
+                    }
+                    tc_commit(x_empty(xs));
+                }
+                if (!ok) break;
+                tc_commit(og_empty(og));
+                tc_commit(w_empty(ws));
+            }
+            if (ok) tc_commit(acc_full_bar);
+        }
+        __syncwarp();
+    } else if (warp >= 8) {
+        const int j = (warp - 8) >> 2, q = warp & 3;
+        const int row = q * 32 + lane;
+        const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::OP_COL0;
+        for (int li = 0; li < n_load; ++li) {
+            const int ws = li % WSTAGES, og = li % OGROUPS, os = og * SUBS + j;
+            if (!mbar_wait_warp(w_full(ws), static_cast<uint32_t>(li / WSTAGES) & 1u, abort_flag)) {
+                atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; break;
+            }
+            uint32_t r[32];
+            const uint32_t sf4 = *reinterpret_cast<const uint32_t*>(gen_base + Cfg::SF_OFF + ws * Cfg::SF_BYTES + j * 512 + lane * 16 + q * 4);
+            expand_w4_row<BF16>(gen_base + Cfg::PK_OFF + ws * Cfg::PK_BYTES + row * 128, row, j, sf4, r);
+            if (!mbar_wait_warp(og_empty(og), (static_cast<uint32_t>(li / OGROUPS) & 1u) ^ 1u, abort_flag)) {
+                atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; break;
+            }
+            tc_fence_after_sync();
+            tmem_st32(t_lane + os * Cfg::OP_COLS, r);
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(og_ready(og));
+        }
+    }
+
+    decode_epilogue_wide<MMA_N, true, Cfg::NACC>(p, base, gen_base, tmem_base, acc_full_bar, abort_flag, n_tile, split_idx, warp, lane);
     decode_teardown(tmem_base, Cfg::TMEM_COLS, abort_flag, warp);
 }
 

@@ -151,26 +151,37 @@ __global__ void quantize_nvfp4_kernel(const T* __restrict__ x, long long rows, l
 
 // ---- NVFP4 weights -> 16-bit values q*sf (exact: 6 significant bits), global scale left out.
 //      data [rows, K/2], sf read through the tiled layout; out [rows, K].
-template <typename T>
+//      One thread per 16-value block: 8 packed bytes in, 32 bytes out, hardware conversions
+//      (fp16: cvt + packed multiply; bf16: the fp16 pattern shifted by three is the value x 2^-112,
+//      multiplied by bf16(scale x 2^112)).
+template <bool BF16>
 __global__ void dequant_nvfp4_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ sf_tiled, long long katoms,
-                                     long long rows, long long K, T* __restrict__ out) {
+                                     long long rows, long long K, uint16_t* __restrict__ out) {
     const long long kb = K / 16, total = rows * kb;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const long long r = i / kb, b = i % kb;
-        const float s = e4m3_bits_to_f32(sf_tiled[tiled_sf_offset(r, b, katoms)]);
+        const uint32_t s8 = sf_tiled[tiled_sf_offset(r, b, katoms)];
         const uint2 w = *reinterpret_cast<const uint2*>(data + r * (K / 2) + b * 8);
-        T o[16];
+        const uint32_t s1 = cvt_e4m3x2_to_f16x2(static_cast<uint16_t>(s8));          // low half = the scale
+        uint32_t s;
+        if constexpr (BF16) {
+            const float f = __half2float(__ushort_as_half(static_cast<unsigned short>(s1 & 0xFFFFu))) * __uint_as_float(0x77800000u);   // x 2^112
+            s = pack_bf16x2(f, f);
+        } else {
+            s = __byte_perm(s1, 0, 0x1010);
+        }
+        uint32_t h[8], o[8];
+        cvt_e2m1x8_to_f16x2x4(w.x, *reinterpret_cast<uint32_t(*)[4]>(&h[0]));
+        cvt_e2m1x8_to_f16x2x4(w.y, *reinterpret_cast<uint32_t(*)[4]>(&h[4]));
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const uint32_t n = ((j < 8 ? w.x : w.y) >> (4 * (j & 7))) & 0xFu;
-            const float f = e2m1_bits_to_f32(n) * s;
-            if constexpr (sizeof(T) == 2 && std::is_same<T, __half>::value) o[j] = __float2half_rn(f);
-            else o[j] = __float2bfloat16_rn(f);
+        for (int j = 0; j < 8; ++j) {
+            if constexpr (BF16) o[j] = mul_bf16x2(((h[j] >> 3) & 0x0FFF0FFFu) | (h[j] & 0x80008000u), s);
+            else o[j] = mul_f16x2(h[j], s);
         }
         uint4* dst = reinterpret_cast<uint4*>(out + r * K + b * 16);
-        dst[0] = *reinterpret_cast<uint4*>(&o[0]);
-        dst[1] = *reinterpret_cast<uint4*>(&o[8]);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
     }
 }
 

@@ -72,6 +72,9 @@ def _dense_inputs(oracle, kind, M, N, K, scale=1.0):
     ("f16", "f16", "decode", (33, 1000, 1032)),      # 64-row instruction, ragged N
     ("bf16", "f32", "decode", (64, 4096, 4096)),     # K split across a cluster
     ("bf16", "bf16", "decode", (5, 512, 8192)),      # deep K split, ring wraps
+    ("bf16", "bf16", "decode", (128, 512, 520)),     # 128-row activation tile, chunked epilogue
+    ("f16", "f32", "decode", (65, 384, 4096)),       # the same with a K split
+    ("f16", "f16", "decode", (100, 4096, 1024)),
 ])
 def test_dense16(oracle, cuda_device, kind, out_dtype, variant, shape):
     from blaze_b200 import GemmPlan
@@ -153,6 +156,9 @@ def _fp8_inputs(oracle, M, N, K):
     ("decode", (48, 1000, 1136)),
     ("decode", (7, 4096, 11008)),
     ("decode", (64, 12288, 4096)),
+    ("decode", (128, 4096, 4096)),                   # 128-row activation tile, K split
+    ("decode", (100, 1000, 1136)),
+    ("decode", (128, 4096, 11008)),
 ])
 def test_fp8(oracle, cuda_device, variant, shape):
     from blaze_b200 import GemmPlan
@@ -380,10 +386,13 @@ def test_nvfp4_config5_sampled(oracle, cuda_device):
 # ------------------------------------------------------------------------------------- W4A16
 
 @pytest.mark.parametrize("kind,shape", [
-    ("w4a16_bf16", (128, 256, 512)), ("w4a16_f16", (200, 328, 160)), ("w4a16_bf16", (512, 1024, 2048)),
+    ("w4a16_bf16", (129, 256, 512)), ("w4a16_f16", (200, 328, 160)), ("w4a16_bf16", (512, 1024, 2048)),
     # M <= 64: the weight-stream kernel that expands the packed weights in shared memory
     ("w4a16_f16", (1, 128, 64)), ("w4a16_bf16", (1, 256, 512)), ("w4a16_f16", (16, 328, 160)), ("w4a16_bf16", (40, 1000, 1056)),
     ("w4a16_bf16", (64, 4096, 4096)), ("w4a16_f16", (8, 4096, 11008)), ("w4a16_bf16", (32, 12288, 4096)),
+    # 64 < M <= 128: the same kernel family with one 128-row activation tile
+    ("w4a16_f16", (65, 128, 64)), ("w4a16_bf16", (100, 328, 160)), ("w4a16_f16", (128, 1000, 1056)),
+    ("w4a16_bf16", (128, 4096, 4096)), ("w4a16_f16", (96, 4096, 11008)), ("w4a16_f16", (128, 12288, 4096)),
 ])
 def test_w4a16(oracle, cuda_device, kind, shape):
     from blaze_b200 import GemmPlan
@@ -397,7 +406,7 @@ def test_w4a16(oracle, cuda_device, kind, shape):
     want = oracle.widen(oracle.narrow(oracle.epilogue(acc, alpha), act), act)
     C = _out_tensor(M, N, act, cuda_device)
     plan = GemmPlan(kind, M, N, K, bits16_to_torch(A, act, cuda_device), _u8(bd, cuda_device), B_sf=_u8(bsf, cuda_device), b_scale=gb, out_dtype=act)
-    if M <= 64:
+    if M <= 128:
         assert plan.info()["variant"] == 3 and plan.info()["launches"] == 1    # one kernel, no expanded copy of the weights
     _run(plan, C)
     assert_close(torch_to_f32(C, oracle, act), want, "w4a16 %s %s" % (kind, shape))
