@@ -43,6 +43,10 @@ WORKLOADS = {
 }
 DECODE_SHAPES = [(16, 12288, 4096), (16, 4096, 4096), (16, 22016, 4096), (16, 4096, 11008)]
 NOMINAL_TFLOPS = {"nvfp4": 9000.0, "fp8": 4500.0, "f16": 2250.0, "bf16": 2250.0, "w4a16_bf16": 2250.0, "w4a16_f16": 2250.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, one ncu capture each on one B200
+# (commands and full figures in profiles/): the default workload read 269.7 MB and wrote 447.5 MB
+# (algorithmic: 169.9 MB of operands, 469.8 MB of output); the decode shape read its weights once.
+NCU_DRAM_BYTES_PER_LAUNCH = {"nvfp4_8192x28672x8192": 717144320, "nvfp4_4096x12288x4096": 87164928, "decode_12288x4096": 28418304}
 PEAK_MULT_OVER_BF16 = {"nvfp4": 4.0, "fp8": 2.0, "f16": 1.0, "bf16": 1.0, "w4a16_bf16": 1.0, "w4a16_f16": 1.0}
 
 
@@ -411,7 +415,7 @@ def main() -> int:
                 "ms_per_step": best["us_per_gemm"] / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4",
                 "data": "synthetic", "config": {"workload": "nvfp4 decode M=16, Llama-7B projections (BASELINE configs[2])", "l2": "weight copies > 2x L2 cycled in one CUDA graph"},
                 "roofline": {"bound": "hbm", "achieved": best["hbm_gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": best["hbm_gbs"] / peaks["hbm_gbs"],
-                             "traffic": None, "peak_source": peaks["source"]},
+                             "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get("decode_%dx%d" % (best["N"], best["K"])), "peak_source": peaks["source"]},
                 "shapes": dec, "worst": worst, "clocks": clk.summary(), "gpu_launches": sum(d["launches"] for d in dec)}
         print(json.dumps(line))
         return 0
@@ -474,7 +478,11 @@ def main() -> int:
     flops_launch = 2.0 * M * n_local * K
     achieved = flops_launch / (ms_local * 1e-3) / 1e12
     peak = peaks["bf16_tflops"] * PEAK_MULT_OVER_BF16[kind]
-    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+    # DRAM bytes per launch from one ncu capture of this exact workload on one GPU
+    # (dram__bytes_read.sum + dram__bytes_write.sum; profiles/gemm_cluster_kernel.md); other
+    # workloads and shard sizes were not captured
+    traffic = NCU_DRAM_BYTES_PER_LAUNCH.get(name) if world == 1 else None
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
                 "peak_source": "%s dense bf16 burst (%.1f TFLOP/s) x %g, the nominal %s : bf16 ratio" % (peaks["source"], peaks["bf16_tflops"], PEAK_MULT_OVER_BF16[kind], kind),
                 "frac_of_nominal_peak": achieved / NOMINAL_TFLOPS[kind], "nominal_peak": NOMINAL_TFLOPS[kind],
                 "algorithmic_flops_per_launch": flops_launch,
