@@ -372,6 +372,15 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                             uint32_t acc[32];
                             tmem_ld32(t_row + c0 + h, acc);
                             tmem_ld_wait();
+                            if (c0 + chunk_cols * Cfg::EPI_SETS >= BN && h + 32 >= chunk_cols) {
+                                // that was this warp's last read of the accumulator: hand it back to the
+                                // MMA role now, the arithmetic and the stores of this chunk need it no more
+                                tc_fence_before_sync();
+                                __syncwarp();
+                                if (lane == 0) {
+                                    if constexpr (CG == 1) mbar_arrive(acc_empty_bar(buf)); else mbar_arrive_cluster(acc_empty_bar(buf), leader_rank);
+                                }
+                            }
                             const int col = n_tile * BN + c0 + h;
                             float v[32];
                             epilogue_math32(p.epi, acc, v, row0 + r_local, col, p.M, p.N);
@@ -416,7 +425,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (ok && lane == 0) {
+            if (ok && !p.use_tma_store && lane == 0) {       // the TMA-store path released the accumulator after its last read
                 if constexpr (CG == 1) mbar_arrive(acc_empty_bar(buf)); else mbar_arrive_cluster(acc_empty_bar(buf), leader_rank);
             }
             BLZ_T_ADD(t_work, tk);
