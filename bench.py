@@ -203,25 +203,35 @@ def run_gemm_workload(kind, M, N, K, device, steps, warmup, flusher, out_dtype="
                 flops=2.0 * M * N * K, out_bytes=M * N * C.element_size())
 
 
-def run_decode(device, steps, warmup, peaks):
-    """BASELINE config 3: NVFP4 M=16 decode projections.  Enough distinct weight copies to exceed twice
-    the L2 are cycled inside one CUDA graph so that every launch streams its weights from HBM."""
+def run_decode(device, steps, warmup, peaks, kind="nvfp4"):
+    """BASELINE config 3: M=16 decode projections (NVFP4; the same shapes for the other kinds on
+    request).  Enough distinct weight copies to exceed twice the L2 are cycled inside one CUDA graph
+    so that every launch streams its weights from HBM."""
     import torch
     from blaze_b200 import GemmPlan
     out = []
     for (M, N, K) in DECODE_SHAPES:
-        kw, _ = make_operands("nvfp4", M, N, K, device)
+        kw, _ = make_operands(kind, M, N, K, device)
         A, B = kw.pop("A"), kw.pop("B")
-        w_bytes = N * K // 2 + N * K // 16
-        algo = w_bytes + M * K // 2 + M * K // 16 + 2 * M * N
+        if kind == "nvfp4":
+            w_bytes = N * K // 2 + N * K // 16
+            algo = w_bytes + M * K // 2 + M * K // 16 + 2 * M * N
+        elif kind == "fp8":
+            w_bytes = N * K
+            algo = w_bytes + M * K + 2 * M * N
+        else:                                                  # 16-bit activations x NVFP4 weights
+            w_bytes = N * K // 2 + N * K // 16
+            algo = w_bytes + M * K * 2 + 2 * M * N
         copies = max(2, -(-2 * 126 * 1024 * 1024 // w_bytes))
         Bs = [B] + [B.clone() for _ in range(copies - 1)]
-        SFs = [kw["B_sf"]] + [kw["B_sf"].clone() for _ in range(copies - 1)]
+        SFs = [kw["B_sf"]] + [kw["B_sf"].clone() for _ in range(copies - 1)] if "B_sf" in kw else [None] * copies
         C = torch.empty((M, N), dtype=torch.bfloat16, device=device)
         plans = []
         for b, sf in zip(Bs, SFs):
-            k2 = dict(kw); k2["B_sf"] = sf
-            plans.append(GemmPlan("nvfp4", M, N, K, A, b, out_dtype="bf16", **k2))
+            k2 = dict(kw)
+            if sf is not None:
+                k2["B_sf"] = sf
+            plans.append(GemmPlan(kind, M, N, K, A, b, out_dtype="bf16", **k2))
         stream = torch.cuda.Stream()
         with torch.cuda.stream(stream):
             for p in plans:
@@ -523,10 +533,11 @@ def main() -> int:
                 torch.cuda.empty_cache()
             except Exception as ex:   # a secondary workload must not lose the headline line
                 others[w] = {"error": str(ex)[:200]}
-        try:
-            others["nvfp4_decode_M16"] = run_decode(device, 5, 3, peaks)
-        except Exception as ex:
-            others["nvfp4_decode_M16"] = {"error": str(ex)[:200]}
+        for dk in ("nvfp4", "fp8", "w4a16_bf16"):
+            try:
+                others["%s_decode_M16" % dk] = run_decode(device, 5, 3, peaks, kind=dk)
+            except Exception as ex:
+                others["%s_decode_M16" % dk] = {"error": str(ex)[:200]}
         line["others"] = others
 
     if rank == 0 and world == 1 and not args.no_cpu:
