@@ -82,7 +82,9 @@ typedef enum blz_variant {
     BLZ_VARIANT_AUTO = 0,
     BLZ_VARIANT_TILE_128x128 = 1, /* one CTA per 128x128 tile, two accumulator buffers */
     BLZ_VARIANT_PAIR_256x256 = 2, /* CTA pairs (cta_group::2), one 256x256 tile per pair */
-    BLZ_VARIANT_DECODE = 3,       /* weights as the 128-row operand, M <= 64, split along K */
+    BLZ_VARIANT_DECODE = 3,       /* skinny M: weights as the 128-row operand, split along K.  AUTO picks it
+                                     for M <= 64 (W4A16: M <= 128, expanding the packed weights in the
+                                     kernel); on request also M <= 128 for FP8 and 16-bit, not NVFP4 */
     BLZ_VARIANT_QUAD_512x256 = 4  /* two CTA pairs per 512x256 tile; the pairs pass each other their
                                      halves of the B tile through distributed shared memory */
 } blz_variant;

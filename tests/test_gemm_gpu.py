@@ -387,7 +387,7 @@ def test_nvfp4_config5_sampled(oracle, cuda_device):
 
 @pytest.mark.parametrize("kind,shape", [
     ("w4a16_bf16", (129, 256, 512)), ("w4a16_f16", (200, 328, 160)), ("w4a16_bf16", (512, 1024, 2048)),
-    # M <= 64: the weight-stream kernel that expands the packed weights in shared memory
+    # M <= 64: the weight-stream kernel that expands the packed weights into tensor memory
     ("w4a16_f16", (1, 128, 64)), ("w4a16_bf16", (1, 256, 512)), ("w4a16_f16", (16, 328, 160)), ("w4a16_bf16", (40, 1000, 1056)),
     ("w4a16_bf16", (64, 4096, 4096)), ("w4a16_f16", (8, 4096, 11008)), ("w4a16_bf16", (32, 12288, 4096)),
     # 64 < M <= 128: the same kernel family with one 128-row activation tile
