@@ -440,10 +440,11 @@ def test_w4a16_config4_sampled(oracle, cuda_device):
 
 @pytest.mark.parametrize("mode", ["bias", "silu", "bias_silu", "residual"])
 @pytest.mark.parametrize("kind,out_dtype", [("fp8", "f16"), ("nvfp4", "bf16"), ("bf16", "f32")])
-def test_epilogues(oracle, cuda_device, mode, kind, out_dtype):
+@pytest.mark.parametrize("M", [160, 24])           # tiled kernel / skinny-M kernel
+def test_epilogues(oracle, cuda_device, mode, kind, out_dtype, M):
     from blaze_b200 import GemmPlan
     torch = _torch()
-    M, N, K = 160, 264, 256
+    N, K = 264, 256
     rng = np.random.default_rng(77)
     bias32 = rng.standard_normal(N).astype(np.float32)
     res32 = rng.standard_normal((M, N)).astype(np.float32)
@@ -475,6 +476,32 @@ def test_epilogues(oracle, cuda_device, mode, kind, out_dtype):
                     residual=dev(res32) if mode == "residual" else None, **kw)
     _run(plan, C)
     assert_close(torch_to_f32(C, oracle, out_dtype), want, "epilogue %s %s" % (mode, kind))
+    plan.destroy()
+
+
+@pytest.mark.parametrize("mode", ["bias", "silu", "bias_silu", "residual"])
+@pytest.mark.parametrize("M", [24, 100])            # 64-row and 128-row activation tiles
+def test_epilogues_w4a16_skinny(oracle, cuda_device, mode, M):
+    """The kernels that expand the packed weights into tensor memory share the skinny-M epilogue;
+    M = 100 goes through its chunked form, K = 1056 through a ragged last load stage."""
+    from blaze_b200 import GemmPlan
+    N, K, act = 392, 1056, "bf16"
+    rng = np.random.default_rng(78)
+    A = oracle.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    bd, bsf, gb = oracle.quantize_nvfp4((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
+    bias_n = oracle.widen(oracle.narrow(rng.standard_normal(N).astype(np.float32), act), act)
+    res_n = oracle.widen(oracle.narrow(rng.standard_normal((M, N)).astype(np.float32), act), act)
+    acc, alpha = oracle.gemm_w4a16(A, act, bd, bsf, gb)
+    want32 = oracle.epilogue(acc, alpha, bias=bias_n if "bias" in mode else None, residual=res_n if mode == "residual" else None, mode=mode)
+    want = oracle.widen(oracle.narrow(want32, act), act)
+    C = _out_tensor(M, N, act, cuda_device)
+    plan = GemmPlan("w4a16_bf16", M, N, K, bits16_to_torch(A, act, cuda_device), _u8(bd, cuda_device), B_sf=_u8(bsf, cuda_device), b_scale=gb,
+                    out_dtype=act, epilogue=mode,
+                    bias=bits16_to_torch(oracle.narrow(bias_n, act), act, cuda_device) if "bias" in mode else None,
+                    residual=bits16_to_torch(oracle.narrow(res_n, act), act, cuda_device) if mode == "residual" else None)
+    assert plan.info()["variant"] == 3
+    _run(plan, C)
+    assert_close(torch_to_f32(C, oracle, act), want, "w4a16 skinny epilogue %s M=%d" % (mode, M))
     plan.destroy()
 
 
