@@ -19,13 +19,13 @@ F16, BF16, F32 = range(3)
 EPI_NONE, EPI_BIAS, EPI_SILU, EPI_BIAS_SILU, EPI_RESIDUAL_ADD = range(5)
 B_KMAJOR, B_NMAJOR = range(2)
 SF_ROWMAJOR, SF_TILED = range(2)
-VARIANT_AUTO, VARIANT_TILE_128x128, VARIANT_PAIR_256x256, VARIANT_DECODE, VARIANT_QUAD_512x256 = range(5)
+VARIANT_AUTO, VARIANT_TILE_128x128, VARIANT_PAIR_256x256, VARIANT_DECODE, VARIANT_QUAD_512x256, VARIANT_PAIR_256x384 = range(6)
 
 KINDS = {"f16": GEMM_F16, "bf16": GEMM_BF16, "fp8": GEMM_FP8, "nvfp4": GEMM_NVFP4,
          "w4a16_f16": GEMM_W4A16_F16, "w4a16_bf16": GEMM_W4A16_BF16}
 DTYPES = {"f16": F16, "bf16": BF16, "f32": F32}
 EPILOGUES = {"none": EPI_NONE, "bias": EPI_BIAS, "silu": EPI_SILU, "bias_silu": EPI_BIAS_SILU, "residual": EPI_RESIDUAL_ADD}
-VARIANTS = {"auto": VARIANT_AUTO, "128x128": VARIANT_TILE_128x128, "256x256": VARIANT_PAIR_256x256, "decode": VARIANT_DECODE, "512x256": VARIANT_QUAD_512x256}
+VARIANTS = {"auto": VARIANT_AUTO, "128x128": VARIANT_TILE_128x128, "256x256": VARIANT_PAIR_256x256, "decode": VARIANT_DECODE, "512x256": VARIANT_QUAD_512x256, "256x384": VARIANT_PAIR_256x384}
 
 # every symbol include/blaze_b200.h declares
 EXPORTS = (

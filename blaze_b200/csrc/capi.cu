@@ -109,7 +109,8 @@ ClusterChoice cluster_choice() {
                          static_cast<int>(Cfg::SMEM_BYTES), static_cast<int>(Cfg::TMEM_COLS), Cfg::THREADS, SHARE};
 }
 
-ClusterChoice pick_cluster_kernel(int mma_kind, int cg, int share) {
+ClusterChoice pick_cluster_kernel(int mma_kind, int cg, int share, bool wide = false) {
+    if (wide) return cluster_choice<MMA_NVF4, 2, 384, 4, 1>();
     if (cg == 2 && share == 2) {
         switch (mma_kind) {
             case MMA_F16: return cluster_choice<MMA_F16, 2, 256, 6, 2, 2>();
@@ -274,16 +275,17 @@ blz_status launch_config_cluster(const blz_gemm_plan* p, cudaLaunchConfig_t& cfg
     return BLZ_OK;
 }
 
-blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1) {
+blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1, bool wide = false) {
     const blz_gemm_desc& d = p->desc;
     const int64_t rb = row_bytes(p->mma_kind, d.K);
-    p->cc = pick_cluster_kernel(p->mma_kind, cg, share);
-    p->variant = share == 2 ? BLZ_VARIANT_QUAD_512x256 : cg == 2 ? BLZ_VARIANT_PAIR_256x256 : BLZ_VARIANT_TILE_128x128;
+    if (wide && p->mma_kind != MMA_NVF4) return BLZ_ERR_UNSUPPORTED;
+    p->cc = pick_cluster_kernel(p->mma_kind, cg, share, wide);
+    p->variant = wide ? BLZ_VARIANT_PAIR_256x384 : share == 2 ? BLZ_VARIANT_QUAD_512x256 : cg == 2 ? BLZ_VARIANT_PAIR_256x256 : BLZ_VARIANT_TILE_128x128;
     BLZ_CUDA(cudaFuncSetAttribute(p->cc.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, p->cc.smem));
     const int bn = p->cc.bn, tile_m = 128 * cg;
     blz_status s = encode_map(&p->tm_a, p->a_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.M), static_cast<uint64_t>(rb), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (s) return s;
-    s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rb), 128, static_cast<uint32_t>(bn / cg / share), CU_TENSOR_MAP_SWIZZLE_128B);
+    s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rb), 128, wide ? 64u : static_cast<uint32_t>(bn / cg / share), CU_TENSOR_MAP_SWIZZLE_128B);
     if (s) return s;
     ClusterGemmParams& cp = p->cp;
     cp.M = d.M; cp.N = d.N;
@@ -297,7 +299,9 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1) {
     if (cp.group_m < 1) cp.group_m = 1;
     cp.k_stages = static_cast<int>(ceil_div(rb, 128));
     const uint32_t fmt = d.kind == BLZ_GEMM_BF16 || d.kind == BLZ_GEMM_W4A16_BF16 ? 1u : 0u;
-    cp.idesc = p->mma_kind == MMA_NVF4 ? make_idesc_nvf4(tile_m, bn) : p->mma_kind == MMA_F8 ? make_idesc(0, 0, tile_m, bn) : make_idesc(fmt, fmt, tile_m, bn);
+    cp.idesc2 = make_idesc_nvf4(tile_m, 128);
+    cp.sfb_row_blocks = static_cast<int>(sf_row_blocks(d.N));
+    cp.idesc = wide ? make_idesc_nvf4(tile_m, 256) : p->mma_kind == MMA_NVF4 ? make_idesc_nvf4(tile_m, bn) : p->mma_kind == MMA_F8 ? make_idesc(0, 0, tile_m, bn) : make_idesc(fmt, fmt, tile_m, bn);
     cp.sfa = p->sfa_used; cp.sfb = p->sfb_used;
     cp.sf_katoms = static_cast<int>(sf_katoms(d.K));
     cp.status = p->status;
@@ -601,7 +605,8 @@ blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_p
             const int64_t tiles256 = ceil_div(desc->M, 256) * ceil_div(desc->N, 256);
             v = (desc->M > 128 && tiles256 >= p->num_sms / 2) ? BLZ_VARIANT_PAIR_256x256 : BLZ_VARIANT_TILE_128x128;
         }
-        if (v == BLZ_VARIANT_QUAD_512x256) s = setup_cluster(p, 2, 2);
+        if (v == BLZ_VARIANT_PAIR_256x384) s = setup_cluster(p, 2, 1, true);
+        else if (v == BLZ_VARIANT_QUAD_512x256) s = setup_cluster(p, 2, 2);
         else if (v == BLZ_VARIANT_PAIR_256x256) s = setup_cluster(p, 2);
         else if (v == BLZ_VARIANT_TILE_128x128) s = setup_cluster(p, 1);
         else s = BLZ_ERR_INVALID_ARGUMENT;

@@ -40,6 +40,8 @@ struct ClusterGemmParams {
     int group_m;             // tile rasterisation: bands of this many M tiles are walked N-first
     int k_stages;            // ceil(K bytes per row / 128)
     uint32_t idesc;
+    uint32_t idesc2;         // 384-wide tiles only: the second instruction of a K step (N = 128)
+    int sfb_row_blocks;      // 128-row blocks the tiled scale factors of B hold
     const uint8_t* sfa;      // tiled scale factors of A: [row blocks of 128][sf_katoms][512]
     const uint8_t* sfb;      // tiled scale factors of B
     int sf_katoms;
@@ -79,6 +81,12 @@ struct ClusterGemmConfig {
     // fetches only half of its share from L2 and forwards it to the matching CTA of the other
     // pair through distributed shared memory (and receives the other half the same way), which
     // cuts the B bytes every SM pulls from L2 in two.
+    // BN = 384 (NVFP4 CTA pairs only): one tile is a 256-wide and a 128-wide instruction per K
+    // step over the same A tile, which brings the bytes pulled from L2 per FLOP down by 16 %
+    // against 256x256 (48 KB for 128 x 384 per CTA and stage instead of 38 KB for 128 x 256) --
+    // the pair kernels are bound by L2 -> SM traffic.  The accumulator takes 384 tensor-memory
+    // columns, so the scale factors get two slots that alternate, not one per stage.
+    static constexpr bool WIDE = (BN > 256);
     static constexpr int CLUSTER = CG * SHARE;
     static constexpr bool HAS_SF = (KIND == MMA_NVF4);
     // With a single accumulator buffer the epilogue is on the critical path: two sets of four
@@ -100,7 +108,8 @@ struct ClusterGemmConfig {
     static constexpr uint32_t ACC_COLS = ACC_BUFS * BN;
     static constexpr uint32_t SF_COLS = HAS_SF ? 16 + 4 * (BN / 32) : 0;  // per stage: A 4 per atom, B BN/32 per atom
     static constexpr uint32_t SF_BASE = ACC_COLS;
-    static constexpr uint32_t TMEM_NEED = ACC_COLS + STAGES * SF_COLS;
+    static constexpr int SF_SLOTS = WIDE ? 2 : STAGES;
+    static constexpr uint32_t TMEM_NEED = ACC_COLS + SF_SLOTS * SF_COLS;
     static constexpr uint32_t TMEM_COLS = tmem_cols_pow2(TMEM_NEED);
     static constexpr uint32_t NUM_BARS = (SHARE == 2 ? 5 : 3) * STAGES + 2 * ACC_BUFS;
     static constexpr uint32_t BAR_BYTES = 8 * NUM_BARS + 16;
@@ -110,7 +119,8 @@ struct ClusterGemmConfig {
     static_assert(SHARE == 1 || (SHARE == 2 && CG == 2), "B sharing needs CTA pairs");
     static_assert(TMEM_NEED <= 512, "accumulators and scale factors exceed tensor memory");
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared-memory limit");
-    static_assert(B_ROWS % 8 == 0 && BN % 128 == 0 && BN <= 256, "tile width");
+    static_assert(B_ROWS % 8 == 0 && BN % 128 == 0 && BN <= 384, "tile width");
+    static_assert(!WIDE || (KIND == MMA_NVF4 && CG == 2 && SHARE == 1 && ACC_BUFS == 1 && STAGES % 2 == 0), "384-wide tiles: NVFP4 CTA pairs only");
 };
 
 template <int KIND, int CG, int BN, int STAGES, int ACC_BUFS, int SHARE = 1>
@@ -213,7 +223,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         bulk_load_1d(ssfa, p.sfa + (a_blk * p.sf_katoms + katom) * 512, Cfg::SF_BLOCK_BYTES, full_bar(stage));
 #pragma unroll
                         for (int blk = 0; blk < static_cast<int>(Cfg::SFB_BLOCKS); ++blk) {
-                            const size_t rb = static_cast<size_t>(n_tile) * Cfg::SFB_BLOCKS + blk;
+                            // a ragged last tile may reach past the last block: any valid block will do, those columns are never stored
+                            const size_t rb = static_cast<size_t>(min(n_tile * static_cast<int>(Cfg::SFB_BLOCKS) + blk, p.sfb_row_blocks - 1));
                             bulk_load_1d(ssfb + blk * Cfg::SF_BLOCK_BYTES, p.sfb + (rb * p.sf_katoms + katom) * 512, Cfg::SF_BLOCK_BYTES, full_bar(stage));
                         }
                     }
@@ -226,6 +237,12 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         }
                         mbar_arrive_expect_tx(bpart_bar(stage), Cfg::B_LOAD_BYTES);
                         tma_load_2d(sb + pair * Cfg::B_LOAD_BYTES, &tm_b, ks * 128, b_row, bpart_bar(stage));
+                    } else if constexpr (Cfg::WIDE) {
+                        // this CTA's share of the 256-wide instruction (128 rows, two boxes of 64) and of the 128-wide one (64 rows)
+                        const int n0 = n_tile * BN;
+                        tma_load_2d(sb, &tm_b, ks * 128, n0 + static_cast<int>(prank) * 128, full_bar(stage));
+                        tma_load_2d(sb + 8192, &tm_b, ks * 128, n0 + static_cast<int>(prank) * 128 + 64, full_bar(stage));
+                        tma_load_2d(sb + 16384, &tm_b, ks * 128, n0 + 256 + static_cast<int>(prank) * 64, full_bar(stage));
                     } else {
                         tma_load_2d(sb, &tm_b, ks * 128, b_row, full_bar(stage));
                     }
@@ -240,6 +257,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (leader && elect_one()) {
             int stage = 0; uint32_t phase = 0;
             int it = 0;
+            [[maybe_unused]] uint32_t g = 0;       // stages issued so far (384-wide tiles: scale-factor slot = g % 2)
             bool ok = true;
             BLZ_T_DECL(t_wait_ready); BLZ_T_DECL(t_wait_acc);
             [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
@@ -262,13 +280,18 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     tc_fence_after_sync();
                     const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
-                    const uint32_t sf_cols = tmem_base + Cfg::SF_BASE + stage * Cfg::SF_COLS;
+                    const uint32_t sf_cols = tmem_base + Cfg::SF_BASE + (Cfg::WIDE ? (g & 1u) : static_cast<uint32_t>(stage)) * Cfg::SF_COLS;
+                    ++g;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         const uint64_t ad = make_desc_k_sw128(sa + k * 32);
                         const uint64_t bd = make_desc_k_sw128(sb + k * 32);
                         const uint32_t accumulate = (ks | k) != 0 ? 1u : 0u;
-                        if constexpr (CG == 1) {
+                        if constexpr (Cfg::WIDE) {
+                            // columns [0, 256) and [256, 384) of the tile; scale columns of one K atom: 8 + 4
+                            umma_nvf4_pair(d_tmem, ad, bd, p.idesc, sf_cols + 4 * k, sf_cols + 16 + k * 12, accumulate);
+                            umma_nvf4_pair(d_tmem + 256, ad, make_desc_k_sw128(sb + 16384 + k * 32), p.idesc2, sf_cols + 4 * k, sf_cols + 16 + k * 12 + 8, accumulate);
+                        } else if constexpr (CG == 1) {
                             if constexpr (KIND == MMA_F16) umma_f16(d_tmem, ad, bd, p.idesc, accumulate);
                             else if constexpr (KIND == MMA_F8) umma_f8(d_tmem, ad, bd, p.idesc, accumulate);
                             else umma_nvf4(d_tmem, ad, bd, p.idesc, sf_cols + 4 * k, sf_cols + 16 + k * (BN / 32), accumulate);
@@ -437,15 +460,28 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if constexpr (Cfg::HAS_SF) {
             const int q = warp & 3;
             int stage = 0; uint32_t phase = 0;
+            [[maybe_unused]] uint32_t g = 0;       // stages handled so far
             bool ok = true;
             for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
                 for (int ks = 0; ks < p.k_stages; ++ks) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
                         atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
                     }
+                    if constexpr (Cfg::WIDE) {
+                        // Two scale-factor slots alternate: slot g % 2 was read by the MMAs of stage g - 2,
+                        // whose completion the MMA role committed to that stage's empty barrier.
+                        if (g >= 2) {
+                            const uint32_t gp = g - 2;
+                            if (!mbar_wait(empty_bar(static_cast<int>(gp % STAGES)), (gp / STAGES) & 1u, abort_flag)) {
+                                atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
+                            }
+                            tc_fence_after_sync();
+                        }
+                    }
                     const uint8_t* ssfa = gen_base + stage * Cfg::STAGE_BYTES + Cfg::A_BYTES + Cfg::B_BYTES;
                     const uint8_t* ssfb = ssfa + Cfg::SFA_BYTES;
-                    const uint32_t t_sf = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::SF_BASE + stage * Cfg::SF_COLS;
+                    const uint32_t t_sf = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::SF_BASE + (Cfg::WIDE ? (g & 1u) : static_cast<uint32_t>(stage)) * Cfg::SF_COLS;
+                    ++g;
                     {
                         uint32_t r[16];
 #pragma unroll
@@ -455,7 +491,19 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         }
                         tmem_st16(t_sf, r);
                     }
-                    if constexpr (BN == 256) {
+                    if constexpr (BN == 384) {
+                        // per K atom: 8 columns for the 256-wide instruction (blocks 0, 1), then 4 for the 128-wide one (block 2)
+                        uint32_t r[48];
+#pragma unroll
+                        for (int a = 0; a < 4; ++a)
+#pragma unroll
+                            for (int blk = 0; blk < 3; ++blk) {
+                                const uint4 v = *reinterpret_cast<const uint4*>(ssfb + blk * Cfg::SF_BLOCK_BYTES + a * 512 + lane * 16);
+                                r[12 * a + 4 * blk] = v.x; r[12 * a + 4 * blk + 1] = v.y; r[12 * a + 4 * blk + 2] = v.z; r[12 * a + 4 * blk + 3] = v.w;
+                            }
+                        tmem_st32(t_sf + 16, *reinterpret_cast<const uint32_t(*)[32]>(&r[0]));
+                        tmem_st16(t_sf + 48, *reinterpret_cast<const uint32_t(*)[16]>(&r[32]));
+                    } else if constexpr (BN == 256) {
                         uint32_t r[32];
 #pragma unroll
                         for (int a = 0; a < 4; ++a)

@@ -85,8 +85,10 @@ typedef enum blz_variant {
     BLZ_VARIANT_DECODE = 3,       /* skinny M: weights as the 128-row operand, split along K.  AUTO picks it
                                      for M <= 64 (W4A16: M <= 128, expanding the packed weights in the
                                      kernel); on request also M <= 128 for FP8 and 16-bit, not NVFP4 */
-    BLZ_VARIANT_QUAD_512x256 = 4  /* two CTA pairs per 512x256 tile; the pairs pass each other their
+    BLZ_VARIANT_QUAD_512x256 = 4, /* two CTA pairs per 512x256 tile; the pairs pass each other their
                                      halves of the B tile through distributed shared memory */
+    BLZ_VARIANT_PAIR_256x384 = 5  /* NVFP4 only: CTA pairs, 256x384 tiles (a 256-wide and a 128-wide
+                                     instruction per K step), fewer L2 bytes per FLOP */
 } blz_variant;
 
 typedef struct blz_gemm_desc {

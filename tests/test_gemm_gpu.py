@@ -262,7 +262,7 @@ def test_nvfp4(oracle, cuda_device, variant, shape):
     plan.destroy()
 
 
-@pytest.mark.parametrize("variant,M", [("128x128", 128), ("256x256", 256), ("256x256", 128), ("decode", 16)])
+@pytest.mark.parametrize("variant,M", [("128x128", 128), ("256x256", 256), ("256x256", 128), ("256x384", 256), ("decode", 16)])
 def test_nvfp4_position_coded(oracle, cuda_device, variant, M):
     """Catches transposition, nibble order and scale-layout errors that constant fills hide:
     row m of A is one-hot at k = (37*m + 5) % K with its own block scale, every weight and every
