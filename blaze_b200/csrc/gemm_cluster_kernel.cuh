@@ -383,7 +383,51 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             const int r_local = q * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
             if (p.use_tma_store) {
-                for (int c0 = eset * chunk_cols; c0 < BN; c0 += chunk_cols * Cfg::EPI_SETS) {
+                // The accumulator reads run one chunk ahead of the staging: the columns of chunk i+1
+                // are taken into registers before the store of chunk i is even issued, and the
+                // accumulator goes back to the MMA role right after the last read -- no wait for a
+                // staging buffer or a TMA store sits between "accumulator full" and "accumulator free".
+                const int step = chunk_cols * Cfg::EPI_SETS;
+                const bool two = chunk_cols == 64;                         // 16-bit outputs: 64 columns per chunk
+                uint32_t acc0[32], acc1[32];
+                auto load_chunk = [&](int c) {
+                    tmem_ld32(t_row + c, acc0);
+                    if (two) tmem_ld32(t_row + c + 32, acc1);
+                    tmem_ld_wait();
+                    if (c + step >= BN) {
+                        // that was this warp's last read of the accumulator
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if constexpr (CG == 1) mbar_arrive(acc_empty_bar(buf)); else mbar_arrive_cluster(acc_empty_bar(buf), leader_rank);
+                        }
+                    }
+                };
+                auto stage32 = [&](const uint32_t (&a)[32], uint32_t sbuf, int c, int h) {
+                    float v[32];
+                    epilogue_math32(p.epi, a, v, row0 + r_local, n_tile * BN + c + h, p.M, p.N);
+                    // 128-byte swizzle: 16-byte unit j of row r lives at unit (j ^ (r % 8))
+                    const uint32_t srow = sbuf + r_local * 128;
+                    if (out_esize == 4) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const uint32_t dst = srow + (((h / 4 + j) ^ (r_local & 7)) << 4);
+                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3]) : "memory");
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) w[t] = pack2_out(p.epi.out_type, v[8 * j + 2 * t], v[8 * j + 2 * t + 1]);
+                            const uint32_t dst = srow + (((h / 8 + j) ^ (r_local & 7)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                        }
+                    }
+                };
+                int c0 = eset * chunk_cols;
+                if (ok) load_chunk(c0);
+                for (; c0 < BN; c0 += step) {
                     // One set: the two staging buffers alternate, buffer `obuf` was handed to a TMA
                     // store two chunks ago.  Two sets: each set owns one buffer and waits for its own
                     // previous store.  Either way: wait until that store has finished reading it.
@@ -391,41 +435,9 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     named_barrier_sync(bar_id, 128);
                     const uint32_t sbuf = out_base + (Cfg::EPI_SETS == 2 ? eset : obuf) * Cfg::OUT_BUF_BYTES;
                     if (ok) {
-                        for (int h = 0; h < chunk_cols; h += 32) {
-                            uint32_t acc[32];
-                            tmem_ld32(t_row + c0 + h, acc);
-                            tmem_ld_wait();
-                            if (c0 + chunk_cols * Cfg::EPI_SETS >= BN && h + 32 >= chunk_cols) {
-                                // that was this warp's last read of the accumulator: hand it back to the
-                                // MMA role now, the arithmetic and the stores of this chunk need it no more
-                                tc_fence_before_sync();
-                                __syncwarp();
-                                if (lane == 0) {
-                                    if constexpr (CG == 1) mbar_arrive(acc_empty_bar(buf)); else mbar_arrive_cluster(acc_empty_bar(buf), leader_rank);
-                                }
-                            }
-                            const int col = n_tile * BN + c0 + h;
-                            float v[32];
-                            epilogue_math32(p.epi, acc, v, row0 + r_local, col, p.M, p.N);
-                            // 128-byte swizzle: 16-byte unit j of row r lives at unit (j ^ (r % 8))
-                            const uint32_t srow = sbuf + r_local * 128;
-                            if (out_esize == 4) {
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) {
-                                    const uint32_t dst = srow + (((h / 4 + j) ^ (r_local & 7)) << 4);
-                                    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3]) : "memory");
-                                }
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    uint32_t w[4];
-#pragma unroll
-                                    for (int t = 0; t < 4; ++t) w[t] = pack2_out(p.epi.out_type, v[8 * j + 2 * t], v[8 * j + 2 * t + 1]);
-                                    const uint32_t dst = srow + (((h / 8 + j) ^ (r_local & 7)) << 4);
-                                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
-                                }
-                            }
-                        }
+                        stage32(acc0, sbuf, c0, 0);
+                        if (two) stage32(acc1, sbuf, c0, 32);
+                        if (c0 + step < BN) load_chunk(c0 + step);
                     }
                     fence_proxy_async_smem();
                     named_barrier_sync(bar_id, 128);
