@@ -470,7 +470,7 @@ blz_status decode_launch(blz_gemm_plan* p, void* C, cudaStream_t stream) {
 blz_status launch_cluster(blz_gemm_plan* p, int n_dst, void* const* dst, int64_t ld, int64_t col_offset, cudaStream_t stream) {
     const blz_gemm_desc& d = p->desc;
     if (p->own_w16) {
-        const int64_t blocks16 = static_cast<int64_t>(d.N) * (d.K / 16);
+        const int64_t blocks16 = static_cast<int64_t>(d.N) * (d.K / 8);     // one thread per 8 values
         if (d.kind == BLZ_GEMM_W4A16_F16)
             dequant_nvfp4_kernel<false><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<uint16_t*>(p->own_w16));
         else

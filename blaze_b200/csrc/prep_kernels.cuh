@@ -151,18 +151,18 @@ __global__ void quantize_nvfp4_kernel(const T* __restrict__ x, long long rows, l
 
 // ---- NVFP4 weights -> 16-bit values q*sf (exact: 6 significant bits), global scale left out.
 //      data [rows, K/2], sf read through the tiled layout; out [rows, K].
-//      One thread per 16-value block: 8 packed bytes in, 32 bytes out, hardware conversions
-//      (fp16: cvt + packed multiply; bf16: the fp16 pattern shifted by three is the value x 2^-112,
-//      multiplied by bf16(scale x 2^112)).
+//      One thread per 8 values: 4 packed bytes in, 16 bytes out, so a warp reads 128 and writes 512
+//      contiguous bytes per instruction; hardware conversions (fp16: cvt + packed multiply; bf16:
+//      the fp16 pattern shifted by three is the value x 2^-112, multiplied by bf16(scale x 2^112)).
 template <bool BF16>
 __global__ void dequant_nvfp4_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ sf_tiled, long long katoms,
                                      long long rows, long long K, uint16_t* __restrict__ out) {
-    const long long kb = K / 16, total = rows * kb;
+    const long long k8 = K / 8, total = rows * k8;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const long long r = i / kb, b = i % kb;
-        const uint32_t s8 = sf_tiled[tiled_sf_offset(r, b, katoms)];
-        const uint2 w = *reinterpret_cast<const uint2*>(data + r * (K / 2) + b * 8);
+        const long long r = i / k8, c = i % k8;                      // c: which group of 8 values of the row
+        const uint32_t s8 = sf_tiled[tiled_sf_offset(r, c >> 1, katoms)];
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(data + r * (K / 2) + c * 4);
         const uint32_t s1 = cvt_e4m3x2_to_f16x2(static_cast<uint16_t>(s8));          // low half = the scale
         uint32_t s;
         if constexpr (BF16) {
@@ -171,17 +171,14 @@ __global__ void dequant_nvfp4_kernel(const uint8_t* __restrict__ data, const uin
         } else {
             s = __byte_perm(s1, 0, 0x1010);
         }
-        uint32_t h[8], o[8];
-        cvt_e2m1x8_to_f16x2x4(w.x, *reinterpret_cast<uint32_t(*)[4]>(&h[0]));
-        cvt_e2m1x8_to_f16x2x4(w.y, *reinterpret_cast<uint32_t(*)[4]>(&h[4]));
+        uint32_t h[4], o[4];
+        cvt_e2m1x8_to_f16x2x4(w, h);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 4; ++j) {
             if constexpr (BF16) o[j] = mul_bf16x2(((h[j] >> 3) & 0x0FFF0FFFu) | (h[j] & 0x80008000u), s);
             else o[j] = mul_f16x2(h[j], s);
         }
-        uint4* dst = reinterpret_cast<uint4*>(out + r * K + b * 16);
-        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        *reinterpret_cast<uint4*>(out + r * K + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
     }
 }
 
