@@ -559,6 +559,53 @@ def test_set_a_rebinds_activations(oracle, cuda_device):
     plan.destroy()
 
 
+@pytest.mark.parametrize("kind,M", [("w4a16_bf16", 24), ("w4a16_f16", 100), ("fp8", 48), ("bf16", 8), ("bf16", 300)])
+def test_set_a_other_kinds(oracle, cuda_device, kind, M):
+    """Rebinding the activations of a plan (decode loops reuse one plan per weight matrix): the
+    skinny-M kernels of every kind and the tiled kernel."""
+    from blaze_b200 import GemmPlan
+    N, K = 392, 1056 if kind != "fp8" else 1040
+    rng = np.random.default_rng(4321)
+
+    def make_a(seed):
+        x = np.random.default_rng(seed).standard_normal((M, K)).astype(np.float32)
+        if kind == "fp8":
+            q, s = oracle.quantize_fp8(x)
+            return q, float(np.float32(1.0) / np.float32(s))
+        enc = oracle.f32_to_f16 if kind.endswith("f16") and not kind.endswith("bf16") else oracle.f32_to_bf16
+        return enc(x), 1.0
+
+    act = "f16" if kind == "w4a16_f16" else "bf16"
+    if kind.startswith("w4a16"):
+        bd, bsf, gb = oracle.quantize_nvfp4((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
+        ref = lambda a, sa: oracle.epilogue(*oracle.gemm_w4a16(a, act, bd, bsf, gb))
+        to_dev = lambda a: bits16_to_torch(a, act, cuda_device)
+        b_args, kw = (_u8(bd, cuda_device),), dict(B_sf=_u8(bsf, cuda_device), b_scale=gb)
+    elif kind == "fp8":
+        qb, sb = oracle.quantize_fp8(rng.uniform(-1, 1, (N, K)).astype(np.float32))
+        db = float(np.float32(1.0) / np.float32(sb))
+        ref = lambda a, sa: oracle.epilogue(oracle.gemm_f32(oracle.e4m3_to_f32(a), oracle.e4m3_to_f32(qb)), float(np.float32(sa) * np.float32(db)))
+        to_dev = lambda a: _u8(a, cuda_device)
+        b_args, kw = (_u8(qb, cuda_device),), dict(b_scale=db)
+    else:
+        Bt = oracle.f32_to_bf16(rng.standard_normal((N, K)).astype(np.float32))
+        ref = lambda a, sa: oracle.gemm_dense16(a, Bt, "bf16")
+        to_dev = lambda a: bits16_to_torch(a, "bf16", cuda_device)
+        b_args, kw = (bits16_to_torch(Bt, "bf16", cuda_device),), {}
+    (a1, s1), (a2, s2) = make_a(1), make_a(2)
+    C = _out_tensor(M, N, act, cuda_device)
+    if kind == "fp8":
+        kw["a_scale"] = s1
+    plan = GemmPlan(kind, M, N, K, to_dev(a1), *b_args, out_dtype=act, **kw)
+    _run(plan, C)
+    assert_close(torch_to_f32(C, oracle, act), oracle.widen(oracle.narrow(ref(a1, s1), act), act), "%s M=%d before set_a" % (kind, M))
+    d2 = to_dev(a2)
+    plan.set_a(d2, None, s2 if kind == "fp8" else 0.0)
+    _run(plan, C)
+    assert_close(torch_to_f32(C, oracle, act), oracle.widen(oracle.narrow(ref(a2, s2), act), act), "%s M=%d after set_a" % (kind, M))
+    plan.destroy()
+
+
 # ------------------------------------------------------------------------ byte-level kernels
 
 def test_quantizers_bit_exact(oracle, cuda_device):
