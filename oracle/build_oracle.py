@@ -100,6 +100,17 @@ def build_ref_programs(force: bool = False) -> list[str]:
             _run([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17", "-w", "-I", os.path.join(root, "include"), src,
                   "-L", lib_dir, "-lblaze_b200", "-lcublas", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../blaze_b200", "-o", out])
         built.append(out)
+    # Blaze's bring-up test of the raw tcgen05 / TMA helpers: compiled to an object only, against this
+    # repository's gemm/tma_utils.cuh and gemm/tmem_utils.cuh (a check that the helper names and
+    # signatures are all there).  It is not linked into a program: its kernels are Blaze's own.
+    src = os.path.join(REF_ROOT, "tests", "test_sm100_primitives.cu")
+    obj = os.path.join(out_dir, "test_sm100_primitives.o")
+    if os.path.exists(src):
+        os.makedirs(out_dir, exist_ok=True)
+        hdrs = [os.path.join(root, "include", "gemm", h) for h in ("tma_utils.cuh", "tmem_utils.cuh")]
+        if force or _newer([src] + hdrs, obj):
+            _run([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17", "-w", "-I", os.path.join(root, "include"), "-c", src, "-o", obj])
+        built.append(obj)
     return built
 
 
