@@ -120,12 +120,14 @@ ClusterChoice pick_cluster_kernel(int mma_kind, int cg, int share, bool wide = f
     }
     if (cg == 2) {
         switch (mma_kind) {
+            case MMA_W4A16: return cluster_choice<MMA_W4A16, 2, 256, 5, 2>();
             case MMA_F16: return cluster_choice<MMA_F16, 2, 256, 6, 2>();
             case MMA_F8: return cluster_choice<MMA_F8, 2, 256, 6, 2>();
             default: return cluster_choice<MMA_NVF4, 2, 256, 5, 1>();
         }
     }
     switch (mma_kind) {
+        case MMA_W4A16: return cluster_choice<MMA_W4A16, 1, 128, 5, 2>();
         case MMA_F16: return cluster_choice<MMA_F16, 1, 128, 6, 2>();
         case MMA_F8: return cluster_choice<MMA_F8, 1, 128, 6, 2>();
         default: return cluster_choice<MMA_NVF4, 1, 128, 5, 2>();
@@ -279,13 +281,22 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1, bool wide = fa
     const blz_gemm_desc& d = p->desc;
     const int64_t rb = row_bytes(p->mma_kind, d.K);
     if (wide && p->mma_kind != MMA_NVF4) return BLZ_ERR_UNSUPPORTED;
-    p->cc = pick_cluster_kernel(p->mma_kind, cg, share, wide);
+    // W4A16 without a 16-bit copy of the weights: the kernel expands the packed weights itself
+    const bool fused_w4 = (d.kind == BLZ_GEMM_W4A16_F16 || d.kind == BLZ_GEMM_W4A16_BF16) && p->own_w16 == nullptr;
+    if (fused_w4 && share != 1) return BLZ_ERR_UNSUPPORTED;
+    p->cc = pick_cluster_kernel(fused_w4 ? static_cast<int>(MMA_W4A16) : p->mma_kind, cg, share, wide);
     p->variant = wide ? BLZ_VARIANT_PAIR_256x384 : share == 2 ? BLZ_VARIANT_QUAD_512x256 : cg == 2 ? BLZ_VARIANT_PAIR_256x256 : BLZ_VARIANT_TILE_128x128;
     BLZ_CUDA(cudaFuncSetAttribute(p->cc.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, p->cc.smem));
     const int bn = p->cc.bn, tile_m = 128 * cg;
     blz_status s = encode_map(&p->tm_a, p->a_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.M), static_cast<uint64_t>(rb), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (s) return s;
-    s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rb), 128, wide ? 64u : static_cast<uint32_t>(bn / cg / share), CU_TENSOR_MAP_SWIZZLE_128B);
+    if (fused_w4) {
+        // packed weights: 32 bytes (64 K values) x 128 rows per stage, unswizzled -- the expansion warps read them
+        const int64_t rbw = d.K / 2;
+        s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rbw), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rbw), 32, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
+    } else {
+        s = encode_map(&p->tm_b, p->b_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.N), static_cast<uint64_t>(rb), 128, wide ? 64u : static_cast<uint32_t>(bn / cg / share), CU_TENSOR_MAP_SWIZZLE_128B);
+    }
     if (s) return s;
     ClusterGemmParams& cp = p->cp;
     cp.M = d.M; cp.N = d.N;
@@ -301,6 +312,7 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1, bool wide = fa
     const uint32_t fmt = d.kind == BLZ_GEMM_BF16 || d.kind == BLZ_GEMM_W4A16_BF16 ? 1u : 0u;
     cp.idesc2 = make_idesc_nvf4(tile_m, 128);
     cp.sfb_row_blocks = static_cast<int>(sf_row_blocks(d.N));
+    cp.expand_bf16 = d.kind == BLZ_GEMM_W4A16_BF16 ? 1 : 0;
     cp.idesc = wide ? make_idesc_nvf4(tile_m, 256) : p->mma_kind == MMA_NVF4 ? make_idesc_nvf4(tile_m, bn) : p->mma_kind == MMA_F8 ? make_idesc(0, 0, tile_m, bn) : make_idesc(fmt, fmt, tile_m, bn);
     cp.sfa = p->sfa_used; cp.sfb = p->sfb_used;
     cp.sf_katoms = static_cast<int>(sf_katoms(d.K));
@@ -584,7 +596,13 @@ blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_p
     const int decode_max_m = desc->kind == BLZ_GEMM_NVFP4 ? 64 : 128;
     const int decode_auto_m = w4a16 ? 128 : 64;
     const bool want_decode = desc->variant == BLZ_VARIANT_DECODE || (desc->variant == BLZ_VARIANT_AUTO && desc->M <= decode_auto_m);
-    if (w4a16 && !want_decode) {
+    // M > 128: up to 2048 rows the tiled kernel expands the packed weights stage by stage in shared
+    // memory (no 16-bit copy; every CTA re-expands the tiles it uses).  Beyond that, expanding all
+    // weights once per call into a plan-owned 16-bit copy costs less than the slower main loop
+    // (measured: 4096 x 22016 x 4096 bf16 1556 against 1427 TFLOP/s).  BLZ_W4A16_PREPASS=0 / 1 forces one.
+    const int prepass_knob = env_int("BLZ_W4A16_PREPASS", -1);
+    const bool prepass = prepass_knob >= 0 ? prepass_knob != 0 : desc->M > 2048;
+    if (w4a16 && !want_decode && (prepass || desc->variant == BLZ_VARIANT_QUAD_512x256)) {
         // The tiled kernels consume 16-bit weights: every execute expands the packed weights into
         // this buffer (q * block scale, exact in 16 bits); the fp32 tensor scale goes into alpha.
         if ((s = dev_alloc(p, &p->own_w16, static_cast<int64_t>(desc->N) * desc->K * 2, false))) return fail(s);
@@ -596,7 +614,7 @@ blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_p
         p->variant = BLZ_VARIANT_DECODE;
         if ((s = decode_setup(p))) return fail(s);
     } else {
-        const void* b_tc = w4a16 ? p->own_w16 : p->b_used;
+        const void* b_tc = (w4a16 && p->own_w16) ? p->own_w16 : p->b_used;
         const void* keep = p->b_used;
         p->b_used = b_tc;
         int v = desc->variant;

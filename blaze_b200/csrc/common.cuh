@@ -10,7 +10,7 @@
 
 namespace blz {
 
-enum MmaKind : int { MMA_F16 = 0, MMA_F8 = 1, MMA_NVF4 = 2 };
+enum MmaKind : int { MMA_F16 = 0, MMA_F8 = 1, MMA_NVF4 = 2, MMA_W4A16 = 3 };   // W4A16: kind::f16 instructions, B expanded from NVFP4 in the kernel
 enum OutType : int { OUT_F16 = 0, OUT_BF16 = 1, OUT_F32 = 2 };
 enum EpiMode : int { EPI_NONE = 0, EPI_BIAS = 1, EPI_SILU = 2, EPI_BIAS_SILU = 3, EPI_RESIDUAL = 4 };
 
@@ -158,6 +158,46 @@ __device__ __forceinline__ void epilogue_store32_dyn(const EpilogueParams& e, co
     if (e.out_type == OUT_BF16) epilogue_store32<OUT_BF16>(e, acc, row, col0, M, N);
     else if (e.out_type == OUT_F16) epilogue_store32<OUT_F16>(e, acc, row, col0, M, N);
     else epilogue_store32<OUT_F32>(e, acc, row, col0, M, N);
+}
+
+// W4A16, tiled kernel: 256 threads turn one stage of packed weights (128 rows x 64 K values) into
+// the 16-bit operand tile.  Thread t takes half a row (32 values = 16 packed bytes, two block
+// scales).  packed: [128][32] bytes, even k in the low nibble; sf_atom: the tiled scale layout,
+// row r at byte (r % 32) * 16 + (r / 32) * 4; dst: shared-memory address of the operand tile
+// (1024-byte aligned), 16-byte unit j of row r at unit j ^ (r % 8), as a 128-byte-swizzled TMA
+// load would have left it.  q * scale has at most six significant bits: exact in fp16 and bf16.
+// bf16: the fp16 bit pattern of an E2M1 value, shifted right by three with the sign put back,
+// read as bf16 is the value times 2^-112; the scale is prepared as bf16(scale * 2^112).
+template <bool BF16>
+__device__ __forceinline__ void expand_w4_stage(const uint8_t* packed, const uint8_t* sf_atom, uint32_t dst, int t) {
+    const int row = t >> 1, half = t & 1;
+    const uint4 w = *reinterpret_cast<const uint4*>(packed + row * 32 + half * 16);
+    const uint32_t sf4 = *reinterpret_cast<const uint32_t*>(sf_atom + (row & 31) * 16 + (row >> 5) * 4);
+    const uint32_t s01 = cvt_e4m3x2_to_f16x2(static_cast<uint16_t>(sf4 >> (16 * half)));
+    uint32_t s_lo, s_hi;
+    if constexpr (BF16) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&s01));
+        const float big = __uint_as_float(0x77800000u);                    // 2^112
+        s_lo = pack_bf16x2(f.x * big, f.x * big);
+        s_hi = pack_bf16x2(f.y * big, f.y * big);
+    } else {
+        s_lo = __byte_perm(s01, 0, 0x1010); s_hi = __byte_perm(s01, 0, 0x3232);
+    }
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+    const uint32_t drow = dst + row * 128;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const uint32_t s = c < 2 ? s_lo : s_hi;
+        uint32_t h[4], o[4];
+        cvt_e2m1x8_to_f16x2x4(words[c], h);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            if constexpr (BF16) o[b] = mul_bf16x2(((h[b] >> 3) & 0x0FFF0FFFu) | (h[b] & 0x80008000u), s);
+            else o[b] = mul_f16x2(h[b], s);
+        }
+        const uint32_t addr = drow + (static_cast<uint32_t>((half * 4 + c) ^ (row & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+    }
 }
 
 __host__ __device__ constexpr uint32_t tmem_cols_pow2(uint32_t need) {

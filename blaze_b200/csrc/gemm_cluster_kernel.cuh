@@ -42,6 +42,7 @@ struct ClusterGemmParams {
     uint32_t idesc;
     uint32_t idesc2;         // 384-wide tiles only: the second instruction of a K step (N = 128)
     int sfb_row_blocks;      // 128-row blocks the tiled scale factors of B hold
+    int expand_bf16;         // W4A16: the activations' (and so the expanded weights') format, 1 = bf16, 0 = fp16
     const uint8_t* sfa;      // tiled scale factors of A: [row blocks of 128][sf_katoms][512]
     const uint8_t* sfb;      // tiled scale factors of B
     int sf_katoms;
@@ -91,8 +92,11 @@ struct ClusterGemmConfig {
     static constexpr bool HAS_SF = (KIND == MMA_NVF4);
     // With a single accumulator buffer the epilogue is on the critical path: two sets of four
     // epilogue warps (warps 4-7 and 12-15) then drain alternate column chunks.
+    // W4A16: B arrives as packed NVFP4 (32 bytes per row and stage) plus one 512-byte scale atom;
+    // warps 8-15 expand it into the 16-bit operand tile and report the stage ready.
+    static constexpr bool HAS_EXPAND = (KIND == MMA_W4A16);
     static constexpr int EPI_SETS = (HAS_SF && ACC_BUFS == 1) ? 2 : 1;
-    static constexpr int THREADS = HAS_SF ? (EPI_SETS == 2 ? 512 : 384) : 256;
+    static constexpr int THREADS = HAS_SF ? (EPI_SETS == 2 ? 512 : 384) : (HAS_EXPAND ? 512 : 256);
     static constexpr uint32_t A_BYTES = 128 * 128;
     static constexpr uint32_t B_ROWS = BN / CG;                        // rows of the B tile staged by one CTA
     static constexpr uint32_t B_BYTES = B_ROWS * 128;
@@ -102,7 +106,10 @@ struct ClusterGemmConfig {
     static constexpr uint32_t SFB_BLOCKS = BN / 128;                   // every CTA needs the scales of all BN columns
     static constexpr uint32_t SFA_BYTES = HAS_SF ? SF_BLOCK_BYTES : 0;
     static constexpr uint32_t SFB_BYTES = HAS_SF ? SFB_BLOCKS * SF_BLOCK_BYTES : 0;
-    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+    static constexpr uint32_t PK_BYTES = HAS_EXPAND ? B_ROWS * 32 : 0;              // packed weights of one stage (64 K values per row)
+    static constexpr uint32_t PK_SF_BYTES = HAS_EXPAND ? 1024 : 0;                  // one scale atom (512 bytes), padded to keep stages 1024-aligned
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + PK_BYTES + PK_SF_BYTES;
+    static constexpr uint32_t TX_BYTES = HAS_EXPAND ? A_BYTES + PK_BYTES + 512 : STAGE_BYTES;   // what TMA delivers per stage
     static constexpr uint32_t OUT_BUF_BYTES = 128 * 128;               // 128 rows x 128 bytes
     static constexpr uint32_t OUT_BYTES = 2 * OUT_BUF_BYTES;
     static constexpr uint32_t ACC_COLS = ACC_BUFS * BN;
@@ -114,9 +121,11 @@ struct ClusterGemmConfig {
     static constexpr uint32_t NUM_BARS = (SHARE == 2 ? 5 : 3) * STAGES + 2 * ACC_BUFS;
     static constexpr uint32_t BAR_BYTES = 8 * NUM_BARS + 16;
     static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BYTES + BAR_BYTES + 1024;
-    static constexpr uint32_t READY_COUNT = HAS_SF ? 4 * CG : CG;      // arrivals that make a stage ready for the MMA
+    static constexpr uint32_t READY_COUNT = HAS_SF ? 4 * CG : HAS_EXPAND ? 4 * CG : CG;      // arrivals that make a stage ready for the MMA
     static_assert(CG == 1 || CG == 2, "CTA group of 1 or 2");
     static_assert(SHARE == 1 || (SHARE == 2 && CG == 2), "B sharing needs CTA pairs");
+    static_assert(!HAS_EXPAND || (SHARE == 1 && B_ROWS == 128), "W4A16: every CTA expands one 128-row block of weights per stage");
+    static_assert(STAGE_BYTES % 1024 == 0, "operand tiles must stay 1024-byte aligned");
     static_assert(TMEM_NEED <= 512, "accumulators and scale factors exceed tensor memory");
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared-memory limit");
     static_assert(B_ROWS % 8 == 0 && BN % 128 == 0 && BN <= 384, "tile width");
@@ -212,7 +221,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES - Cfg::B_LOAD_BYTES);
                         mbar_arrive_cluster(partner_ready_bar(stage), partner);    // my stage is free and armed: send
                     } else {
-                        mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+                        mbar_arrive_expect_tx(full_bar(stage), Cfg::TX_BYTES);
                     }
                     if constexpr (Cfg::HAS_SF) {
                         // the small scale-factor copies go first: the helper warps need them before the MMA needs the tiles
@@ -237,6 +246,12 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         }
                         mbar_arrive_expect_tx(bpart_bar(stage), Cfg::B_LOAD_BYTES);
                         tma_load_2d(sb + pair * Cfg::B_LOAD_BYTES, &tm_b, ks * 128, b_row, bpart_bar(stage));
+                    } else if constexpr (Cfg::HAS_EXPAND) {
+                        // packed weights of this CTA's 128 rows (32 bytes = 64 K values per row) and their scale atom
+                        const uint32_t spk = sb + Cfg::B_BYTES;
+                        tma_load_2d(spk, &tm_b, ks * 32, b_row, full_bar(stage));
+                        const size_t rb = static_cast<size_t>(n_tile) * (BN / 128) + prank;
+                        bulk_load_1d(spk + Cfg::PK_BYTES, p.sfb + (rb * p.sf_katoms + static_cast<size_t>(ks)) * 512, 512, full_bar(stage));
                     } else if constexpr (Cfg::WIDE) {
                         // this CTA's share of the 256-wide instruction (128 rows, two boxes of 64) and of the 128-wide one (64 rows)
                         const int n0 = n_tile * BN;
@@ -292,11 +307,11 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                             umma_nvf4_pair(d_tmem, ad, bd, p.idesc, sf_cols + 4 * k, sf_cols + 16 + k * 12, accumulate);
                             umma_nvf4_pair(d_tmem + 256, ad, make_desc_k_sw128(sb + 16384 + k * 32), p.idesc2, sf_cols + 4 * k, sf_cols + 16 + k * 12 + 8, accumulate);
                         } else if constexpr (CG == 1) {
-                            if constexpr (KIND == MMA_F16) umma_f16(d_tmem, ad, bd, p.idesc, accumulate);
+                            if constexpr (KIND == MMA_F16 || KIND == MMA_W4A16) umma_f16(d_tmem, ad, bd, p.idesc, accumulate);
                             else if constexpr (KIND == MMA_F8) umma_f8(d_tmem, ad, bd, p.idesc, accumulate);
                             else umma_nvf4(d_tmem, ad, bd, p.idesc, sf_cols + 4 * k, sf_cols + 16 + k * (BN / 32), accumulate);
                         } else {
-                            if constexpr (KIND == MMA_F16) umma_f16_pair(d_tmem, ad, bd, p.idesc, accumulate);
+                            if constexpr (KIND == MMA_F16 || KIND == MMA_W4A16) umma_f16_pair(d_tmem, ad, bd, p.idesc, accumulate);
                             else if constexpr (KIND == MMA_F8) umma_f8_pair(d_tmem, ad, bd, p.idesc, accumulate);
                             else umma_nvf4_pair(d_tmem, ad, bd, p.idesc, sf_cols + 4 * k, sf_cols + 16 + k * (BN / 32), accumulate);
                         }
@@ -313,7 +328,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         __syncwarp();
     } else if (warp == 2) {
         // ----------------------------------- relay for kinds without scale factors (every CTA)
-        if constexpr (!Cfg::HAS_SF) {
+        if constexpr (!Cfg::HAS_SF && !Cfg::HAS_EXPAND) {
             if (lane == 0) {
                 int stage = 0; uint32_t phase = 0;
                 bool ok = true;
@@ -467,6 +482,36 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
         if (epi_tid == 0 && eset == 0) { BLZ_T_STORE(5, t_wait); BLZ_T_STORE(6, t_work); BLZ_T_STORE(7, BLZ_T_NOW() - t_begin); }
         if (epi_tid == 0) tma_store_wait_all<0>();     // staging memory must outlive the last store's reads
+    } else if (Cfg::HAS_EXPAND && warp >= 8) {
+        // ------------- W4A16: packed weights + block scales -> 16-bit operand tile (warps 8-15)
+        if constexpr (Cfg::HAS_EXPAND) {
+            // Two groups of four warps take alternate stages (one stage's expansion is a chain of
+            // barrier poll, loads, conversions, stores and a fence that outlasts the stage's MMAs);
+            // inside a group every thread expands one weight row.
+            const int eg = (warp - 8) >> 2;
+            const int row = (threadIdx.x - 256) & 127;
+            uint32_t n = 0;                                  // stages seen so far, over all tiles of this CTA
+            bool ok = true;
+            for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
+                for (int ks = 0; ks < p.k_stages; ++ks, ++n) {
+                    if ((n & 1u) != static_cast<uint32_t>(eg)) continue;
+                    const int stage = static_cast<int>(n % STAGES);
+                    // landed = this stage's buffers were free (the producer waited for that) and TMA filled them
+                    if (!mbar_wait_warp(full_bar(stage), (n / STAGES) & 1u, abort_flag)) {
+                        atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
+                    }
+                    const uint8_t* spk = gen_base + stage * Cfg::STAGE_BYTES + Cfg::A_BYTES + Cfg::B_BYTES;
+                    const uint32_t sb = base + stage * Cfg::STAGE_BYTES + Cfg::A_BYTES;
+                    if (p.expand_bf16) { expand_w4_stage<true>(spk, spk + Cfg::PK_BYTES, sb, 2 * row); expand_w4_stage<true>(spk, spk + Cfg::PK_BYTES, sb, 2 * row + 1); }
+                    else { expand_w4_stage<false>(spk, spk + Cfg::PK_BYTES, sb, 2 * row); expand_w4_stage<false>(spk, spk + Cfg::PK_BYTES, sb, 2 * row + 1); }
+                    fence_proxy_async_smem();        // the tensor core reads the tile through the async proxy
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (CG == 1) mbar_arrive(ready_bar(stage)); else mbar_arrive_cluster(ready_bar(stage), leader_rank);
+                    }
+                }
+            }
+        }
     } else if (warp >= 8 && warp < 12) {
         // -------------------------------- NVFP4: scale factors smem -> registers -> tensor memory
         if constexpr (Cfg::HAS_SF) {

@@ -387,6 +387,7 @@ def test_nvfp4_config5_sampled(oracle, cuda_device):
 
 @pytest.mark.parametrize("kind,shape", [
     ("w4a16_bf16", (129, 256, 512)), ("w4a16_f16", (200, 328, 160)), ("w4a16_bf16", (512, 1024, 2048)),
+    ("w4a16_f16", (1024, 2304, 1056)), ("w4a16_bf16", (2100, 520, 544)),          # pair tiles, ragged K stage; M > 2048: 16-bit copy first
     # M <= 64: the weight-stream kernel that expands the packed weights into tensor memory
     ("w4a16_f16", (1, 128, 64)), ("w4a16_bf16", (1, 256, 512)), ("w4a16_f16", (16, 328, 160)), ("w4a16_bf16", (40, 1000, 1056)),
     ("w4a16_bf16", (64, 4096, 4096)), ("w4a16_f16", (8, 4096, 11008)), ("w4a16_bf16", (32, 12288, 4096)),
@@ -408,6 +409,8 @@ def test_w4a16(oracle, cuda_device, kind, shape):
     plan = GemmPlan(kind, M, N, K, bits16_to_torch(A, act, cuda_device), _u8(bd, cuda_device), B_sf=_u8(bsf, cuda_device), b_scale=gb, out_dtype=act)
     if M <= 128:
         assert plan.info()["variant"] == 3 and plan.info()["launches"] == 1    # one kernel, no expanded copy of the weights
+    elif M <= 2048:
+        assert plan.info()["launches"] == 1 and plan.info()["workspace_bytes"] < N * K   # tiled kernel expands in shared memory
     _run(plan, C)
     assert_close(torch_to_f32(C, oracle, act), want, "w4a16 %s %s" % (kind, shape))
     plan.destroy()
