@@ -151,6 +151,9 @@ struct blz_gemm_plan {
     void* own_sfa = nullptr;
     void* own_sfb = nullptr;
     void* own_w16 = nullptr;      // W4A16: weights expanded to 16 bit, refreshed by every execute
+    float* own_partial = nullptr; // split-K of the tiled kernel: [splits][m_tiles*128][partial_pitch] fp32
+    int split_k = 1;
+    int64_t partial_pitch = 0, partial_rows = 0;
     int* status = nullptr;
     int64_t owned_bytes = 0;
     CUtensorMap tm_a{}, tm_b{};
@@ -309,6 +312,31 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1, bool wide = fa
     cp.group_m = env_int("BLZ_GROUP_M", cp.group_m);
     if (cp.group_m < 1) cp.group_m = 1;
     cp.k_stages = static_cast<int>(ceil_div(rb, 128));
+    // Few 128x128 tiles and a long K (decode-like N with a prefill-like M): split K over up to four
+    // CTAs per tile.  Split s of M tile m runs as M tile s * m_tiles + m and stores fp32 partial
+    // sums to its own row block of a scratch matrix; a small second kernel adds the splits in order
+    // and applies the epilogue.
+    cp.m_tiles_real = cp.m_tiles; cp.split_k = 1; cp.k_per_split = cp.k_stages;
+    if (cg == 1 && share == 1 && !wide) {
+        int split = 1;
+        const int64_t tiles1 = static_cast<int64_t>(cp.m_tiles) * cp.n_tiles;
+        while (split < 4 && tiles1 * split * 2 <= p->num_sms && cp.k_stages / (split * 2) >= 16) split *= 2;
+        split = env_int("BLZ_TILE_SPLIT_K", split);
+        while (split > 1 && (split - 1) * static_cast<int>(ceil_div(cp.k_stages, split)) >= cp.k_stages) --split;   // no empty split
+        if (split > 1) {
+            p->split_k = split;
+            p->partial_rows = static_cast<int64_t>(cp.m_tiles) * 128;
+            p->partial_pitch = round_up(d.N, 4);
+            void* mem = nullptr;
+            blz_status st = dev_alloc(p, &mem, static_cast<int64_t>(split) * p->partial_rows * p->partial_pitch * 4, false);
+            if (st) return st;
+            p->own_partial = static_cast<float*>(mem);
+            cp.split_k = split;
+            cp.k_per_split = static_cast<int>(ceil_div(cp.k_stages, split));
+            cp.m_tiles = cp.m_tiles_real * split;
+            p->launches += 1;
+        }
+    }
     const uint32_t fmt = d.kind == BLZ_GEMM_BF16 || d.kind == BLZ_GEMM_W4A16_BF16 ? 1u : 0u;
     cp.idesc2 = make_idesc_nvf4(tile_m, 128);
     cp.sfb_row_blocks = static_cast<int>(sf_row_blocks(d.N));
@@ -491,6 +519,35 @@ blz_status launch_cluster(blz_gemm_plan* p, int n_dst, void* const* dst, int64_t
     }
     const int eb = elem_bytes_out(d.out_dtype);
     ClusterGemmParams cp = p->cp;
+    if (p->split_k > 1) {
+        // K split: the GEMM kernel writes raw fp32 partial sums of every split into the plan's scratch
+        // matrix (its "M" is all splits' row blocks), the second kernel finishes into C.
+        if (n_dst != 1) return BLZ_ERR_UNSUPPORTED;
+        const int64_t rows_all = p->partial_rows * p->split_k;
+        cp.M = static_cast<int>(rows_all);
+        cp.epi.C = p->own_partial; cp.epi.bias = nullptr; cp.epi.residual = nullptr;
+        cp.epi.ldc = p->partial_pitch; cp.epi.ldr = p->partial_pitch;
+        cp.epi.alpha = 1.0f; cp.epi.mode = EPI_NONE; cp.epi.out_type = OUT_F32; cp.epi.vec_ok = 1;
+        cp.use_tma_store = 1; cp.n_dst = 1;
+        if (p->out_n != -1) {
+            blz_status s = encode_map(&p->out.m[0], p->own_partial, static_cast<uint64_t>(d.N) * 4, static_cast<uint64_t>(rows_all),
+                                      static_cast<uint64_t>(p->partial_pitch) * 4, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+            if (s) return s;
+            p->out_n = -1;                          // the cached map describes the scratch matrix
+        }
+        cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[1];
+        launch_config_cluster(p, cfg, attr, stream);
+        void* cargs[4] = {&p->tm_a, &p->tm_b, &p->out, &cp};
+        BLZ_CUDA(cudaLaunchKernelExC(&cfg, p->cc.fn, cargs));
+        EpilogueParams e;
+        e.C = static_cast<uint8_t*>(dst[0]) + col_offset * eb;
+        e.bias = d.bias; e.residual = d.residual; e.ldc = ld; e.ldr = ld;
+        e.alpha = d.a_scale * d.b_scale; e.mode = d.epilogue; e.out_type = d.out_dtype; e.vec_ok = 0;
+        const int64_t groups = static_cast<int64_t>(d.M) * ceil_div(d.N, 4);
+        splitk_reduce_kernel<<<grid_for(groups, 256), 256, 0, stream>>>(p->own_partial, p->split_k, p->partial_rows, p->partial_pitch, d.M, d.N, e);
+        BLZ_CUDA(cudaGetLastError());
+        return BLZ_OK;
+    }
     cp.epi.C = static_cast<uint8_t*>(dst[0]) + col_offset * eb;
     cp.epi.bias = d.bias; cp.epi.residual = d.residual;
     cp.epi.ldc = ld; cp.epi.ldr = ld;
@@ -651,7 +708,7 @@ blz_status blz_gemm_execute_gather(blz_gemm_plan* p, int32_t n_dst, void* const*
     if (p->variant == BLZ_VARIANT_DECODE) return BLZ_ERR_UNSUPPORTED;
     const blz_gemm_desc& d = p->desc;
     if (ld_total < col_offset + d.N || col_offset < 0) return BLZ_ERR_INVALID_ARGUMENT;
-    if (d.epilogue == BLZ_EPI_RESIDUAL_ADD) return BLZ_ERR_UNSUPPORTED;
+    if (d.epilogue == BLZ_EPI_RESIDUAL_ADD || p->split_k > 1) return BLZ_ERR_UNSUPPORTED;
     for (int i = 0; i < n_dst; ++i) if (!dst[i]) return BLZ_ERR_INVALID_ARGUMENT;
     return launch_cluster(p, n_dst, dst, ld_total, col_offset, static_cast<cudaStream_t>(stream_v));
 }
@@ -698,7 +755,7 @@ blz_status blz_gemm_plan_info(const blz_gemm_plan* p, blz_plan_info* info) {
         info->grid = p->grid; info->smem_bytes = p->decode_smem; info->tmem_cols = p->decode_tmem;
     } else {
         info->tile_m = 128 * p->cc.cg * p->cc.share; info->tile_n = p->cc.bn;
-        info->stages = p->cc.stages; info->split_k = 1;
+        info->stages = p->cc.stages; info->split_k = p->split_k;
         info->grid = p->grid; info->smem_bytes = p->cc.smem; info->tmem_cols = p->cc.tmem_cols;
     }
     info->launches = p->launches;
@@ -708,7 +765,7 @@ blz_status blz_gemm_plan_info(const blz_gemm_plan* p, blz_plan_info* info) {
 
 blz_status blz_gemm_plan_destroy(blz_gemm_plan* p) {
     if (!p) return BLZ_OK;
-    cudaFree(p->own_b); cudaFree(p->own_sfa); cudaFree(p->own_sfb); cudaFree(p->own_w16);
+    cudaFree(p->own_b); cudaFree(p->own_sfa); cudaFree(p->own_sfb); cudaFree(p->own_w16); cudaFree(p->own_partial);
     cudaFree(p->status);
     (void)cudaGetLastError();
     delete p;

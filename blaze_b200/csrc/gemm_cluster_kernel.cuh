@@ -39,6 +39,9 @@ struct ClusterGemmParams {
     int m_tiles, n_tiles;    // tiles of (128*CG) x BN
     int group_m;             // tile rasterisation: bands of this many M tiles are walked N-first
     int k_stages;            // ceil(K bytes per row / 128)
+    int split_k;             // K splits: split s of M tile m is scheduled as M tile s * m_tiles_real + m and writes its
+    int k_per_split;         //   fp32 partial sums to that row block of a scratch matrix; stages per split
+    int m_tiles_real;        // M tiles of the problem itself (m_tiles counts all splits)
     uint32_t idesc;
     uint32_t idesc2;         // 384-wide tiles only: the second instruction of a K step (N = 128)
     int sfb_row_blocks;      // 128-row blocks the tiled scale factors of B hold
@@ -64,6 +67,15 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
     const int in_band = tile - band * band_tiles;
     m_tile = first_m + in_band % rows;
     n_tile = in_band / rows;
+}
+
+// K range of a scheduled tile and the problem's own M tile behind it (see split_k above).
+template <typename P>
+__device__ __forceinline__ void tile_k_range(const P& p, int m_ext, int& m_tile, int& ks0, int& ks1) {
+    const int sidx = m_ext / p.m_tiles_real;
+    m_tile = m_ext - sidx * p.m_tiles_real;
+    ks0 = sidx * p.k_per_split;
+    ks1 = min(p.k_stages, ks0 + p.k_per_split);
 }
 
 // Where the epilogue stores a tile.  Normally one map (C).  For the fused GEMM + all-gather every
@@ -203,10 +215,12 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
             for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
                 int m_tile, n_tile;
-                tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_tile, n_tile);
+                int m_ext, ks0, ks1;
+                tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_ext, n_tile);
+                tile_k_range(p, m_ext, m_tile, ks0, ks1);
                 const int a_row = ((m_tile * SHARE + static_cast<int>(pair)) * CG + static_cast<int>(prank)) * 128;
                 const int b_row = n_tile * BN + static_cast<int>(prank) * static_cast<int>(Cfg::B_ROWS) + static_cast<int>(pair) * static_cast<int>(Cfg::B_LOAD_ROWS);
-                for (int ks = 0; ks < p.k_stages; ++ks) {
+                for (int ks = ks0; ks < ks1; ++ks) {
                     [[maybe_unused]] const long long te = BLZ_T_NOW();
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
                         atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_PRODUCER); *abort_flag = 1; ok = false; break;
@@ -286,7 +300,10 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 BLZ_T_ADD(t_wait_acc, ta);
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int ks = 0; ks < p.k_stages; ++ks) {
+                int ks0, ks1;
+                if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
+                else { int m_e, n_e, m_r; tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_e, n_e); tile_k_range(p, m_e, m_r, ks0, ks1); }
+                for (int ks = ks0; ks < ks1; ++ks) {
                     [[maybe_unused]] const long long tr = BLZ_T_NOW();
                     if (!mbar_wait(ready_bar(stage), phase, abort_flag)) {
                         atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
@@ -301,7 +318,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     for (int k = 0; k < 4; ++k) {
                         const uint64_t ad = make_desc_k_sw128(sa + k * 32);
                         const uint64_t bd = make_desc_k_sw128(sb + k * 32);
-                        const uint32_t accumulate = (ks | k) != 0 ? 1u : 0u;
+                        const uint32_t accumulate = (ks != ks0 || k != 0) ? 1u : 0u;
                         if constexpr (Cfg::WIDE) {
                             // columns [0, 256) and [256, 384) of the tile; scale columns of one K atom: 8 + 4
                             umma_nvf4_pair(d_tmem, ad, bd, p.idesc, sf_cols + 4 * k, sf_cols + 16 + k * 12, accumulate);
@@ -333,7 +350,10 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 int stage = 0; uint32_t phase = 0;
                 bool ok = true;
                 for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
-                    for (int ks = 0; ks < p.k_stages; ++ks) {
+                    int ks0, ks1;
+                    if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
+                else { int m_e, n_e, m_r; tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_e, n_e); tile_k_range(p, m_e, m_r, ks0, ks1); }
+                    for (int ks = ks0; ks < ks1; ++ks) {
                         bool landed = mbar_wait(full_bar(stage), phase, abort_flag);
                         if constexpr (SHARE == 2) landed = landed && mbar_wait(bpart_bar(stage), phase, abort_flag);
                         if (!landed) {
@@ -353,7 +373,10 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 int stage = 0; uint32_t phase = 0;
                 bool ok = true;
                 for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
-                    for (int ks = 0; ks < p.k_stages; ++ks) {
+                    int ks0, ks1;
+                    if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
+                else { int m_e, n_e, m_r; tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_e, n_e); tile_k_range(p, m_e, m_r, ks0, ks1); }
+                    for (int ks = ks0; ks < ks1; ++ks) {
                         if (!mbar_wait(bpart_bar(stage), phase, abort_flag)) {
                             atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_PRODUCER); *abort_flag = 1; ok = false; break;
                         }
@@ -398,6 +421,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             const int r_local = q * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
             if (p.use_tma_store) {
+                if constexpr (Cfg::EPI_SETS == 2) {
+                // (single accumulator buffer: the epilogue is on the tensor pipe's critical path)
                 // The accumulator reads run one chunk ahead of the staging: the columns of chunk i+1
                 // are taken into registers before the store of chunk i is even issued, and the
                 // accumulator goes back to the MMA role right after the last read -- no wait for a
@@ -464,6 +489,63 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     }
                     obuf ^= 1;
                 }
+                } else {
+                // two accumulator buffers: the epilogue overlaps the next tile's MMAs; chunk by chunk
+                for (int c0 = eset * chunk_cols; c0 < BN; c0 += chunk_cols * Cfg::EPI_SETS) {
+                    // One set: the two staging buffers alternate, buffer `obuf` was handed to a TMA
+                    // store two chunks ago.  Two sets: each set owns one buffer and waits for its own
+                    // previous store.  Either way: wait until that store has finished reading it.
+                    if (epi_tid == 0) { if constexpr (Cfg::EPI_SETS == 2) tma_store_wait_read<0>(); else tma_store_wait_read<1>(); }
+                    named_barrier_sync(bar_id, 128);
+                    const uint32_t sbuf = out_base + (Cfg::EPI_SETS == 2 ? eset : obuf) * Cfg::OUT_BUF_BYTES;
+                    if (ok) {
+                        for (int h = 0; h < chunk_cols; h += 32) {
+                            uint32_t acc[32];
+                            tmem_ld32(t_row + c0 + h, acc);
+                            tmem_ld_wait();
+                            if (c0 + chunk_cols * Cfg::EPI_SETS >= BN && h + 32 >= chunk_cols) {
+                                // that was this warp's last read of the accumulator: hand it back to the
+                                // MMA role now, the arithmetic and the stores of this chunk need it no more
+                                tc_fence_before_sync();
+                                __syncwarp();
+                                if (lane == 0) {
+                                    if constexpr (CG == 1) mbar_arrive(acc_empty_bar(buf)); else mbar_arrive_cluster(acc_empty_bar(buf), leader_rank);
+                                }
+                            }
+                            const int col = n_tile * BN + c0 + h;
+                            float v[32];
+                            epilogue_math32(p.epi, acc, v, row0 + r_local, col, p.M, p.N);
+                            // 128-byte swizzle: 16-byte unit j of row r lives at unit (j ^ (r % 8))
+                            const uint32_t srow = sbuf + r_local * 128;
+                            if (out_esize == 4) {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    const uint32_t dst = srow + (((h / 4 + j) ^ (r_local & 7)) << 4);
+                                    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3]) : "memory");
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    uint32_t w[4];
+#pragma unroll
+                                    for (int t = 0; t < 4; ++t) w[t] = pack2_out(p.epi.out_type, v[8 * j + 2 * t], v[8 * j + 2 * t + 1]);
+                                    const uint32_t dst = srow + (((h / 8 + j) ^ (r_local & 7)) << 4);
+                                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                                }
+                            }
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    named_barrier_sync(bar_id, 128);
+                    if (epi_tid == 0) {
+                        if (ok) {
+                            for (int d = 0; d < p.n_dst; ++d) tma_store_2d(&out.m[d], sbuf, (n_tile * BN + c0) * out_esize, row0);
+                        }
+                        tma_store_commit();
+                    }
+                    obuf ^= 1;
+                }
+                }
             } else if (ok) {
 #pragma unroll 1
                 for (int c0 = eset * 32; c0 < BN; c0 += 32 * Cfg::EPI_SETS) {
@@ -493,7 +575,10 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             uint32_t n = 0;                                  // stages seen so far, over all tiles of this CTA
             bool ok = true;
             for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
-                for (int ks = 0; ks < p.k_stages; ++ks, ++n) {
+                int ks0, ks1;
+                if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
+                else { int m_e, n_e, m_r; tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_e, n_e); tile_k_range(p, m_e, m_r, ks0, ks1); }
+                for (int ks = ks0; ks < ks1; ++ks, ++n) {
                     if ((n & 1u) != static_cast<uint32_t>(eg)) continue;
                     const int stage = static_cast<int>(n % STAGES);
                     // landed = this stage's buffers were free (the producer waited for that) and TMA filled them
@@ -520,7 +605,10 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             [[maybe_unused]] uint32_t g = 0;       // stages handled so far
             bool ok = true;
             for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
-                for (int ks = 0; ks < p.k_stages; ++ks) {
+                int ks0, ks1;
+                if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
+                else { int m_e, n_e, m_r; tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_e, n_e); tile_k_range(p, m_e, m_r, ks0, ks1); }
+                for (int ks = ks0; ks < ks1; ++ks) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
                         atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
                     }

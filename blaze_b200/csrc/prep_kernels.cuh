@@ -182,4 +182,46 @@ __global__ void dequant_nvfp4_kernel(const uint8_t* __restrict__ data, const uin
     }
 }
 
+// ---- split-K, tiled kernel: C = epilogue(alpha * sum_s partial[s]) ; partial: [splits][rows_per_split][pitch] fp32,
+//      summed in split order (fixed, so results do not depend on timing).  One thread per 4 columns.
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, long long rows_per_split, long long pitch,
+                                     int M, int N, EpilogueParams e) {
+    const long long groups = (static_cast<long long>(N) + 3) / 4, total = static_cast<long long>(M) * groups;
+    const int esize = e.out_type == OUT_F32 ? 4 : 2;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long m = i / groups;
+        const int n0 = static_cast<int>(i % groups) * 4;
+        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int sidx = 0; sidx < splits; ++sidx) {
+            const float4 t = *reinterpret_cast<const float4*>(partial + (sidx * rows_per_split + m) * pitch + n0);
+            v[0] += t.x; v[1] += t.y; v[2] += t.z; v[3] += t.w;
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const int n = n0 + t;
+            v[t] *= e.alpha;
+            if (n < N && e.mode != EPI_NONE) {
+                if ((e.mode == EPI_BIAS || e.mode == EPI_BIAS_SILU) && e.bias != nullptr)
+                    v[t] += e.out_type == OUT_BF16 ? load_out_elem<OUT_BF16>(e.bias, n) : e.out_type == OUT_F16 ? load_out_elem<OUT_F16>(e.bias, n) : load_out_elem<OUT_F32>(e.bias, n);
+                if (e.mode == EPI_SILU || e.mode == EPI_BIAS_SILU) v[t] = silu_f32(v[t]);
+                if (e.mode == EPI_RESIDUAL && e.residual != nullptr) {
+                    const long long roff = m * e.ldr + n;
+                    v[t] += e.out_type == OUT_BF16 ? load_out_elem<OUT_BF16>(e.residual, roff) : e.out_type == OUT_F16 ? load_out_elem<OUT_F16>(e.residual, roff) : load_out_elem<OUT_F32>(e.residual, roff);
+                }
+            }
+        }
+        uint8_t* dst = reinterpret_cast<uint8_t*>(e.C) + (m * e.ldc + n0) * esize;
+        const bool whole = n0 + 4 <= N && (reinterpret_cast<uintptr_t>(dst) & (esize == 4 ? 15u : 7u)) == 0;
+        if (e.out_type == OUT_F32) {
+            if (whole) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+            else for (int t = 0; t < 4 && n0 + t < N; ++t) reinterpret_cast<float*>(dst)[t] = v[t];
+        } else {
+            const uint32_t w0 = pack2_out(e.out_type, v[0], v[1]), w1 = pack2_out(e.out_type, v[2], v[3]);
+            if (whole) *reinterpret_cast<uint2*>(dst) = make_uint2(w0, w1);
+            else for (int t = 0; t < 4 && n0 + t < N; ++t) reinterpret_cast<uint16_t*>(dst)[t] = static_cast<uint16_t>((t < 2 ? w0 : w1) >> (16 * (t & 1)));
+        }
+    }
+}
+
 }  // namespace blz

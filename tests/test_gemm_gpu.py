@@ -410,7 +410,8 @@ def test_w4a16(oracle, cuda_device, kind, shape):
     if M <= 128:
         assert plan.info()["variant"] == 3 and plan.info()["launches"] == 1    # one kernel, no expanded copy of the weights
     elif M <= 2048:
-        assert plan.info()["launches"] == 1 and plan.info()["workspace_bytes"] < N * K   # tiled kernel expands in shared memory
+        # the tiled kernel expands in shared memory: no 16-bit copy; a second launch only to add K splits
+        assert plan.info()["launches"] == (2 if plan.info()["split_k"] > 1 else 1)
     _run(plan, C)
     assert_close(torch_to_f32(C, oracle, act), want, "w4a16 %s %s" % (kind, shape))
     plan.destroy()
@@ -606,6 +607,55 @@ def test_set_a_other_kinds(oracle, cuda_device, kind, M):
     plan.set_a(d2, None, s2 if kind == "fp8" else 0.0)
     _run(plan, C)
     assert_close(torch_to_f32(C, oracle, act), oracle.widen(oracle.narrow(ref(a2, s2), act), act), "%s M=%d after set_a" % (kind, M))
+    plan.destroy()
+
+
+@pytest.mark.parametrize("kind,shape,mode", [
+    ("bf16", (128, 512, 8192), "none"), ("bf16", (200, 300, 4104), "bias_silu"), ("fp8", (100, 384, 8192), "residual"),
+    ("nvfp4", (128, 512, 16384), "none"), ("nvfp4", (300, 264, 8224), "bias"), ("w4a16_f16", (200, 384, 4096), "none"),
+    ("w4a16_bf16", (130, 520, 4128), "residual"),
+])
+def test_tiled_split_k(oracle, cuda_device, kind, shape, mode):
+    """Few 128x128 tiles and a long K: the tiled kernel splits K over several CTAs per tile (fp32
+    partial sums in a scratch matrix, summed in split order by a second kernel that also applies
+    the epilogue); ragged M / N / K, every kind."""
+    from blaze_b200 import GemmPlan
+    M, N, K = shape
+    rng = np.random.default_rng(99)
+    out = "f16" if kind == "w4a16_f16" else "bf16"
+    kw = {}
+    if kind == "bf16":
+        A, Bt = _dense_inputs(oracle, "bf16", M, N, K, scale=0.25)
+        acc, alpha = oracle.gemm_dense16(A, Bt, "bf16"), 1.0
+        args = (bits16_to_torch(A, "bf16", cuda_device), bits16_to_torch(Bt, "bf16", cuda_device))
+    elif kind == "fp8":
+        qa, da, qb, db = _fp8_inputs(oracle, M, N, K)
+        acc, alpha = oracle.gemm_f32(oracle.e4m3_to_f32(qa), oracle.e4m3_to_f32(qb)), float(np.float32(da) * np.float32(db))
+        args = (_u8(qa, cuda_device), _u8(qb, cuda_device)); kw = dict(a_scale=da, b_scale=db)
+    elif kind == "nvfp4":
+        (ad, asf, ga), (bd, bsf, gb) = _nvfp4_inputs(oracle, M, N, K)
+        acc, alpha = oracle.gemm_nvfp4(ad, asf, ga, bd, bsf, gb)
+        args = (_u8(ad, cuda_device), _u8(bd, cuda_device)); kw = dict(A_sf=_u8(asf, cuda_device), B_sf=_u8(bsf, cuda_device), a_scale=ga, b_scale=gb)
+    else:
+        enc = oracle.f32_to_f16 if out == "f16" else oracle.f32_to_bf16
+        A = enc(rng.standard_normal((M, K)).astype(np.float32))
+        bd, bsf, gb = oracle.quantize_nvfp4((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
+        acc, alpha = oracle.gemm_w4a16(A, out, bd, bsf, gb)
+        args = (bits16_to_torch(A, out, cuda_device), _u8(bd, cuda_device)); kw = dict(B_sf=_u8(bsf, cuda_device), b_scale=gb)
+    bias_n = oracle.widen(oracle.narrow(rng.standard_normal(N).astype(np.float32), out), out)
+    res_n = oracle.widen(oracle.narrow(rng.standard_normal((M, N)).astype(np.float32), out), out)
+    want32 = oracle.epilogue(acc, alpha, bias=bias_n if "bias" in mode else None, residual=res_n if mode == "residual" else None, mode=mode)
+    want = oracle.widen(oracle.narrow(want32, out), out)
+    C = _out_tensor(M, N, out, cuda_device)
+    plan = GemmPlan(kind, M, N, K, *args, out_dtype=out, epilogue=mode, variant="128x128",
+                    bias=bits16_to_torch(oracle.narrow(bias_n, out), out, cuda_device) if "bias" in mode else None,
+                    residual=bits16_to_torch(oracle.narrow(res_n, out), out, cuda_device) if mode == "residual" else None, **kw)
+    assert plan.info()["split_k"] > 1, plan.info()
+    _run(plan, C)
+    first = C.clone()
+    assert_close(torch_to_f32(C, oracle, out), want, "tiled split-K %s %s %s %s" % (kind, shape, mode, plan.info()))
+    _run(plan, C)
+    assert _torch().equal(first, C), "split-K result changed between two runs"
     plan.destroy()
 
 
