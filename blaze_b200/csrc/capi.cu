@@ -651,7 +651,10 @@ blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_p
     // The 128-row forms of the FP8 and 16-bit kernels exist (explicit variant) but lose to the tiled
     // kernel: both re-read the activations once per 128 weight rows and are bound by L2 -> SM traffic.
     const int decode_max_m = desc->kind == BLZ_GEMM_NVFP4 ? 64 : 128;
-    const int decode_auto_m = w4a16 ? 128 : 64;
+    // ... unless the tiled kernel would split K four ways (few tiles, long K): measured 27 against 42 us
+    // for 128 x 4096 x 11008
+    const bool w4_tiled_split = w4a16 && desc->M > 64 && ceil_div(desc->N, 128) * 4 <= p->num_sms && desc->K >= 8192;
+    const int decode_auto_m = (w4a16 && !w4_tiled_split) ? 128 : 64;
     const bool want_decode = desc->variant == BLZ_VARIANT_DECODE || (desc->variant == BLZ_VARIANT_AUTO && desc->M <= decode_auto_m);
     // M > 128: up to 2048 rows the tiled kernel expands the packed weights stage by stage in shared
     // memory (no 16-bit copy; every CTA re-expands the tiles it uses).  Beyond that, expanding all

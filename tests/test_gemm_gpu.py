@@ -407,7 +407,7 @@ def test_w4a16(oracle, cuda_device, kind, shape):
     want = oracle.widen(oracle.narrow(oracle.epilogue(acc, alpha), act), act)
     C = _out_tensor(M, N, act, cuda_device)
     plan = GemmPlan(kind, M, N, K, bits16_to_torch(A, act, cuda_device), _u8(bd, cuda_device), B_sf=_u8(bsf, cuda_device), b_scale=gb, out_dtype=act)
-    if M <= 128:
+    if M <= 128 and not (M > 64 and K >= 8192 and -(-N // 128) * 4 <= 148):
         assert plan.info()["variant"] == 3 and plan.info()["launches"] == 1    # one kernel, no expanded copy of the weights
     elif M <= 2048:
         # the tiled kernel expands in shared memory: no 16-bit copy; a second launch only to add K splits
