@@ -188,6 +188,46 @@ def time_steps(fn, steps, warmup, flusher, barrier=None):
     return sum(times) / steps, times
 
 
+def run_gate_up(M, N, K, device, steps, warmup, flusher):
+    """Llama-7B MLP entry, W4A16 bf16: silu(x Wg) * (x Wu) as ONE GEMM with the swiglu epilogue, beside the
+    same result from two GEMMs (the gate one with SiLU) and one elementwise multiply."""
+    import torch
+    from blaze_b200 import GemmPlan, interleave_gate_up
+    kg, _ = make_operands("w4a16_bf16", M, N, K, device, seed_b=123)
+    ku, _ = make_operands("w4a16_bf16", M, N, K, device, seed_b=124)
+    A = kg["A"]
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+    tmp = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+    p_g = GemmPlan("w4a16_bf16", M, N, K, A, kg["B"], B_sf=kg["B_sf"], b_scale=kg["b_scale"], b_sf_layout="tiled", epilogue="silu")
+    p_u = GemmPlan("w4a16_bf16", M, N, K, A, ku["B"], B_sf=ku["B_sf"], b_scale=ku["b_scale"], b_sf_layout="tiled")
+
+    def separate():
+        p_g.execute(tmp); p_u.execute(out); out.mul_(tmp)
+
+    ms_sep, _ = time_steps(separate, steps, warmup, flusher)
+    p_g.check(); p_u.check(); p_g.destroy(); p_u.destroy()
+    # one kernel: rows interleaved in groups of 16; the tiled scale layout is per 128 rows, so the
+    # row-major scales are interleaved and then tiled by the plan
+    from blaze_b200 import quantize_nvfp4
+    sf = []
+    for seed in (123, 124):
+        g = torch.Generator(device=device).manual_seed(seed)
+        W = torch.randn((N, K), generator=g, device=device) * 0.02
+        sf.append(quantize_nvfp4(W, tiled=False)[1]); del W
+    B2 = interleave_gate_up(kg["B"], ku["B"], 16 * K // 2)
+    S2 = interleave_gate_up(sf[0], sf[1], 16 * K // 16)
+    p = GemmPlan("w4a16_bf16", M, 2 * N, K, A, B2, B_sf=S2, b_scale=kg["b_scale"], b_scale2=ku["b_scale"], epilogue="swiglu")
+    fused = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+    ms_fused, _ = time_steps(lambda: p.execute(fused), steps, warmup, flusher)
+    p.check()
+    info = p.info()
+    p.destroy()
+    diff = (fused.float() - out.float()).abs().max().item()
+    flops = 2.0 * M * (2 * N) * K
+    return {"M": M, "N": N, "K": K, "one_kernel_ms": ms_fused, "one_kernel_tflops": flops / (ms_fused * 1e-3) / 1e12,
+            "two_gemms_and_multiply_ms": ms_sep, "max_abs_diff": diff, "kernel": info, "launches": steps * info["launches"]}
+
+
 def run_gemm_workload(kind, M, N, K, device, steps, warmup, flusher, out_dtype="bf16", barrier=None, variant="auto", seed_b=123):
     import torch
     from blaze_b200 import GemmPlan
@@ -423,11 +463,11 @@ def main() -> int:
             dec = run_decode(device, args.steps, args.warmup, peaks, kind=args.decode_kind)
         worst = min(dec, key=lambda d: d["hbm_gbs"])
         best = max(dec, key=lambda d: d["hbm_gbs"])
-        line = {"metric": "nvfp4_decode_hbm_gbs", "value": best["hbm_gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": best["us_per_gemm"] / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4",
+        line = {"metric": "%s_decode_hbm_gbs" % args.decode_kind, "value": best["hbm_gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": best["us_per_gemm"] / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.decode_kind,
                 "data": "synthetic", "config": {"workload": "%s decode M=16, Llama-7B projections (BASELINE configs[2])" % args.decode_kind, "l2": "weight copies > 2x L2 cycled in one CUDA graph"},
                 "roofline": {"bound": "hbm", "achieved": best["hbm_gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": best["hbm_gbs"] / peaks["hbm_gbs"],
-                             "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get("decode_%dx%d" % (best["N"], best["K"])), "peak_source": peaks["source"]},
+                             "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get("decode_%dx%d" % (best["N"], best["K"])) if args.decode_kind == "nvfp4" else None, "peak_source": peaks["source"]},
                 "shapes": dec, "worst": worst, "clocks": clk.summary(), "gpu_launches": sum(d["launches"] for d in dec)}
         print(json.dumps(line))
         return 0
@@ -540,6 +580,14 @@ def main() -> int:
                 others["%s_decode_M16" % dk] = run_decode(device, 5, 3, peaks, kind=dk)
             except Exception as ex:
                 others["%s_decode_M16" % dk] = {"error": str(ex)[:200]}
+        for m2 in (512, 2048):
+            try:
+                gu = run_gate_up(m2, 11008, 4096, device, 10, 3, flusher)
+                launches += gu.pop("launches")
+                others["w4a16_bf16_gate_up_M%d" % m2] = gu
+                torch.cuda.empty_cache()
+            except Exception as ex:
+                others["w4a16_bf16_gate_up_M%d" % m2] = {"error": str(ex)[:200]}
         line["others"] = others
 
     if rank == 0 and world == 1 and not args.no_cpu:

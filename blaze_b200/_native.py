@@ -16,7 +16,7 @@ LIB_PATH = os.environ.get("BLAZE_B200_LIBRARY") or os.path.join(_HERE, "libblaze
 OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE, ERR_TOO_LARGE, ERR_OUT_OF_MEMORY = range(8)
 GEMM_F16, GEMM_BF16, GEMM_FP8, GEMM_NVFP4, GEMM_W4A16_F16, GEMM_W4A16_BF16 = range(6)
 F16, BF16, F32 = range(3)
-EPI_NONE, EPI_BIAS, EPI_SILU, EPI_BIAS_SILU, EPI_RESIDUAL_ADD = range(5)
+EPI_NONE, EPI_BIAS, EPI_SILU, EPI_BIAS_SILU, EPI_RESIDUAL_ADD, EPI_SWIGLU = range(6)
 B_KMAJOR, B_NMAJOR = range(2)
 SF_ROWMAJOR, SF_TILED = range(2)
 VARIANT_AUTO, VARIANT_TILE_128x128, VARIANT_PAIR_256x256, VARIANT_DECODE, VARIANT_QUAD_512x256, VARIANT_PAIR_256x384 = range(6)
@@ -24,7 +24,7 @@ VARIANT_AUTO, VARIANT_TILE_128x128, VARIANT_PAIR_256x256, VARIANT_DECODE, VARIAN
 KINDS = {"f16": GEMM_F16, "bf16": GEMM_BF16, "fp8": GEMM_FP8, "nvfp4": GEMM_NVFP4,
          "w4a16_f16": GEMM_W4A16_F16, "w4a16_bf16": GEMM_W4A16_BF16}
 DTYPES = {"f16": F16, "bf16": BF16, "f32": F32}
-EPILOGUES = {"none": EPI_NONE, "bias": EPI_BIAS, "silu": EPI_SILU, "bias_silu": EPI_BIAS_SILU, "residual": EPI_RESIDUAL_ADD}
+EPILOGUES = {"none": EPI_NONE, "bias": EPI_BIAS, "silu": EPI_SILU, "bias_silu": EPI_BIAS_SILU, "residual": EPI_RESIDUAL_ADD, "swiglu": EPI_SWIGLU}
 VARIANTS = {"auto": VARIANT_AUTO, "128x128": VARIANT_TILE_128x128, "256x256": VARIANT_PAIR_256x256, "decode": VARIANT_DECODE, "512x256": VARIANT_QUAD_512x256, "256x384": VARIANT_PAIR_256x384}
 
 # every symbol include/blaze_b200.h declares
@@ -32,7 +32,7 @@ EXPORTS = (
     "blz_version", "blz_status_string", "blz_last_cuda_error", "blz_last_cuda_error_string",
     "blz_gemm_plan_create", "blz_gemm_execute", "blz_gemm_plan_set_a", "blz_gemm_plan_check",
     "blz_gemm_plan_info", "blz_gemm_plan_destroy", "blz_gemm_launch",
-    "blz_amax", "blz_quantize_fp8", "blz_quantize_nvfp4", "blz_tiled_scales_bytes", "blz_tile_scales",
+    "blz_amax", "blz_quantize_fp8", "blz_quantize_nvfp4", "blz_tiled_scales_bytes", "blz_tile_scales", "blz_interleave_gate_up",
     "blz_gemm_nvfp4_decode_static",
     "blz_peer_buffer_create", "blz_peer_buffer_open", "blz_peer_buffer_close", "blz_peer_buffer_destroy", "blz_gemm_execute_gather",
     "blz_wait_probe",
@@ -47,6 +47,7 @@ class GemmDesc(ctypes.Structure):
         ("A", ctypes.c_void_p), ("A_sf", ctypes.c_void_p), ("B", ctypes.c_void_p), ("B_sf", ctypes.c_void_p),
         ("a_scale", ctypes.c_float), ("b_scale", ctypes.c_float),
         ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("ldc", ctypes.c_int64),
+        ("b_scale2", ctypes.c_float), ("reserved", ctypes.c_int32),
     ]
 
 
@@ -98,6 +99,8 @@ def lib() -> ctypes.CDLL:
     L.blz_tiled_scales_bytes.restype = i64
     L.blz_tiled_scales_bytes.argtypes = [i64, i64]
     L.blz_tile_scales.argtypes = [vp, i64, i64, i64, i64, vp, vp]
+    L.blz_interleave_gate_up.argtypes = [vp, vp, vp, i64, i64, vp]
+    L.blz_interleave_gate_up.restype = ctypes.c_int
     L.blz_gemm_nvfp4_decode_static.argtypes = [vp, vp, ctypes.c_float, vp, vp, ctypes.c_float, i32, i32, i32, vp, i32, i64, vp, vp]
     L.blz_gemm_nvfp4_decode_static.restype = ctypes.c_int
     L.blz_peer_buffer_create.argtypes = [i64, ctypes.POINTER(vp), ctypes.c_char_p]

@@ -124,9 +124,30 @@ MixedGemmPlan* create_mixed_gemm_plan(const half* A, const Fp4WeightTensor& B, i
 void execute_mixed_gemm(MixedGemmPlan* plan, half* C, cudaStream_t stream) { run_plan(plan, C, stream, "execute_mixed_gemm"); }
 void destroy_mixed_gemm_plan(MixedGemmPlan* plan) { blz_gemm_plan_destroy(reinterpret_cast<blz_gemm_plan*>(plan)); }
 
-// output = SiLU(x W_gate) * (x W_up): the gate GEMM applies SiLU in its epilogue, the up GEMM
-// writes `output`, one elementwise pass multiplies them.
+// output = SiLU(x W_gate) * (x W_up).  One GEMM over the 2N interleaved gate / up columns whose
+// epilogue multiplies the pairs (BLZ_EPI_SWIGLU); the interleaved copy of the packed weights and
+// their scales is made here per call, as launch_* owns no state.  N not a multiple of 16: two
+// GEMMs (the gate one applies SiLU) and one elementwise pass.
 void launch_fused_gate_up(const half* x, const Fp4WeightTensor& W_gate, const Fp4WeightTensor& W_up, half* output, int M, int N, int K, cudaStream_t stream) {
+    if (N % 16 == 0 && K % 32 == 0) {
+        const long long data_bytes = static_cast<long long>(K) * (N / 2), sf_bytes = static_cast<long long>(K / 16) * N;
+        uint8_t *data = nullptr, *sf = nullptr;
+        if (cudaMalloc(&data, static_cast<size_t>(2 * data_bytes)) != cudaSuccess || cudaMalloc(&sf, static_cast<size_t>(2 * sf_bytes)) != cudaSuccess) {
+            (void)cudaGetLastError();
+            cudaFree(data);
+            fprintf(stderr, "blaze: launch_fused_gate_up could not allocate %lld bytes\n", 2 * (data_bytes + sf_bytes));
+            return;
+        }
+        // [K, N/2] bytes: 16 columns = 8 bytes per group; [K/16, N] scales: 16 bytes per group
+        report("launch_fused_gate_up(interleave)", blz_interleave_gate_up(W_gate.data, W_up.data, data, data_bytes / 8, 8, stream));
+        report("launch_fused_gate_up(interleave)", blz_interleave_gate_up(W_gate.block_scales, W_up.block_scales, sf, sf_bytes / 16, 16, stream));
+        blz_gemm_desc d = base_desc(BLZ_GEMM_W4A16_F16, M, 2 * N, K, BLZ_EPI_SWIGLU, nullptr, nullptr);
+        d.A = x; d.B = data; d.B_sf = sf;
+        d.b_scale = W_gate.tensor_scale; d.b_scale2 = W_up.tensor_scale;
+        run_once(d, output, stream, "launch_fused_gate_up");      // synchronises the stream
+        cudaFree(data); cudaFree(sf);
+        return;
+    }
     half* gate = nullptr;
     const long long n = static_cast<long long>(M) * N;
     if (cudaMalloc(&gate, static_cast<size_t>(n) * sizeof(half)) != cudaSuccess) {

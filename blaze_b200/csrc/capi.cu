@@ -187,8 +187,13 @@ blz_status validate(const blz_gemm_desc* d) {
     if (!d->A || !d->B) return BLZ_ERR_INVALID_ARGUMENT;
     if (d->kind < BLZ_GEMM_F16 || d->kind > BLZ_GEMM_W4A16_BF16) return BLZ_ERR_INVALID_ARGUMENT;
     if (d->out_dtype < BLZ_F16 || d->out_dtype > BLZ_F32) return BLZ_ERR_INVALID_ARGUMENT;
-    if (d->epilogue < BLZ_EPI_NONE || d->epilogue > BLZ_EPI_RESIDUAL_ADD) return BLZ_ERR_INVALID_ARGUMENT;
-    if (d->ldc != 0 && d->ldc < d->N) return BLZ_ERR_INVALID_ARGUMENT;
+    if (d->epilogue < BLZ_EPI_NONE || d->epilogue > BLZ_EPI_SWIGLU) return BLZ_ERR_INVALID_ARGUMENT;
+    if (d->epilogue == BLZ_EPI_SWIGLU) {
+        // gate / up rows interleaved in groups of 16; C is [M, N/2]
+        if (d->N % 32) return BLZ_ERR_INVALID_ARGUMENT;
+        if (d->ldc != 0 && d->ldc < d->N / 2) return BLZ_ERR_INVALID_ARGUMENT;
+        if (d->variant == BLZ_VARIANT_DECODE) return BLZ_ERR_UNSUPPORTED;
+    } else if (d->ldc != 0 && d->ldc < d->N) return BLZ_ERR_INVALID_ARGUMENT;
     const bool fp4_a = d->kind == BLZ_GEMM_NVFP4;
     const bool fp4_b = d->kind == BLZ_GEMM_NVFP4 || d->kind == BLZ_GEMM_W4A16_F16 || d->kind == BLZ_GEMM_W4A16_BF16;
     if (fp4_a && !d->A_sf) return BLZ_ERR_INVALID_ARGUMENT;
@@ -317,7 +322,7 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1, bool wide = fa
     // sums to its own row block of a scratch matrix; a small second kernel adds the splits in order
     // and applies the epilogue.
     cp.m_tiles_real = cp.m_tiles; cp.split_k = 1; cp.k_per_split = cp.k_stages;
-    if (cg == 1 && share == 1 && !wide) {
+    if (cg == 1 && share == 1 && !wide && d.epilogue != BLZ_EPI_SWIGLU) {
         int split = 1;
         const int64_t tiles1 = static_cast<int64_t>(cp.m_tiles) * cp.n_tiles;
         while (split < 4 && tiles1 * split * 2 <= p->num_sms && cp.k_stages / (split * 2) >= 16) split *= 2;
@@ -368,6 +373,7 @@ void fill_epilogue(const blz_gemm_plan* p, void* C, EpilogueParams& e) {
     e.bias = d.bias; e.residual = d.residual;
     e.ldc = d.ldc ? d.ldc : d.N; e.ldr = e.ldc;
     e.alpha = d.a_scale * d.b_scale;
+    e.alpha2 = e.alpha;
     e.mode = d.epilogue;
     e.out_type = d.out_dtype;
     const int eb = elem_bytes_out(d.out_dtype);
@@ -527,7 +533,7 @@ blz_status launch_cluster(blz_gemm_plan* p, int n_dst, void* const* dst, int64_t
         cp.M = static_cast<int>(rows_all);
         cp.epi.C = p->own_partial; cp.epi.bias = nullptr; cp.epi.residual = nullptr;
         cp.epi.ldc = p->partial_pitch; cp.epi.ldr = p->partial_pitch;
-        cp.epi.alpha = 1.0f; cp.epi.mode = EPI_NONE; cp.epi.out_type = OUT_F32; cp.epi.vec_ok = 1;
+        cp.epi.alpha = 1.0f; cp.epi.alpha2 = 1.0f; cp.epi.mode = EPI_NONE; cp.epi.out_type = OUT_F32; cp.epi.vec_ok = 1;
         cp.use_tma_store = 1; cp.n_dst = 1;
         if (p->out_n != -1) {
             blz_status s = encode_map(&p->out.m[0], p->own_partial, static_cast<uint64_t>(d.N) * 4, static_cast<uint64_t>(rows_all),
@@ -542,7 +548,7 @@ blz_status launch_cluster(blz_gemm_plan* p, int n_dst, void* const* dst, int64_t
         EpilogueParams e;
         e.C = static_cast<uint8_t*>(dst[0]) + col_offset * eb;
         e.bias = d.bias; e.residual = d.residual; e.ldc = ld; e.ldr = ld;
-        e.alpha = d.a_scale * d.b_scale; e.mode = d.epilogue; e.out_type = d.out_dtype; e.vec_ok = 0;
+        e.alpha = d.a_scale * d.b_scale; e.alpha2 = e.alpha; e.mode = d.epilogue; e.out_type = d.out_dtype; e.vec_ok = 0;
         const int64_t groups = static_cast<int64_t>(d.M) * ceil_div(d.N, 4);
         splitk_reduce_kernel<<<grid_for(groups, 256), 256, 0, stream>>>(p->own_partial, p->split_k, p->partial_rows, p->partial_pitch, d.M, d.N, e);
         BLZ_CUDA(cudaGetLastError());
@@ -552,13 +558,15 @@ blz_status launch_cluster(blz_gemm_plan* p, int n_dst, void* const* dst, int64_t
     cp.epi.bias = d.bias; cp.epi.residual = d.residual;
     cp.epi.ldc = ld; cp.epi.ldr = ld;
     cp.epi.alpha = d.a_scale * d.b_scale;
+    cp.epi.alpha2 = d.a_scale * (d.b_scale2 != 0.0f ? d.b_scale2 : d.b_scale);
     cp.epi.mode = d.epilogue;
     cp.epi.out_type = d.out_dtype;
     bool vec = ((ld * eb) & 15) == 0 && ((col_offset * eb) & 15) == 0;
     for (int i = 0; i < n_dst; ++i) vec = vec && (reinterpret_cast<uintptr_t>(dst[i]) & 15u) == 0;
     if (d.residual) vec = vec && (reinterpret_cast<uintptr_t>(d.residual) & 15u) == 0;
     cp.epi.vec_ok = vec ? 1 : 0;
-    cp.use_tma_store = cp.epi.vec_ok;
+    // the fused gate / up epilogue writes half-width rows straight from registers
+    cp.use_tma_store = (cp.epi.vec_ok && d.epilogue != BLZ_EPI_SWIGLU) ? 1 : 0;
     cp.n_dst = n_dst;
     if (n_dst > 1 && !cp.use_tma_store) return BLZ_ERR_INVALID_ARGUMENT;   // peer outputs go through TMA stores only
     if (cp.use_tma_store) {
@@ -587,7 +595,7 @@ blz_status launch_cluster(blz_gemm_plan* p, int n_dst, void* const* dst, int64_t
 
 extern "C" {
 
-int blz_version(void) { return 1; }
+int blz_version(void) { return 2; }
 
 const char* blz_status_string(blz_status s) {
     switch (s) {
@@ -655,7 +663,8 @@ blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_p
     // for 128 x 4096 x 11008
     const bool w4_tiled_split = w4a16 && desc->M > 64 && ceil_div(desc->N, 128) * 4 <= p->num_sms && desc->K >= 8192;
     const int decode_auto_m = (w4a16 && !w4_tiled_split) ? 128 : 64;
-    const bool want_decode = desc->variant == BLZ_VARIANT_DECODE || (desc->variant == BLZ_VARIANT_AUTO && desc->M <= decode_auto_m);
+    const bool swiglu = desc->epilogue == BLZ_EPI_SWIGLU;      // tiled kernels only
+    const bool want_decode = desc->variant == BLZ_VARIANT_DECODE || (desc->variant == BLZ_VARIANT_AUTO && desc->M <= decode_auto_m && !swiglu);
     // M > 128: up to 2048 rows the tiled kernel expands the packed weights stage by stage in shared
     // memory (no 16-bit copy; every CTA re-expands the tiles it uses).  Beyond that, expanding all
     // weights once per call into a plan-owned 16-bit copy costs less than the slower main loop
@@ -703,7 +712,7 @@ blz_status blz_gemm_execute(blz_gemm_plan* p, void* C, void* stream_v) {
     if (p->variant == BLZ_VARIANT_DECODE) return decode_launch(p, C, stream);
 
     void* one[1] = {C};
-    return launch_cluster(p, 1, one, d.ldc ? d.ldc : d.N, 0, stream);
+    return launch_cluster(p, 1, one, d.ldc ? d.ldc : (d.epilogue == BLZ_EPI_SWIGLU ? d.N / 2 : d.N), 0, stream);
 }
 
 blz_status blz_gemm_execute_gather(blz_gemm_plan* p, int32_t n_dst, void* const* dst, int64_t ld_total, int64_t col_offset, void* stream_v) {
@@ -711,7 +720,7 @@ blz_status blz_gemm_execute_gather(blz_gemm_plan* p, int32_t n_dst, void* const*
     if (p->variant == BLZ_VARIANT_DECODE) return BLZ_ERR_UNSUPPORTED;
     const blz_gemm_desc& d = p->desc;
     if (ld_total < col_offset + d.N || col_offset < 0) return BLZ_ERR_INVALID_ARGUMENT;
-    if (d.epilogue == BLZ_EPI_RESIDUAL_ADD || p->split_k > 1) return BLZ_ERR_UNSUPPORTED;
+    if (d.epilogue == BLZ_EPI_RESIDUAL_ADD || d.epilogue == BLZ_EPI_SWIGLU || p->split_k > 1) return BLZ_ERR_UNSUPPORTED;
     for (int i = 0; i < n_dst; ++i) if (!dst[i]) return BLZ_ERR_INVALID_ARGUMENT;
     return launch_cluster(p, n_dst, dst, ld_total, col_offset, static_cast<cudaStream_t>(stream_v));
 }
@@ -908,6 +917,16 @@ blz_status blz_tile_scales(const uint8_t* sf, int64_t rows, int64_t K, int64_t r
     BLZ_CUDA(cudaMemsetAsync(tiled, 0, static_cast<size_t>(blz_tiled_scales_bytes(rows, K)), stream));
     const int64_t kb = K / 16;
     tile_scales_kernel<<<grid_for(rows * kb, 256), 256, 0, stream>>>(sf, rows, kb, row_stride, blk_stride, sf_katoms(K), tiled);
+    BLZ_CUDA(cudaGetLastError());
+    return BLZ_OK;
+}
+
+blz_status blz_interleave_gate_up(const void* gate, const void* up, void* out, int64_t n_groups, int64_t group_bytes, void* stream_v) {
+    if (!gate || !up || !out || n_groups <= 0 || group_bytes <= 0 || (group_bytes % 4) != 0) return BLZ_ERR_INVALID_ARGUMENT;
+    if (((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(out)) & 3u) != 0) return BLZ_ERR_INVALID_ARGUMENT;
+    const int64_t words = group_bytes / 4;
+    interleave_groups_kernel<<<grid_for(n_groups * words, 256), 256, 0, static_cast<cudaStream_t>(stream_v)>>>(
+        static_cast<const uint32_t*>(gate), static_cast<const uint32_t*>(up), static_cast<uint32_t*>(out), n_groups, words);
     BLZ_CUDA(cudaGetLastError());
     return BLZ_OK;
 }

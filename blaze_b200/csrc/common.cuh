@@ -12,7 +12,12 @@ namespace blz {
 
 enum MmaKind : int { MMA_F16 = 0, MMA_F8 = 1, MMA_NVF4 = 2, MMA_W4A16 = 3 };   // W4A16: kind::f16 instructions, B expanded from NVFP4 in the kernel
 enum OutType : int { OUT_F16 = 0, OUT_BF16 = 1, OUT_F32 = 2 };
-enum EpiMode : int { EPI_NONE = 0, EPI_BIAS = 1, EPI_SILU = 2, EPI_BIAS_SILU = 3, EPI_RESIDUAL = 4 };
+enum EpiMode : int { EPI_NONE = 0, EPI_BIAS = 1, EPI_SILU = 2, EPI_BIAS_SILU = 3, EPI_RESIDUAL = 4, EPI_SWIGLU = 5 };
+// EPI_SWIGLU: the GEMM's N columns are gate / up projections interleaved in groups of 16 (columns
+// 32b .. 32b+15 gate, 32b+16 .. 32b+31 up, of outputs 16b .. 16b+15); C is [M, N/2]:
+// C[m, 16b+i] = silu(alpha * acc[32b+i]) * (alpha2 * acc[32b+16+i]).  What Blaze declares as
+// launch_fused_gate_up (include/gemm/mixed_gemm_sm100.cuh:87-109; its body is a stub,
+// src/kernels/gemm_mixed_sm100.cu:520-543).
 
 struct EpilogueParams {
     void* C;                 // [M, ldc] in the output type
@@ -20,6 +25,7 @@ struct EpilogueParams {
     const void* residual;    // [M, ldr] in the output type, or null
     long long ldc, ldr;      // row pitches in elements
     float alpha;
+    float alpha2;            // EPI_SWIGLU: multiplier of the up columns
     int mode;                // EpiMode
     int out_type;            // OutType
     int vec_ok;              // rows of C (and residual) are 16-byte aligned: wide stores allowed
@@ -62,9 +68,53 @@ template <int OUT> __device__ __forceinline__ float load_out_elem(const void* p,
 
 // Applies the epilogue to 32 consecutive accumulator columns of one row and stores them.
 //   acc: raw fp32 bits from tensor memory; row / col0: position in C.
+// EPI_SWIGLU on one 32-column group of the GEMM (col0 a multiple of 32): 16 outputs at column col0 / 2.
+template <int OUT>
+__device__ __forceinline__ void epilogue_store_swiglu32(const EpilogueParams& e, const uint32_t (&acc)[32], int row, int col0, int N) {
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = silu_f32(__uint_as_float(acc[i]) * e.alpha) * (__uint_as_float(acc[16 + i]) * e.alpha2);
+    using T = typename OutElem<OUT>::type;
+    const int ocol = col0 >> 1, n_out = N >> 1;
+    T* dst = reinterpret_cast<T*>(e.C) + static_cast<long long>(row) * e.ldc + ocol;
+    if (ocol + 16 <= n_out && e.vec_ok) {
+        if constexpr (OUT == OUT_F32) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 4)
+                *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; i += 8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if constexpr (OUT == OUT_F16) {
+                        __half2 h = __floats2half2_rn(clamp_f16_range(v[i + 2 * j]), clamp_f16_range(v[i + 2 * j + 1]));
+                        w[j] = *reinterpret_cast<uint32_t*>(&h);
+                    } else {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
+                        w[j] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                }
+                *reinterpret_cast<uint4*>(dst + i) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if (ocol + i < n_out) {
+                if constexpr (OUT == OUT_F16) dst[i] = __float2half_rn(clamp_f16_range(v[i]));
+                else if constexpr (OUT == OUT_BF16) dst[i] = __float2bfloat16_rn(v[i]);
+                else dst[i] = v[i];
+            }
+        }
+    }
+}
+
 template <int OUT>
 __device__ __forceinline__ void epilogue_store32(const EpilogueParams& e, const uint32_t (&acc)[32], int row, int col0, int M, int N) {
     if (row >= M || col0 >= N) return;
+    if (e.mode == EPI_SWIGLU) { epilogue_store_swiglu32<OUT>(e, acc, row, col0, N); return; }
     float v[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]) * e.alpha;

@@ -224,4 +224,16 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
     }
 }
 
+// out = 4-byte words of groups taken alternately from `a` and `b`: group g of a, group g of b, ...
+// (words_per_group words each).  Builds the gate / up interleaved weights of the EPI_SWIGLU epilogue.
+__global__ void interleave_groups_kernel(const uint32_t* __restrict__ a, const uint32_t* __restrict__ b, uint32_t* __restrict__ out,
+                                         long long n_groups, long long words_per_group) {
+    const long long total = n_groups * words_per_group;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long g = i / words_per_group, w = i - g * words_per_group;
+        out[(2 * g) * words_per_group + w] = a[i];
+        out[(2 * g + 1) * words_per_group + w] = b[i];
+    }
+}
+
 }  // namespace blz

@@ -37,7 +37,7 @@ class GemmPlan:
     def __init__(self, kind: str, M: int, N: int, K: int, A, B, *, A_sf=None, B_sf=None, a_scale: float = 1.0,
                  b_scale: float = 1.0, out_dtype: str = "bf16", epilogue: str = "none", bias=None, residual=None,
                  b_layout: str = "kmajor", a_sf_layout: str = "rowmajor", b_sf_layout: str = "rowmajor",
-                 variant: str = "auto", ldc: int = 0):
+                 variant: str = "auto", ldc: int = 0, b_scale2: float = 0.0):
         L = nv.lib()
         d = nv.GemmDesc()
         d.kind = nv.KINDS[kind]
@@ -52,6 +52,7 @@ class GemmPlan:
         d.a_scale, d.b_scale = float(a_scale), float(b_scale)
         d.bias, d.residual = _ptr(bias), _ptr(residual)
         d.ldc = int(ldc)
+        d.b_scale2, d.reserved = float(b_scale2), 0
         self._keep = (A, B, A_sf, B_sf, bias, residual)   # operands must outlive the plan
         self._handle = ctypes.c_void_p()
         self.kind, self.M, self.N, self.K, self.out_dtype = kind, int(M), int(N), int(K), out_dtype
@@ -115,6 +116,28 @@ def create_mixed_gemm_plan(A, B: dict, M, N, K, bias=None, residual=None, epilog
     """fp16 activations A [M,K] x NVFP4 weights B (Fp4WeightTensor fields, [K,N] convention)."""
     return GemmPlan("w4a16_f16", M, N, K, A, B["data"], B_sf=B["block_scales"], b_scale=B["tensor_scale"], out_dtype="f16",
                     epilogue=epilogue, bias=bias, residual=residual, b_layout="nmajor")
+
+
+def interleave_gate_up(gate, up, group_bytes: int, stream=None):
+    """Groups of `group_bytes` bytes alternately from two equally sized uint8 tensors (blz_interleave_gate_up):
+    the weight layout the "swiglu" epilogue expects."""
+    import torch  # noqa: PLC0415
+    nbytes = gate.numel() * gate.element_size()
+    assert nbytes == up.numel() * up.element_size() and nbytes % group_bytes == 0
+    out = torch.empty(2 * nbytes, dtype=torch.uint8, device=gate.device)
+    nv.check("blz_interleave_gate_up", nv.lib().blz_interleave_gate_up(gate.data_ptr(), up.data_ptr(), out.data_ptr(), nbytes // group_bytes,
+                                                                        int(group_bytes), _stream(stream)))
+    return out
+
+
+def create_fused_gate_up_plan(x, W_gate: dict, W_up: dict, M, N, K) -> GemmPlan:
+    """output[M, N] = silu(x W_gate) * (x W_up) in one kernel: fp16 activations x [M, K], two NVFP4
+    weights with Blaze's Fp4WeightTensor fields ([K, N] convention), N a multiple of 16.
+    Mirrors launch_fused_gate_up (Blaze: include/gemm/mixed_gemm_sm100.cuh:87-109)."""
+    data = interleave_gate_up(W_gate["data"], W_up["data"], 8)                    # [K, N/2] bytes: 16 columns per group
+    sf = interleave_gate_up(W_gate["block_scales"], W_up["block_scales"], 16)      # [K/16, N] bytes
+    return GemmPlan("w4a16_f16", M, 2 * N, K, x, data, B_sf=sf, b_scale=W_gate["tensor_scale"], b_scale2=W_up["tensor_scale"],
+                    out_dtype="f16", epilogue="swiglu", b_layout="nmajor")
 
 
 def create_fp16_gemm_plan(A, B_colmajor, M, N, K) -> GemmPlan:

@@ -64,7 +64,14 @@ typedef enum blz_epilogue {
     BLZ_EPI_BIAS = 1,
     BLZ_EPI_SILU = 2,
     BLZ_EPI_BIAS_SILU = 3,
-    BLZ_EPI_RESIDUAL_ADD = 4
+    BLZ_EPI_RESIDUAL_ADD = 4,
+    BLZ_EPI_SWIGLU = 5 /* fused gate + up projection (Blaze: launch_fused_gate_up,
+                          include/gemm/mixed_gemm_sm100.cuh:87-109, a stub there).  B holds N = 2 * N_out
+                          weight rows, gate and up rows interleaved in groups of 16 (rows 32b..32b+15:
+                          gate rows 16b..16b+15; rows 32b+16..32b+31: up rows 16b..16b+15; see
+                          blz_interleave_gate_up); N a multiple of 32.  C is [M, N/2] (ldc 0 = N/2):
+                          C[m, j] = silu(a_scale*b_scale*gate[m, j]) * (a_scale*b_scale2*up[m, j]).
+                          Tiled variants only; one kernel. */
 } blz_epilogue;
 
 typedef enum blz_b_layout {
@@ -108,7 +115,9 @@ typedef struct blz_gemm_desc {
     float b_scale;        /* same for B.  alpha = a_scale * b_scale is applied to the accumulator */
     const void* bias;     /* [N] or null */
     const void* residual; /* [M, ldc] or null */
-    int64_t ldc;          /* row pitch of C and residual in elements; 0 = N */
+    int64_t ldc;          /* row pitch of C and residual in elements; 0 = N (N/2 for BLZ_EPI_SWIGLU) */
+    float b_scale2;       /* BLZ_EPI_SWIGLU: dequantisation multiplier of the up rows; 0 = b_scale */
+    int32_t reserved;     /* set to 0 */
 } blz_gemm_desc;
 
 typedef struct blz_plan_info {
@@ -175,6 +184,16 @@ blz_status blz_quantize_fp8(const void* x, int32_t x_dtype, int64_t n, const flo
  * blz_tiled_scales_bytes(rows, K) long and are fully written; *d_global = g. */
 blz_status blz_quantize_nvfp4(const void* x, int32_t x_dtype, int64_t rows, int64_t K, const float* d_amax,
                               uint8_t* data, uint8_t* sf, int32_t sf_layout, float* d_global, void* stream);
+
+/* out = groups of `group_bytes` bytes taken alternately from `gate` and `up` (group g of gate, group g
+ * of up, group g+1 of gate, ...); n_groups groups from each, group_bytes a multiple of 4.  Builds the
+ * interleaved weights of BLZ_EPI_SWIGLU from two separate tensors:
+ *   K-major packed E2M1 [N_out, K/2]:  n_groups = N_out/16, group_bytes = 16*K/2
+ *   row-major scales [N_out, K/16]:    n_groups = N_out/16, group_bytes = 16*K/16
+ *   Blaze's [K, N_out/2] packed data:  n_groups = K*N_out/16, group_bytes = 8
+ *   Blaze's [K/16, N_out] scales:      n_groups = (K/16)*N_out/16, group_bytes = 16
+ *   16-bit or E4M3 K-major weights:    n_groups = N_out/16, group_bytes = 16 * bytes per row */
+blz_status blz_interleave_gate_up(const void* gate, const void* up, void* out, int64_t n_groups, int64_t group_bytes, void* stream);
 
 /* Size of the tiled scale-factor array for a [rows, K] operand:
  * ceil(rows/128) row blocks x (ceil(K/64) rounded up to a multiple of 4) atoms x 512 bytes. */

@@ -192,6 +192,15 @@ def epilogue(C32, alpha: float = 1.0, bias=None, residual=None, mode: str = "non
     return C
 
 
+def swiglu(acc_gate, alpha_gate: float, acc_up, alpha_up: float) -> np.ndarray:
+    """Fused gate / up projection: silu(alpha_gate * gate) * (alpha_up * up) in fp32 -- what Blaze's
+    launch_fused_gate_up declares (include/gemm/mixed_gemm_sm100.cuh:87-109; SiLU as in
+    src/kernels/gemm_mixed_sm100.cu:202-229)."""
+    g = epilogue(acc_gate, alpha_gate, mode="silu")
+    u = epilogue(acc_up, alpha_up)
+    return (g * u).astype(np.float32)
+
+
 def gemm_dense16(A_raw, Bt_raw, in_dtype: str, nthreads: int = 0) -> np.ndarray:
     """fp16 / bf16 operands (raw 16-bit codes) -> fp32 accumulator."""
     w = f16_to_f32 if in_dtype == "f16" else bf16_to_f32

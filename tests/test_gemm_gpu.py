@@ -440,6 +440,129 @@ def test_w4a16_config4_sampled(oracle, cuda_device):
     plan.destroy()
 
 
+# ------------------------------------------------------------------- fused gate + up (SwiGLU)
+
+def _interleave_rows16(g, u):
+    """[n, w] x 2 -> [2n, w]: groups of 16 rows alternately from g and u (the layout the epilogue expects)."""
+    n, w = g.shape
+    return np.ascontiguousarray(np.stack([g.reshape(n // 16, 16, w), u.reshape(n // 16, 16, w)], axis=1).reshape(2 * n, w))
+
+
+@pytest.mark.parametrize("kind,variant,shape", [
+    ("w4a16_f16", "auto", (1, 176, 256)),            # a single row through the tiled kernel (no skinny-M form of this epilogue)
+    ("w4a16_bf16", "auto", (100, 176, 160)),         # ragged 128-wide tile of the 2N interleaved columns
+    ("w4a16_f16", "auto", (300, 1024, 1056)),        # ragged M and K stage
+    ("w4a16_bf16", "256x256", (520, 1024, 512)),     # CTA pairs
+    ("w4a16_bf16", "auto", (2100, 272, 544)),        # M > 2048: 16-bit copy of the weights first
+    ("bf16", "auto", (160, 144, 192)),
+    ("fp8", "auto", (160, 144, 256)),
+    ("nvfp4", "256x256", (384, 400, 512)),
+])
+def test_swiglu_one_kernel(oracle, cuda_device, kind, variant, shape):
+    """C[M, N] = silu(x Wg^T) * (x Wu^T) from ONE GEMM over the 2N interleaved weight rows, against the
+    oracle's two separate products; different tensor scales for the two weights."""
+    from blaze_b200 import GemmPlan, interleave_gate_up
+    M, N, K = shape
+    rng_a, rng_g, rng_u = np.random.default_rng(42), np.random.default_rng(123), np.random.default_rng(124)
+    kw = {}
+    if kind.startswith("w4a16"):
+        act = "bf16" if kind.endswith("bf16") else "f16"
+        enc = oracle.f32_to_bf16 if act == "bf16" else oracle.f32_to_f16
+        A = enc(rng_a.standard_normal((M, K)).astype(np.float32))
+        gd, gsf, gg = oracle.quantize_nvfp4((rng_g.standard_normal((N, K)) * 0.02).astype(np.float32))
+        ud, usf, gu = oracle.quantize_nvfp4((rng_u.standard_normal((N, K)) * 0.05).astype(np.float32))
+        acc_g, alpha_g = oracle.gemm_w4a16(A, act, gd, gsf, gg)
+        acc_u, alpha_u = oracle.gemm_w4a16(A, act, ud, usf, gu)
+        a_dev = bits16_to_torch(A, act, cuda_device)
+        # the device helper interleaves the K-major packed rows and the row-major scales in groups of 16 rows
+        b_dev = interleave_gate_up(_u8(gd, cuda_device), _u8(ud, cuda_device), 16 * K // 2)
+        sf_dev = interleave_gate_up(_u8(gsf, cuda_device), _u8(usf, cuda_device), 16 * K // 16)
+        assert np.array_equal(b_dev.cpu().numpy().reshape(2 * N, K // 2), _interleave_rows16(gd, ud))
+        kw = dict(B_sf=sf_dev, b_scale=gg, b_scale2=gu)
+        out = act
+    elif kind == "bf16":
+        A, G = _dense_inputs(oracle, "bf16", M, N, K, scale=0.25)
+        U = oracle.f32_to_bf16((rng_u.standard_normal((N, K)) * 0.25).astype(np.float32))
+        acc_g, acc_u = oracle.gemm_dense16(A, G, "bf16"), oracle.gemm_dense16(A, U, "bf16")
+        alpha_g = alpha_u = 1.0
+        a_dev = bits16_to_torch(A, "bf16", cuda_device)
+        b_dev = bits16_to_torch(_interleave_rows16(G, U), "bf16", cuda_device)
+        out = "bf16"
+    elif kind == "fp8":
+        qa, da, qg, dg = _fp8_inputs(oracle, M, N, K)
+        xu = rng_u.uniform(-1, 1, (N, K)).astype(np.float32) * 3.0
+        qu, su = oracle.quantize_fp8(xu)
+        du = float(np.float32(1.0) / np.float32(su))
+        acc_g = oracle.gemm_f32(oracle.e4m3_to_f32(qa), oracle.e4m3_to_f32(qg)); alpha_g = float(np.float32(da) * np.float32(dg))
+        acc_u = oracle.gemm_f32(oracle.e4m3_to_f32(qa), oracle.e4m3_to_f32(qu)); alpha_u = float(np.float32(da) * np.float32(du))
+        a_dev = _u8(qa, cuda_device)
+        b_dev = _u8(_interleave_rows16(qg, qu), cuda_device)
+        kw = dict(a_scale=da, b_scale=dg, b_scale2=du)
+        out = "f16"
+    else:
+        (ad, asf, ga), (gd, gsf, gg) = _nvfp4_inputs(oracle, M, N, K)
+        ud, usf, gu = oracle.quantize_nvfp4((rng_u.standard_normal((N, K)) * 0.5).astype(np.float32))
+        acc_g, alpha_g = oracle.gemm_nvfp4(ad, asf, ga, gd, gsf, gg)
+        acc_u, alpha_u = oracle.gemm_nvfp4(ad, asf, ga, ud, usf, gu)
+        a_dev = _u8(ad, cuda_device)
+        b_dev = _u8(_interleave_rows16(gd, ud), cuda_device)
+        kw = dict(A_sf=_u8(asf, cuda_device), B_sf=_u8(_interleave_rows16(gsf, usf), cuda_device), a_scale=ga, b_scale=gg, b_scale2=gu)
+        out = "bf16"
+    want = oracle.widen(oracle.narrow(oracle.swiglu(acc_g, alpha_g, acc_u, alpha_u), out), out)
+    C = _out_tensor(M, N, out, cuda_device)
+    plan = GemmPlan(kind, M, 2 * N, K, a_dev, b_dev, out_dtype=out, epilogue="swiglu", variant=variant, **kw)
+    info = plan.info()
+    assert info["variant"] != 3 and info["split_k"] == 1
+    assert info["launches"] == (2 if (kind.startswith("w4a16") and M > 2048) else 1)
+    _run(plan, C)
+    assert_close(torch_to_f32(C, oracle, out), want, "swiglu %s %s" % (kind, shape))
+    plan.destroy()
+
+
+def test_swiglu_blaze_layout_strided(oracle, cuda_device):
+    """The mirror of Blaze's launch_fused_gate_up: weights in its [K, N/2] / [K/16, N] convention,
+    fp16 in and out; also a strided output and the argument checks of the epilogue."""
+    from blaze_b200 import GemmPlan, create_fused_gate_up_plan, interleave_gate_up
+    from blaze_b200 import _native as nv
+    M, N, K = 200, 208, 320
+    rng_a, rng_g, rng_u = np.random.default_rng(42), np.random.default_rng(123), np.random.default_rng(124)
+    A = oracle.f32_to_f16(rng_a.standard_normal((M, K)).astype(np.float32))
+    q = [oracle.quantize_nvfp4((r.standard_normal((N, K)) * 0.03).astype(np.float32)) for r in (rng_g, rng_u)]
+    acc_g, alpha_g = oracle.gemm_w4a16(A, "f16", *q[0])
+    acc_u, alpha_u = oracle.gemm_w4a16(A, "f16", *q[1])
+    want = oracle.widen(oracle.narrow(oracle.swiglu(acc_g, alpha_g, acc_u, alpha_u), "f16"), "f16")
+
+    def blaze_tensor(bd, bsf, g):
+        nib = np.empty((N, K), np.uint8); nib[:, 0::2] = bd & 15; nib[:, 1::2] = bd >> 4
+        nib_kn = np.ascontiguousarray(nib.T)
+        return {"data": _u8(nib_kn[:, 0::2] | (nib_kn[:, 1::2] << 4), cuda_device), "block_scales": _u8(np.ascontiguousarray(bsf.T), cuda_device), "tensor_scale": g}
+
+    Wg, Wu = blaze_tensor(*q[0]), blaze_tensor(*q[1])
+    a_dev = bits16_to_torch(A, "f16", cuda_device)
+    C = _out_tensor(M, N, "f16", cuda_device)
+    plan = create_fused_gate_up_plan(a_dev, Wg, Wu, M, N, K)
+    assert plan.info()["launches"] == 1
+    _run(plan, C)
+    assert_close(torch_to_f32(C, oracle, "f16"), want, "fused gate+up, Blaze layout")
+    plan.destroy()
+    # strided output: the columns beyond N keep their fill value
+    ldc = N + 24
+    data = interleave_gate_up(Wg["data"], Wu["data"], 8)
+    sf = interleave_gate_up(Wg["block_scales"], Wu["block_scales"], 16)
+    C2 = _out_tensor(M, N, "f16", cuda_device, ldc=ldc)
+    plan = GemmPlan("w4a16_f16", M, 2 * N, K, a_dev, data, B_sf=sf, b_scale=q[0][2], b_scale2=q[1][2], out_dtype="f16", epilogue="swiglu",
+                    b_layout="nmajor", ldc=ldc)
+    _run(plan, C2)
+    assert_close(torch_to_f32(C2[:, :N].contiguous(), oracle, "f16"), want, "fused gate+up, strided C")
+    assert bool((C2[:, N:] == -7.0).all())
+    plan.destroy()
+    for bad in (dict(N=2 * N + 16), dict(variant="decode"), dict(ldc=N - 8)):
+        args = dict(N=2 * N, variant="auto", ldc=0); args.update(bad)
+        with pytest.raises(nv.BlazeError):
+            GemmPlan("w4a16_f16", M, args["N"], K, a_dev, data, B_sf=sf, b_scale=1.0, out_dtype="f16", epilogue="swiglu", b_layout="nmajor",
+                     variant=args["variant"], ldc=args["ldc"])
+
+
 # ---------------------------------------------------------------------------------- epilogues
 
 @pytest.mark.parametrize("mode", ["bias", "silu", "bias_silu", "residual"])

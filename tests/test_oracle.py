@@ -131,3 +131,12 @@ def test_epilogue_and_narrow(oracle):
     h = oracle.widen(oracle.narrow(np.array([70000.0, -1e9, 1.0], np.float32), "f16"), "f16")
     assert h.tolist() == [65504.0, -65504.0, 1.0]                      # saturating fp16 store
     assert oracle.widen(oracle.narrow(np.array([1.00390625], np.float32), "bf16"), "bf16")[0] == 1.0   # ties to even
+
+
+def test_swiglu(oracle):
+    g = np.array([[1.0, -3.0, 0.0, 8.0]], np.float32)
+    u = np.array([[2.0, 0.5, 7.0, -1.0]], np.float32)
+    out = oracle.swiglu(g, 0.5, u, 2.0)
+    x = np.float32(0.5) * g[0]
+    np.testing.assert_allclose(out[0], x / (1 + np.exp(-x)) * (2.0 * u[0]), rtol=1e-6)
+    assert out[0, 2] == 0.0
