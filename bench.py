@@ -580,7 +580,7 @@ def main() -> int:
                 others["%s_decode_M16" % dk] = run_decode(device, 5, 3, peaks, kind=dk)
             except Exception as ex:
                 others["%s_decode_M16" % dk] = {"error": str(ex)[:200]}
-        for m2 in (512, 2048):
+        for m2 in (16, 512, 2048):
             try:
                 gu = run_gate_up(m2, 11008, 4096, device, 10, 3, flusher)
                 launches += gu.pop("launches")

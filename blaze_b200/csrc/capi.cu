@@ -192,7 +192,6 @@ blz_status validate(const blz_gemm_desc* d) {
         // gate / up rows interleaved in groups of 16; C is [M, N/2]
         if (d->N % 32) return BLZ_ERR_INVALID_ARGUMENT;
         if (d->ldc != 0 && d->ldc < d->N / 2) return BLZ_ERR_INVALID_ARGUMENT;
-        if (d->variant == BLZ_VARIANT_DECODE) return BLZ_ERR_UNSUPPORTED;
     } else if (d->ldc != 0 && d->ldc < d->N) return BLZ_ERR_INVALID_ARGUMENT;
     const bool fp4_a = d->kind == BLZ_GEMM_NVFP4;
     const bool fp4_b = d->kind == BLZ_GEMM_NVFP4 || d->kind == BLZ_GEMM_W4A16_F16 || d->kind == BLZ_GEMM_W4A16_BF16;
@@ -371,9 +370,9 @@ void fill_epilogue(const blz_gemm_plan* p, void* C, EpilogueParams& e) {
     const blz_gemm_desc& d = p->desc;
     e.C = C;
     e.bias = d.bias; e.residual = d.residual;
-    e.ldc = d.ldc ? d.ldc : d.N; e.ldr = e.ldc;
+    e.ldc = d.ldc ? d.ldc : (d.epilogue == BLZ_EPI_SWIGLU ? d.N / 2 : d.N); e.ldr = e.ldc;
     e.alpha = d.a_scale * d.b_scale;
-    e.alpha2 = e.alpha;
+    e.alpha2 = d.a_scale * (d.b_scale2 != 0.0f ? d.b_scale2 : d.b_scale);
     e.mode = d.epilogue;
     e.out_type = d.out_dtype;
     const int eb = elem_bytes_out(d.out_dtype);
@@ -661,10 +660,9 @@ blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_p
     const int decode_max_m = desc->kind == BLZ_GEMM_NVFP4 ? 64 : 128;
     // ... unless the tiled kernel would split K four ways (few tiles, long K): measured 27 against 42 us
     // for 128 x 4096 x 11008
-    const bool w4_tiled_split = w4a16 && desc->M > 64 && ceil_div(desc->N, 128) * 4 <= p->num_sms && desc->K >= 8192;
+    const bool w4_tiled_split = w4a16 && desc->M > 64 && ceil_div(desc->N, 128) * 4 <= p->num_sms && desc->K >= 8192 && desc->epilogue != BLZ_EPI_SWIGLU;
     const int decode_auto_m = (w4a16 && !w4_tiled_split) ? 128 : 64;
-    const bool swiglu = desc->epilogue == BLZ_EPI_SWIGLU;      // tiled kernels only
-    const bool want_decode = desc->variant == BLZ_VARIANT_DECODE || (desc->variant == BLZ_VARIANT_AUTO && desc->M <= decode_auto_m && !swiglu);
+    const bool want_decode = desc->variant == BLZ_VARIANT_DECODE || (desc->variant == BLZ_VARIANT_AUTO && desc->M <= decode_auto_m);
     // M > 128: up to 2048 rows the tiled kernel expands the packed weights stage by stage in shared
     // memory (no 16-bit copy; every CTA re-expands the tiles it uses).  Beyond that, expanding all
     // weights once per call into a plan-owned 16-bit copy costs less than the slower main loop

@@ -56,22 +56,35 @@ __device__ __forceinline__ void st_shared_cluster_f32(uint32_t addr, uint32_t ct
 
 // The 128 epilogue threads (threadIdx 128..255) write the staged fp32 sums stag[m][128] to C:
 // alpha, bias / SiLU / residual, narrowing, 16-byte row stores.  Compact on purpose: it runs once.
-__device__ __forceinline__ void decode_store_rows(const float* stag, int p_M, int p_N, int n_tile, float e_alpha, int e_mode, int e_out, int e_vec,
+__device__ __forceinline__ void decode_store_rows(const float* stag, int p_M, int p_N, int n_tile, float e_alpha, float e_alpha2, int e_mode, int e_out, int e_vec,
                                                   long long e_ldc, long long e_ldr, void* e_C, const void* e_bias, const void* e_res) {
                 const int tid = threadIdx.x - 128;
                 const int esize = e_out == OUT_F32 ? 4 : 2;
-                // one item = 8 consecutive columns of one row: 128 / 8 = 16 items per row
+                // one item = 8 consecutive output columns of one row: 128 / 8 = 16 items per row; the fused
+                // gate / up epilogue makes 64 outputs of the tile's 128 columns: 8 items per row
+                const bool swiglu = e_mode == EPI_SWIGLU;
+                const int ishift = swiglu ? 3 : 4;
+                const int n_out = swiglu ? (p_N >> 1) : p_N;
     #pragma unroll 1
-                for (int c = tid; c < p_M * 16; c += 128) {
-                    const int m = c >> 4, j = c & 15;
-                    const int col = n_tile * 128 + j * 8;
-                    if (col >= p_N) continue;
-                    const float4 lo = *reinterpret_cast<const float4*>(stag + m * 128 + j * 8);
-                    const float4 hi = *reinterpret_cast<const float4*>(stag + m * 128 + j * 8 + 4);
+                for (int c = tid; c < (p_M << ishift); c += 128) {
+                    const int m = c >> ishift, j = c & ((1 << ishift) - 1);
+                    // columns of the staged tile this item reads, and the output column it writes
+                    const int scol = swiglu ? ((j >> 1) * 32 + (j & 1) * 8) : j * 8;
+                    const int col = swiglu ? (n_tile * 64 + j * 8) : (n_tile * 128 + j * 8);
+                    if (col >= n_out) continue;
+                    const float4 lo = *reinterpret_cast<const float4*>(stag + m * 128 + scol);
+                    const float4 hi = *reinterpret_cast<const float4*>(stag + m * 128 + scol + 4);
                     float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
     #pragma unroll
                     for (int t = 0; t < 8; ++t) v[t] *= e_alpha;
-                    if (e_mode != EPI_NONE) {
+                    if (swiglu) {
+                        // columns 32b .. 32b+15 of the GEMM are gate, 32b+16 .. 32b+31 up, of outputs 16b .. 16b+15
+                        const float4 ulo = *reinterpret_cast<const float4*>(stag + m * 128 + scol + 16);
+                        const float4 uhi = *reinterpret_cast<const float4*>(stag + m * 128 + scol + 20);
+                        const float u[8] = {ulo.x, ulo.y, ulo.z, ulo.w, uhi.x, uhi.y, uhi.z, uhi.w};
+    #pragma unroll
+                        for (int t = 0; t < 8; ++t) v[t] = silu_f32(v[t]) * (u[t] * e_alpha2);
+                    } else if (e_mode != EPI_NONE) {
     #pragma unroll 1
                         for (int t = 0; t < 8; ++t) {
                             const int n = col + t;
@@ -86,13 +99,13 @@ __device__ __forceinline__ void decode_store_rows(const float* stag, int p_M, in
                         }
                     }
                     uint8_t* dst = reinterpret_cast<uint8_t*>(e_C) + (static_cast<long long>(m) * e_ldc + col) * esize;
-                    const bool whole = e_vec && col + 8 <= p_N;
+                    const bool whole = e_vec && col + 8 <= n_out;
                     if (e_out == OUT_F32) {
                         if (whole) {
                             reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
                             reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
                         } else {
-                            for (int t = 0; t < 8 && col + t < p_N; ++t) reinterpret_cast<float*>(dst)[t] = v[t];
+                            for (int t = 0; t < 8 && col + t < n_out; ++t) reinterpret_cast<float*>(dst)[t] = v[t];
                         }
                     } else {
                         uint32_t w[4];
@@ -101,7 +114,7 @@ __device__ __forceinline__ void decode_store_rows(const float* stag, int p_M, in
                         if (whole) {
                             *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
                         } else {
-                            for (int t = 0; t < 8 && col + t < p_N; ++t)
+                            for (int t = 0; t < 8 && col + t < n_out; ++t)
                                 reinterpret_cast<uint16_t*>(dst)[t] = static_cast<uint16_t>(w[t >> 1] >> (16 * (t & 1)));
                         }
                     }
@@ -206,7 +219,7 @@ __device__ __forceinline__ void decode_epilogue(const DecodeStreamParams& p, uin
         if (threadIdx.x == 128) BLZ_T_STORE(6, clock64() - t_entry);
 #endif
         if (epi_ok) {
-            decode_store_rows(stag, p_M, p_N, n_tile, e_alpha, e_mode, e_out, e_vec, e_ldc, e_ldr, e_C, e_bias, e_res);
+            decode_store_rows(stag, p_M, p_N, n_tile, e_alpha, p.epi.alpha2, e_mode, e_out, e_vec, e_ldc, e_ldr, e_C, e_bias, e_res);
         }
     }
 
@@ -281,7 +294,7 @@ __device__ __forceinline__ void decode_epilogue_wide(const DecodeStreamParams& p
         }
         tc_fence_before_sync();
         named_barrier_sync(1, 128);
-        if (epi_ok) decode_store_rows(stag, p_M, p_N, n_tile, e_alpha, e_mode, e_out, e_vec, e_ldc, e_ldr, e_C, e_bias, e_res);
+        if (epi_ok) decode_store_rows(stag, p_M, p_N, n_tile, e_alpha, p.epi.alpha2, e_mode, e_out, e_vec, e_ldc, e_ldr, e_C, e_bias, e_res);
     }
 }
 

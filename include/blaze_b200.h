@@ -71,7 +71,8 @@ typedef enum blz_epilogue {
                           gate rows 16b..16b+15; rows 32b+16..32b+31: up rows 16b..16b+15; see
                           blz_interleave_gate_up); N a multiple of 32.  C is [M, N/2] (ldc 0 = N/2):
                           C[m, j] = silu(a_scale*b_scale*gate[m, j]) * (a_scale*b_scale2*up[m, j]).
-                          Tiled variants only; one kernel. */
+                          One kernel, every variant; no K split of the tiled kernel, not with
+                          blz_gemm_execute_gather. */
 } blz_epilogue;
 
 typedef enum blz_b_layout {

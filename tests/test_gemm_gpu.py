@@ -449,8 +449,13 @@ def _interleave_rows16(g, u):
 
 
 @pytest.mark.parametrize("kind,variant,shape", [
-    ("w4a16_f16", "auto", (1, 176, 256)),            # a single row through the tiled kernel (no skinny-M form of this epilogue)
-    ("w4a16_bf16", "auto", (100, 176, 160)),         # ragged 128-wide tile of the 2N interleaved columns
+    ("w4a16_f16", "auto", (1, 176, 256)),            # skinny-M kernels: a single row
+    ("w4a16_bf16", "auto", (100, 176, 160)),         # 128-row activation tile, ragged last weight tile
+    ("w4a16_bf16", "auto", (16, 2048, 4096)),        # K split over the cluster
+    ("nvfp4", "auto", (16, 400, 512)),
+    ("fp8", "auto", (48, 144, 256)),
+    ("bf16", "auto", (8, 144, 192)),
+    ("w4a16_f16", "128x128", (24, 176, 256)),        # the tiled kernel on few rows
     ("w4a16_f16", "auto", (300, 1024, 1056)),        # ragged M and K stage
     ("w4a16_bf16", "256x256", (520, 1024, 512)),     # CTA pairs
     ("w4a16_bf16", "auto", (2100, 272, 544)),        # M > 2048: 16-bit copy of the weights first
@@ -512,7 +517,8 @@ def test_swiglu_one_kernel(oracle, cuda_device, kind, variant, shape):
     C = _out_tensor(M, N, out, cuda_device)
     plan = GemmPlan(kind, M, 2 * N, K, a_dev, b_dev, out_dtype=out, epilogue="swiglu", variant=variant, **kw)
     info = plan.info()
-    assert info["variant"] != 3 and info["split_k"] == 1
+    skinny = variant == "auto" and M <= (128 if kind.startswith("w4a16") else 64)
+    assert (info["variant"] == 3) == skinny and (skinny or info["split_k"] == 1)
     assert info["launches"] == (2 if (kind.startswith("w4a16") and M > 2048) else 1)
     _run(plan, C)
     assert_close(torch_to_f32(C, oracle, out), want, "swiglu %s %s" % (kind, shape))
@@ -556,7 +562,7 @@ def test_swiglu_blaze_layout_strided(oracle, cuda_device):
     assert_close(torch_to_f32(C2[:, :N].contiguous(), oracle, "f16"), want, "fused gate+up, strided C")
     assert bool((C2[:, N:] == -7.0).all())
     plan.destroy()
-    for bad in (dict(N=2 * N + 16), dict(variant="decode"), dict(ldc=N - 8)):
+    for bad in (dict(N=2 * N + 16), dict(ldc=N - 8)):
         args = dict(N=2 * N, variant="auto", ldc=0); args.update(bad)
         with pytest.raises(nv.BlazeError):
             GemmPlan("w4a16_f16", M, args["N"], K, a_dev, data, B_sf=sf, b_scale=1.0, out_dtype="f16", epilogue="swiglu", b_layout="nmajor",
