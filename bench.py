@@ -292,23 +292,43 @@ def run_decode(device, steps, warmup, peaks, kind="nvfp4"):
         e.record()
         torch.cuda.synchronize()
         us = s.elapsed_time(e) * 1000.0 / (reps * copies)
+        # beside it: the same number of launches of ONE plan, whose weights then stay in L2
+        with torch.cuda.stream(stream):
+            graph_l2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph_l2, stream=stream):
+                for _ in range(copies):
+                    plans[0].execute(C)
+        for _ in range(3):
+            graph_l2.replay()
+        torch.cuda.synchronize()
+        s.record()
+        for _ in range(reps):
+            graph_l2.replay()
+        e.record()
+        torch.cuda.synchronize()
+        us_l2 = s.elapsed_time(e) * 1000.0 / (reps * copies)
         plans[0].check()
         info = plans[0].info()
         gbs = algo / (us * 1e-6) / 1e9
         out.append({"M": M, "N": N, "K": K, "us_per_gemm": round(us, 3), "hbm_gbs": round(gbs, 1), "algorithmic_bytes": algo,
                     "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4), "weight_copies_cycled": copies,
-                    "split_k": info["split_k"], "grid": info["grid"], "launches": reps * copies})
+                    "us_per_gemm_weights_in_l2": round(us_l2, 3),
+                    "split_k": info["split_k"], "grid": info["grid"], "launches": 2 * reps * copies})
         for p in plans:
             p.destroy()
-        del Bs, SFs, plans, graph
+        del Bs, SFs, plans, graph, graph_l2
         torch.cuda.empty_cache()
     return out
 
 
-def run_e2e(res, steps, device):
-    """Same GEMM through the public call with host buffers: pinned A (and its scale factors) copied to
-    the device, the GEMM, the whole output copied back to pinned host memory, every step."""
+def run_e2e(res, steps, device, kind=None, shape=None, chunks=8):
+    """Same GEMM through the public call with HOST buffers: pinned activations (and their scale factors)
+    copied to the device, the GEMM, the whole output copied back to pinned host memory, every step.
+    The rows are cut into `chunks` blocks with one plan each (same weights), so that within a step the
+    copy back of block i overlaps the copy in and the GEMM of block i+1 (three streams).  Steps do not
+    overlap each other: a step's first copy in waits for the previous step's last copy back."""
     import torch
+    from blaze_b200 import GemmPlan
     plan, C, A, kw = res["plan"], res["C"], res["A"], res["kw"]
     hA = torch.empty(A.shape, dtype=A.dtype, pin_memory=True); hA.copy_(A)
     sf = kw.get("A_sf")
@@ -318,24 +338,78 @@ def run_e2e(res, steps, device):
     hC = torch.empty(C.shape, dtype=C.dtype, pin_memory=True)
     h2d = A.numel() * A.element_size() + (sf.numel() if sf is not None else 0)
     d2h = C.numel() * C.element_size()
+    M = A.shape[0]
+    tiled_sf = sf is None or (kw.get("a_sf_layout") == "tiled" and sf.numel() % (M // 128 if M >= 128 else 1) == 0)
+    if kind is None or M % (chunks * 256) != 0 or M // chunks < 1024 or not tiled_sf:
+        chunks = 1
 
-    def step():
-        A.copy_(hA, non_blocking=True)
-        if hS is not None:
-            sf.copy_(hS, non_blocking=True)
-        plan.execute(C)
-        hC.copy_(C, non_blocking=True)
+    if chunks == 1:
+        def step():
+            A.copy_(hA, non_blocking=True)
+            if hS is not None:
+                sf.copy_(hS, non_blocking=True)
+            plan.execute(C)
+            hC.copy_(C, non_blocking=True)
+        plans = []
+    else:
+        _, N, K = shape
+        Mc = M // chunks
+        sf_per_block = sf.numel() // (M // 128) if sf is not None else 0       # tiled scales: contiguous per 128 rows
+        s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        plans, views = [], []
+        for i in range(chunks):
+            k2 = {k: v for k, v in kw.items() if k != "A_sf"}
+            rows = slice(i * Mc, (i + 1) * Mc)
+            sfv = hsv = None
+            if sf is not None:
+                blk = slice(i * (Mc // 128) * sf_per_block, (i + 1) * (Mc // 128) * sf_per_block)
+                sfv, hsv = sf.view(-1)[blk], hS.view(-1)[blk]
+                k2["A_sf"] = sfv
+            plans.append(GemmPlan(kind, Mc, N, K, A[rows], res["B"], out_dtype=plan.out_dtype, **k2))
+            views.append((A[rows], hA[rows], sfv, hsv, C[rows], hC[rows]))
+        done_prev = [torch.cuda.Event()]
+        done_prev[0].record()
+
+        def step():
+            s_in.wait_event(done_prev[0])
+            for i in range(chunks):
+                a_d, a_h, s_d, s_h, c_d, c_h = views[i]
+                with torch.cuda.stream(s_in):
+                    a_d.copy_(a_h, non_blocking=True)
+                    if s_d is not None:
+                        s_d.copy_(s_h, non_blocking=True)
+                    ev_in = torch.cuda.Event(); ev_in.record(s_in)
+                s_cmp.wait_event(ev_in)
+                with torch.cuda.stream(s_cmp):
+                    plans[i].execute(c_d, stream=s_cmp.cuda_stream)
+                    ev_c = torch.cuda.Event(); ev_c.record(s_cmp)
+                s_out.wait_event(ev_c)
+                with torch.cuda.stream(s_out):
+                    c_h.copy_(c_d, non_blocking=True)
+            ev = torch.cuda.Event(); ev.record(s_out)
+            done_prev[0] = ev
 
     step(); torch.cuda.synchronize()
+    t0 = time.perf_counter()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record()
-    for _ in range(steps):
-        step()
-    e.record()
+    if chunks == 1:
+        s.record()
+        for _ in range(steps):
+            step()
+        e.record()
+    else:
+        s.record(s_in)
+        for _ in range(steps):
+            step()
+        s_out.wait_event(done_prev[0])
+        e.record(s_out)
     torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3 / steps
     ms = s.elapsed_time(e) / steps
+    for p in plans:
+        p.check(); p.destroy()
     checksum = float(hC.view(-1)[:1024].float().abs().sum())       # the host copy is read
-    return ms, h2d, d2h, checksum
+    return ms, h2d, d2h, checksum, chunks, wall_ms
 
 
 # ------------------------------------------------------------------------- CPU reference arm
@@ -541,13 +615,15 @@ def main() -> int:
                 "algorithmic_bytes_per_launch": res["op_bytes"] + res["out_bytes"],
                 "hbm_gbs_at_this_rate": (res["op_bytes"] + res["out_bytes"]) / (ms_local * 1e-3) / 1e9}
 
-    e2e_ms, h2d, d2h, _ = run_e2e(res, max(3, min(args.steps, 10)), device)
+    e2e_ms, h2d, d2h, _, e2e_chunks, e2e_wall = run_e2e(res, max(3, min(args.steps, 10)), device, kind=kind, shape=(M, n_local, K))
     if world > 1:
         t = torch.tensor([e2e_ms], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e = {"value": flops_total / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-           "ms_per_step": e2e_ms, "note": "pinned host activations in, whole bf16 output back to pinned host memory, every step; weights resident"}
+           "ms_per_step": e2e_ms, "host_clock_ms_per_step": e2e_wall, "row_blocks": e2e_chunks,
+           "note": "pinned host activations in, whole bf16 output back to pinned host memory, every step; weights resident; "
+                   "within a step the copy back of one row block overlaps the copy in and the GEMM of the next, steps do not overlap"}
 
     launches = args.steps * res["info"]["launches"]
     line = {"metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
