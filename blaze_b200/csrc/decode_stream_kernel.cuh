@@ -38,6 +38,7 @@ struct DecodeStreamParams {
     const uint8_t* sfw;      // tiled scale factors of the weights
     const uint8_t* sfx;      // tiled scale factors of the activations (row block 0)
     int sf_katoms;
+    int l2_prefetch;         // weight stages beyond the first ring to pull into L2 before the wait for the predecessor grid
     EpilogueParams epi;
     int* status;
 };
@@ -412,6 +413,14 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
                 if constexpr (Cfg::HAS_SF)
                     bulk_load_1d(ssfw, p.sfw + (static_cast<size_t>(n_tile) * p.sf_katoms + static_cast<size_t>(ks) * 4) * 512, Cfg::SF_BYTES, full_bar(i));
             }
+            // ... and neither do the stages after them: while the predecessor grid drains (its epilogue
+            // and completion leave HBM idle) they are pulled into L2, from where the ring refills faster
+            const int pf_end = min(ks_end, ks_begin + n_pre + p.l2_prefetch);
+            for (int ks = ks_begin + n_pre; ks < pf_end; ++ks) {
+                tma_prefetch_l2_2d(&tm_w, ks * 128, n_tile * 128);
+                if constexpr (Cfg::HAS_SF)
+                    bulk_prefetch_l2(p.sfw + (static_cast<size_t>(n_tile) * p.sf_katoms + static_cast<size_t>(ks) * 4) * 512, Cfg::SF_BYTES);
+            }
             griddep_wait();
 #ifdef BLZ_DECODE_LATE_DEPENDENTS
             griddep_launch_dependents();     // at most one successor prefetches while this grid runs
@@ -671,6 +680,12 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             // packed weights and their scales of the first ring do not depend on earlier kernels
             const int n_pre = min(ks_end - ks_begin, LSTAGES);
             for (int i = 0; i < n_pre; ++i) load_weights(ks_begin + i, i);
+            // later stages: into L2 while the predecessor grid drains
+            const int pf_end = min(ks_end, ks_begin + n_pre + p.l2_prefetch);
+            for (int ks = ks_begin + n_pre; ks < pf_end; ++ks) {
+                tma_prefetch_l2_2d(&tm_w, ks * 128, n_tile * 128);
+                bulk_prefetch_l2(p.sfw + (static_cast<size_t>(n_tile) * p.sf_katoms + static_cast<size_t>(ks) * SUBS) * 512, Cfg::SF_BYTES);
+            }
             griddep_wait();
             int stage = 0; uint32_t phase = 0;
             for (int ks = ks_begin; ks < ks_end; ++ks) {
@@ -879,6 +894,12 @@ decode_w4a16_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
             };
             const int n_pre = min(n_load, WSTAGES);
             for (int i = 0; i < n_pre; ++i) load_weights(ks_begin + i, i);
+            // later stages: into L2 while the predecessor grid drains
+            const int pf_end = min(ks_begin + n_load, ks_begin + n_pre + p.l2_prefetch);
+            for (int ks = ks_begin + n_pre; ks < pf_end; ++ks) {
+                tma_prefetch_l2_2d(&tm_w, ks * 128, n_tile * 128);
+                bulk_prefetch_l2(p.sfw + (static_cast<size_t>(n_tile) * p.sf_katoms + static_cast<size_t>(ks) * SUBS) * 512, Cfg::SF_BYTES);
+            }
             griddep_wait();
             bool ok = true;
             int xi = 0;
