@@ -39,6 +39,7 @@ struct DecodeStreamParams {
     const uint8_t* sfx;      // tiled scale factors of the activations (row block 0)
     int sf_katoms;
     int l2_prefetch;         // weight stages beyond the first ring to pull into L2 before the wait for the predecessor grid
+    int tiles_per_cta;       // W4A16 kernel for M <= 32 only: consecutive weight tiles per CTA (1 elsewhere)
     EpilogueParams epi;
     int* status;
 };
@@ -641,10 +642,16 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     [[maybe_unused]] const long long t_entry = BLZ_T_NOW();
-    const int n_tile = blockIdx.x / p.split;
+    // A CTA takes p.tiles_per_cta consecutive weight tiles (every CTA of a cluster the same ones, each its
+    // own K range): their load stages run through the rings as one sequence, each tile into accumulator
+    // columns of its own; the epilogue, with its reduction over the cluster, then runs once per tile.
+    const int n_tile = (blockIdx.x / p.split) * p.tiles_per_cta;
+    const int n_own = min(p.tiles_per_cta, p.n_tiles - n_tile);
     const int split_idx = blockIdx.x % p.split;
     const int ks_begin = split_idx * p.stages_per_split;
     const int ks_end = min(p.k_stages_total, ks_begin + p.stages_per_split);
+    const int n_load_tile = ks_end - ks_begin;
+    const int n_load_all = n_load_tile * n_own;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < LSTAGES; ++s) { mbar_init(load_full(s), 1); mbar_init(load_empty(s), 1); }
@@ -671,34 +678,44 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if (elect_one()) {
             const uint64_t pol_stream = l2_policy_evict_first();
             const uint64_t pol_keep = l2_policy_evict_last();
-            auto load_weights = [&](int ks, int stage) {
+            auto load_weights = [&](int tile, int ks, int stage) {
                 mbar_arrive_expect_tx(load_full(stage), Cfg::TX_BYTES);
-                tma_load_2d_hint(base + Cfg::PK_OFF + stage * Cfg::PK_BYTES, &tm_w, ks * 128, n_tile * 128, load_full(stage), pol_stream);
-                bulk_load_1d(base + Cfg::SF_OFF + stage * Cfg::SF_BYTES, p.sfw + (static_cast<size_t>(n_tile) * p.sf_katoms + static_cast<size_t>(ks) * SUBS) * 512,
+                tma_load_2d_hint(base + Cfg::PK_OFF + stage * Cfg::PK_BYTES, &tm_w, ks * 128, tile * 128, load_full(stage), pol_stream);
+                bulk_load_1d(base + Cfg::SF_OFF + stage * Cfg::SF_BYTES, p.sfw + (static_cast<size_t>(tile) * p.sf_katoms + static_cast<size_t>(ks) * SUBS) * 512,
                              Cfg::SF_BYTES, load_full(stage));
             };
             // packed weights and their scales of the first ring do not depend on earlier kernels
-            const int n_pre = min(ks_end - ks_begin, LSTAGES);
-            for (int i = 0; i < n_pre; ++i) load_weights(ks_begin + i, i);
-            // later stages: into L2 while the predecessor grid drains
-            const int pf_end = min(ks_end, ks_begin + n_pre + p.l2_prefetch);
-            for (int ks = ks_begin + n_pre; ks < pf_end; ++ks) {
-                tma_prefetch_l2_2d(&tm_w, ks * 128, n_tile * 128);
-                bulk_prefetch_l2(p.sfw + (static_cast<size_t>(n_tile) * p.sf_katoms + static_cast<size_t>(ks) * SUBS) * 512, Cfg::SF_BYTES);
+            const int n_pre = min(n_load_all, LSTAGES);
+            {
+                int tile = n_tile, ks = ks_begin;
+                for (int i = 0; i < n_pre; ++i) {
+                    load_weights(tile, ks, i);
+                    if (++ks == ks_end) { ks = ks_begin; ++tile; }
+                }
+                // later stages of the first tile: into L2 while the predecessor grid drains
+                if (n_pre < n_load_tile) {
+                    const int pf_end = min(ks_end, ks_begin + n_pre + p.l2_prefetch);
+                    for (int kp = ks_begin + n_pre; kp < pf_end; ++kp) {
+                        tma_prefetch_l2_2d(&tm_w, kp * 128, n_tile * 128);
+                        bulk_prefetch_l2(p.sfw + (static_cast<size_t>(n_tile) * p.sf_katoms + static_cast<size_t>(kp) * SUBS) * 512, Cfg::SF_BYTES);
+                    }
+                }
             }
             griddep_wait();
             int stage = 0; uint32_t phase = 0;
-            for (int ks = ks_begin; ks < ks_end; ++ks) {
-                if (ks - ks_begin >= LSTAGES) {
+            int tile = n_tile, ks = ks_begin;
+            for (int li = 0; li < n_load_all; ++li) {
+                if (li >= LSTAGES) {
                     if (!mbar_wait(load_empty(stage), phase ^ 1u, abort_flag)) {
                         atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_PRODUCER); *abort_flag = 1; break;
                     }
-                    load_weights(ks, stage);
+                    load_weights(tile, ks, stage);
                 }
 #pragma unroll
                 for (int j = 0; j < SUBS; ++j)
                     tma_load_2d_hint(base + Cfg::X_OFF + (stage * SUBS + j) * Cfg::X_REGION, &tm_x, (ks * SUBS + j) * 128, 0, load_full(stage), pol_keep);
                 if (++stage == LSTAGES) { stage = 0; phase ^= 1u; }
+                if (++ks == ks_end) { ks = ks_begin; ++tile; }
             }
         }
         __syncwarp();
@@ -712,8 +729,10 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             static_assert(LPERIOD % LSTAGES == 0 && LPERIOD % (2 * OGROUPS) == 0, "unroll period (load stages): rings and phases repeat");
             const uint64_t dx0 = make_desc_k_sw128(base + Cfg::X_OFF);
             const uint32_t a0 = tmem_base + Cfg::OP_COL0;
-            const int n_load = ks_end - ks_begin;
+            const int n_load = n_load_all;
             bool ok = true;
+            int li_tile = 0;                      // load stage within the current tile
+            uint32_t acc0 = tmem_base;            // the current tile's accumulators
             BLZ_T_DECL(t_ready);
             for (int l0 = 0; ok && l0 < n_load; l0 += LPERIOD) {
 #pragma unroll
@@ -735,14 +754,15 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                         const int os = og * SUBS + j;
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            const uint32_t accumulate = (ul | j) != 0 ? 1u : (l0 != 0 ? 1u : 0u);
+                            const uint32_t accumulate = j != 0 ? 1u : (li_tile != 0 ? 1u : 0u);
                             // A: 16 K values = 8 columns of this slot; B: 32 bytes further into the activation tile
-                            umma_f16_ts(tmem_base + 64 * k, a0 + os * Cfg::OP_COLS + k * 8, dx0 + (((ls * SUBS + j) * Cfg::X_REGION + k * 32) >> 4), p.idesc, accumulate);
+                            umma_f16_ts(acc0 + 64 * k, a0 + os * Cfg::OP_COLS + k * 8, dx0 + (((ls * SUBS + j) * Cfg::X_REGION + k * 32) >> 4), p.idesc, accumulate);
                         }
                     }
                     if (!ok) break;
                     tc_commit(og_empty(og));        // the four operand slots of this load stage
                     tc_commit(load_empty(ls));      // its packed bytes were expanded before the MMAs, its activation tiles are read by them
+                    if (++li_tile == n_load_tile) { li_tile = 0; acc0 += MMA_N; }     // next tile: next accumulator columns
                 }
             }
             if (ok) tc_commit(acc_full_bar);
@@ -753,7 +773,7 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const int j = (warp - 8) >> 2, q = warp & 3;               // group = the sub-stage it takes; which 32 tensor-memory lanes
         const int row = q * 32 + lane;
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::OP_COL0;
-        const int n_load = ks_end - ks_begin;
+        const int n_load = n_load_all;
         BLZ_T_DECL(t_load); BLZ_T_DECL(t_slot); BLZ_T_DECL(t_expand); BLZ_T_DECL(t_sync);
         for (int li = 0; li < n_load; ++li) {
             const int ls = li % LSTAGES, og = li % Cfg::OGROUPS, os = og * SUBS + j;
@@ -789,7 +809,8 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     }
 
     // the epilogue warps sleep between polls: the expansion warps need every issue slot
-    decode_epilogue<MMA_N, true, Cfg::NACC>(p, base, gen_base, tmem_base, acc_full_bar, abort_flag, n_tile, split_idx, warp, lane, t_entry);
+    for (int t = 0; t < n_own; ++t)
+        decode_epilogue<MMA_N, true, Cfg::NACC>(p, base, gen_base, tmem_base + t * MMA_N, acc_full_bar, abort_flag, n_tile + t, split_idx, warp, lane, t_entry);
     decode_teardown(tmem_base, Cfg::TMEM_COLS, abort_flag, warp);
 }
 

@@ -417,6 +417,65 @@ def test_w4a16(oracle, cuda_device, kind, shape):
     plan.destroy()
 
 
+@pytest.mark.parametrize("kind,shape,tiles_per_cta,mode", [
+    ("w4a16_f16", (16, 1000, 1056), 3, "none"),       # 8 tiles (last ragged) on 3 CTAs: 3 + 3 + 2; ragged K stage
+    ("w4a16_f16", (16, 1000, 2080), -3, "none"),      # the same with K split over clusters of 2: 3 clusters, 9 stages as 5 + 4
+    ("w4a16_bf16", (30, 896, 4096), -2, "bias_silu"), # clusters of 2, two tiles per CTA (7 tiles: 2 + 2 + 2 + 1)
+    ("w4a16_bf16", (5, 1024, 512), 4, "bias_silu"),   # 4 tiles per CTA: every accumulator column of M <= 16 in use
+    ("w4a16_bf16", (32, 640, 768), 2, "none"),        # M <= 32: two tiles per CTA at most
+    ("w4a16_f16", (24, 640, 768), 7, "none"),         # request beyond what the accumulators hold: clamped to 2
+    ("w4a16_f16", (16, 1024, 512), 2, "swiglu"),
+    ("w4a16_bf16", (8, 19200, 256), 0, "none"),       # 150 tiles > 148 SMs: two tiles per CTA chosen automatically
+])
+def test_w4a16_skinny_several_tiles_per_cta(oracle, cuda_device, monkeypatch, kind, shape, tiles_per_cta, mode):
+    """The W4A16 skinny-M kernel with several consecutive weight tiles per CTA (what it does by itself
+    when the tiles outnumber the SMs), forced on small shapes through BLZ_DECODE_TILES_PER_CTA."""
+    from blaze_b200 import GemmPlan
+    M, N, K = shape
+    split = 1
+    if tiles_per_cta:
+        split = 2 if tiles_per_cta < 0 else 1                # negative: the same tiles per CTA with a 2-way K split
+        tiles_per_cta = abs(tiles_per_cta)
+        monkeypatch.setenv("BLZ_DECODE_TILES_PER_CTA", str(tiles_per_cta))
+        monkeypatch.setenv("BLZ_DECODE_SPLIT", str(split))
+    act = "bf16" if kind.endswith("bf16") else "f16"
+    rng_a, rng_b = np.random.default_rng(42), np.random.default_rng(123)
+    enc = oracle.f32_to_bf16 if act == "bf16" else oracle.f32_to_f16
+    A = enc(rng_a.standard_normal((M, K)).astype(np.float32))
+    bd, bsf, gb = oracle.quantize_nvfp4((rng_b.standard_normal((N, K)) * 0.02).astype(np.float32))
+    acc, alpha = oracle.gemm_w4a16(A, act, bd, bsf, gb)
+    kw = {}
+    if mode == "swiglu":
+        # rows of B read as 16 gate rows, 16 up rows, ...: outputs [M, N/2]
+        g_rows = np.arange(N).reshape(N // 32, 2, 16)[:, 0].reshape(-1); u_rows = g_rows + 16
+        want32 = oracle.swiglu(acc[:, g_rows], alpha, acc[:, u_rows], alpha)
+        n_out = N // 2
+    elif mode == "bias_silu":
+        bias32 = np.random.default_rng(5).standard_normal(N).astype(np.float32)
+        bias_n = oracle.widen(oracle.narrow(bias32, act), act)
+        want32 = oracle.epilogue(acc, alpha, bias=bias_n, mode=mode)
+        kw["bias"] = bits16_to_torch(oracle.narrow(bias32, act), act, cuda_device)
+        n_out = N
+    else:
+        want32 = oracle.epilogue(acc, alpha)
+        n_out = N
+    want = oracle.widen(oracle.narrow(want32, act), act)
+    C = _out_tensor(M, n_out, act, cuda_device)
+    plan = GemmPlan(kind, M, N, K, bits16_to_torch(A, act, cuda_device), _u8(bd, cuda_device), B_sf=_u8(bsf, cuda_device), b_scale=gb, out_dtype=act,
+                    epilogue=mode, **kw)
+    info = plan.info()
+    n_tiles = -(-N // 128)
+    if tiles_per_cta:
+        t_eff = min(tiles_per_cta, 4 if M <= 16 else 2)
+        assert info["variant"] == 3 and info["split_k"] == split and info["grid"] == -(-n_tiles // t_eff) * split, info
+    else:
+        t_eff = 0
+        assert info["variant"] == 3 and info["grid"] <= 148 and info["grid"] < n_tiles * info["split_k"], info
+    _run(plan, C)
+    assert_close(torch_to_f32(C, oracle, act), want, "w4a16 skinny, %d tiles per CTA, %s %s" % (t_eff, kind, shape))
+    plan.destroy()
+
+
 def test_w4a16_config4_sampled(oracle, cuda_device):
     """BASELINE config 4: M=4096, N=22016, K=4096, bf16 activations N(0,1), weights N(0,0.02) as NVFP4."""
     torch = _torch()
