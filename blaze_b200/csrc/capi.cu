@@ -466,12 +466,12 @@ blz_status decode_setup(blz_gemm_plan* p) {
     dp.stages_per_split = static_cast<int>(ceil_div(dp.k_stages_total, dp.split));
     // W4A16, M <= 32: one CTA per SM, so a grid beyond one wave costs a whole second kernel time
     // (22016 x 4096: 172 tiles, 24.6 us).  The CTAs then take several consecutive tiles each, up to what
-    // the accumulator columns hold (64 / instruction N): 86 CTAs x 2 tiles, 22.2 us.  Combining this with
+    // the accumulator columns hold (two for M <= 16): 86 CTAs x 2 tiles, 22.2 us.  Combining this with
     // a K split (58 clusters of 2 x 3 tiles) measured 26.1 us -- the reduction over the cluster runs once
     // per tile -- so the automatic choice never splits; BLZ_DECODE_TILES_PER_CTA with BLZ_DECODE_SPLIT forces both.
     dp.tiles_per_cta = 1;
     if (is_w4a16(d) && dc.mma_n <= 32) {
-        const int t_max = 64 / dc.mma_n;
+        const int t_max = dc.mma_n <= 16 ? 2 : 1;      // DecodeW4A16Config::MAX_TILES
         int t = env_int("BLZ_DECODE_TILES_PER_CTA", 0);
         if (t <= 0) t = (dp.split == 1 && dp.n_tiles > p->num_sms) ? static_cast<int>(ceil_div(dp.n_tiles, p->num_sms)) : 1;
         dp.tiles_per_cta = t > t_max ? t_max : t;

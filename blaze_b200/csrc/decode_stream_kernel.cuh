@@ -128,7 +128,7 @@ __device__ __forceinline__ void decode_store_rows(const float* stag, int p_M, in
 // a K split every thread of every CTA of the cluster meets at two cluster barriers around the
 // reduction through the leader's shared memory (at `base`, free once the main loops are over);
 // the leader applies the epilogue and writes C.
-template <int MMA_N, bool SLEEPY = false, int NACC = 1>
+template <int MMA_N, bool SLEEPY = false, int NACC = 1, int ACC_STRIDE = 64>
 __device__ __forceinline__ void decode_epilogue(const DecodeStreamParams& p, uint32_t base, uint8_t* gen_base, uint32_t tmem_base,
                                                 uint32_t acc_full_bar, volatile int* abort_flag, int n_tile, int split_idx,
                                                 int warp, int lane, [[maybe_unused]] long long t_entry) {
@@ -160,7 +160,7 @@ __device__ __forceinline__ void decode_epilogue(const DecodeStreamParams& p, uin
         if (epi_ok) {
             tc_fence_after_sync();
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-            // NACC > 1: the kernel kept NACC independent partial accumulators 64 columns apart
+            // NACC > 1: the kernel kept NACC independent partial accumulators ACC_STRIDE columns apart
             // (consecutive tcgen05.mma into one accumulator wait for each other); they are added
             // here in a fixed order.
 #pragma unroll
@@ -168,7 +168,7 @@ __device__ __forceinline__ void decode_epilogue(const DecodeStreamParams& p, uin
 #pragma unroll
                 for (int c = 0; c < MMA_N; c += 16) {
                     uint32_t r[16];
-                    tmem_ld16(t_row + a * 64 + c, r);
+                    tmem_ld16(t_row + a * ACC_STRIDE + c, r);
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) acc[c + j] = a == 0 ? __uint_as_float(r[j]) : acc[c + j] + __uint_as_float(r[j]);
@@ -553,7 +553,15 @@ struct DecodeW4A16Config {
     static constexpr int EXPAND_GROUPS = 4;                  // groups of four warps (one per 32 lanes)
     static constexpr int THREADS = 256 + 128 * EXPAND_GROUPS;
     static constexpr int SUBS = 4;                           // sub-stages (64 K values) per load stage
-    static constexpr int OGROUPS = 2;                        // operand slot groups in tensor memory, one per load stage in flight
+    // independent accumulators, one per K = 16 slice of a sub-stage, ACC_STRIDE columns apart; a CTA that
+    // takes several weight tiles puts tile t at column offset t * MMA_N inside every stride
+    static constexpr int NACC = 4;
+    static constexpr uint32_t ACC_STRIDE = MMA_N <= 32 ? 32 : 64;
+    static constexpr int MAX_TILES = ACC_STRIDE / MMA_N;
+    static constexpr uint32_t OP_COL0 = ACC_STRIDE * NACC;
+    static constexpr uint32_t OP_COLS = 32;                  // 64 K values x 16 bit per lane
+    // operand slot groups in tensor memory, one per load stage in flight: whatever the accumulators leave
+    static constexpr int OGROUPS = (512 - OP_COL0) / (SUBS * OP_COLS);
     static constexpr int OSLOTS = OGROUPS * SUBS;
     static constexpr uint32_t X_BYTES = MMA_N * 128;         // one activation tile (64 K values)
     static constexpr uint32_t X_REGION = X_BYTES < 1024 ? 1024 : X_BYTES;
@@ -564,9 +572,6 @@ struct DecodeW4A16Config {
     static constexpr uint32_t X_OFF = PK_OFF + LSTAGES * PK_BYTES;
     static constexpr uint32_t SF_OFF = X_OFF + LSTAGES * SUBS * X_REGION;
     static constexpr uint32_t RING_BYTES = SF_OFF + LSTAGES * SF_BYTES;
-    static constexpr int NACC = 4;                           // independent accumulators, one per K = 16 slice of a sub-stage, 64 columns apart
-    static constexpr uint32_t OP_COL0 = 64 * NACC;
-    static constexpr uint32_t OP_COLS = 32;                  // 64 K values x 16 bit per lane
     static constexpr uint32_t TMEM_COLS = 512;               // the whole tensor memory: one CTA per SM (see SMEM_BYTES)
     static constexpr uint32_t NUM_BARS = 2 * LSTAGES + 2 * OGROUPS + 1;
     static constexpr uint32_t BAR_BYTES = 8 * NUM_BARS + 16;
@@ -756,7 +761,7 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                         for (int k = 0; k < 4; ++k) {
                             const uint32_t accumulate = j != 0 ? 1u : (li_tile != 0 ? 1u : 0u);
                             // A: 16 K values = 8 columns of this slot; B: 32 bytes further into the activation tile
-                            umma_f16_ts(acc0 + 64 * k, a0 + os * Cfg::OP_COLS + k * 8, dx0 + (((ls * SUBS + j) * Cfg::X_REGION + k * 32) >> 4), p.idesc, accumulate);
+                            umma_f16_ts(acc0 + Cfg::ACC_STRIDE * k, a0 + os * Cfg::OP_COLS + k * 8, dx0 + (((ls * SUBS + j) * Cfg::X_REGION + k * 32) >> 4), p.idesc, accumulate);
                         }
                     }
                     if (!ok) break;
@@ -810,7 +815,7 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
     // the epilogue warps sleep between polls: the expansion warps need every issue slot
     for (int t = 0; t < n_own; ++t)
-        decode_epilogue<MMA_N, true, Cfg::NACC>(p, base, gen_base, tmem_base + t * MMA_N, acc_full_bar, abort_flag, n_tile + t, split_idx, warp, lane, t_entry);
+        decode_epilogue<MMA_N, true, Cfg::NACC, Cfg::ACC_STRIDE>(p, base, gen_base, tmem_base + t * MMA_N, acc_full_bar, abort_flag, n_tile + t, split_idx, warp, lane, t_entry);
     decode_teardown(tmem_base, Cfg::TMEM_COLS, abort_flag, warp);
 }
 

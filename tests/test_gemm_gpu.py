@@ -418,12 +418,12 @@ def test_w4a16(oracle, cuda_device, kind, shape):
 
 
 @pytest.mark.parametrize("kind,shape,tiles_per_cta,mode", [
-    ("w4a16_f16", (16, 1000, 1056), 3, "none"),       # 8 tiles (last ragged) on 3 CTAs: 3 + 3 + 2; ragged K stage
-    ("w4a16_f16", (16, 1000, 2080), -3, "none"),      # the same with K split over clusters of 2: 3 clusters, 9 stages as 5 + 4
-    ("w4a16_bf16", (30, 896, 4096), -2, "bias_silu"), # clusters of 2, two tiles per CTA (7 tiles: 2 + 2 + 2 + 1)
-    ("w4a16_bf16", (5, 1024, 512), 4, "bias_silu"),   # 4 tiles per CTA: every accumulator column of M <= 16 in use
-    ("w4a16_bf16", (32, 640, 768), 2, "none"),        # M <= 32: two tiles per CTA at most
-    ("w4a16_f16", (24, 640, 768), 7, "none"),         # request beyond what the accumulators hold: clamped to 2
+    ("w4a16_f16", (16, 1000, 1056), 3, "none"),       # 8 tiles (last ragged), request clamped to 2 per CTA; ragged K stage
+    ("w4a16_f16", (16, 1000, 2080), -2, "none"),      # the same with K split over clusters of 2: 4 clusters, 9 stages as 5 + 4
+    ("w4a16_bf16", (12, 896, 4096), -2, "bias_silu"), # clusters of 2, two tiles per CTA (7 tiles: 2 + 2 + 2 + 1)
+    ("w4a16_bf16", (5, 1024, 512), 2, "bias_silu"),
+    ("w4a16_bf16", (16, 1152, 768), 2, "none"),       # 9 tiles: 2 + 2 + 2 + 2 + 1
+    ("w4a16_f16", (24, 640, 768), 7, "none"),         # M > 16: the accumulator columns hold one tile, the request is clamped
     ("w4a16_f16", (16, 1024, 512), 2, "swiglu"),
     ("w4a16_bf16", (8, 19200, 256), 0, "none"),       # 150 tiles > 148 SMs: two tiles per CTA chosen automatically
 ])
@@ -466,7 +466,7 @@ def test_w4a16_skinny_several_tiles_per_cta(oracle, cuda_device, monkeypatch, ki
     info = plan.info()
     n_tiles = -(-N // 128)
     if tiles_per_cta:
-        t_eff = min(tiles_per_cta, 4 if M <= 16 else 2)
+        t_eff = min(tiles_per_cta, 2 if M <= 16 else 1)
         assert info["variant"] == 3 and info["split_k"] == split and info["grid"] == -(-n_tiles // t_eff) * split, info
     else:
         t_eff = 0
