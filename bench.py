@@ -321,12 +321,14 @@ def run_decode(device, steps, warmup, peaks, kind="nvfp4"):
     return out
 
 
-def run_e2e(res, steps, device, kind=None, shape=None, chunks=8):
+def run_e2e(res, steps, device, kind=None, shape=None, chunks=8, world=1, rank=0):
     """Same GEMM through the public call with HOST buffers: pinned activations (and their scale factors)
     copied to the device, the GEMM, the whole output copied back to pinned host memory, every step.
     The rows are cut into `chunks` blocks with one plan each (same weights), so that within a step the
     copy back of block i overlaps the copy in and the GEMM of block i+1 (three streams).  Steps do not
-    overlap each other: a step's first copy in waits for the previous step's last copy back."""
+    overlap each other: a step's first copy in waits for the previous step's last copy back.
+    With several ranks the host link is shared (the activations are replicated on every GPU), so each
+    rank copies in only its 1/world share of a row block and the ranks all-gather the block over NVLink."""
     import torch
     from blaze_b200 import GemmPlan
     plan, C, A, kw = res["plan"], res["C"], res["A"], res["kw"]
@@ -354,6 +356,11 @@ def run_e2e(res, steps, device, kind=None, shape=None, chunks=8):
     else:
         _, N, K = shape
         Mc = M // chunks
+        share = world > 1 and Mc % (world * 128) == 0        # the same decision on every rank
+        part = Mc // world if share else Mc
+        if share:
+            import torch.distributed as dist
+            h2d = h2d // world
         sf_per_block = sf.numel() // (M // 128) if sf is not None else 0       # tiled scales: contiguous per 128 rows
         s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
         plans, views = [], []
@@ -366,18 +373,31 @@ def run_e2e(res, steps, device, kind=None, shape=None, chunks=8):
                 sfv, hsv = sf.view(-1)[blk], hS.view(-1)[blk]
                 k2["A_sf"] = sfv
             plans.append(GemmPlan(kind, Mc, N, K, A[rows], res["B"], out_dtype=plan.out_dtype, **k2))
-            views.append((A[rows], hA[rows], sfv, hsv, C[rows], hC[rows]))
+            if share:
+                mine = slice(i * Mc + rank * part, i * Mc + (rank + 1) * part)
+                sf_mine = sf_mine_h = None
+                if sf is not None:
+                    b0 = (i * (Mc // 128) + rank * (part // 128)) * sf_per_block
+                    sf_mine, sf_mine_h = sf.view(-1)[b0:b0 + (part // 128) * sf_per_block], hS.view(-1)[b0:b0 + (part // 128) * sf_per_block]
+                views.append((A[mine], hA[mine], sf_mine, sf_mine_h, C[rows], hC[rows], A[rows], sfv))
+            else:
+                views.append((A[rows], hA[rows], sfv, hsv, C[rows], hC[rows], None, None))
         done_prev = [torch.cuda.Event()]
         done_prev[0].record()
 
         def step():
             s_in.wait_event(done_prev[0])
             for i in range(chunks):
-                a_d, a_h, s_d, s_h, c_d, c_h = views[i]
+                a_d, a_h, s_d, s_h, c_d, c_h, a_all, s_all = views[i]
                 with torch.cuda.stream(s_in):
                     a_d.copy_(a_h, non_blocking=True)
                     if s_d is not None:
                         s_d.copy_(s_h, non_blocking=True)
+                    if a_all is not None:
+                        # in place: every rank's share already sits at its offset of the gathered block
+                        dist.all_gather_into_tensor(a_all.view(-1), a_d.view(-1))
+                        if s_all is not None:
+                            dist.all_gather_into_tensor(s_all, s_d)
                     ev_in = torch.cuda.Event(); ev_in.record(s_in)
                 s_cmp.wait_event(ev_in)
                 with torch.cuda.stream(s_cmp):
@@ -389,6 +409,10 @@ def run_e2e(res, steps, device, kind=None, shape=None, chunks=8):
             ev = torch.cuda.Event(); ev.record(s_out)
             done_prev[0] = ev
 
+    # the device copies of the activations are cleared first: what the GEMMs read must have come in through the steps
+    A.zero_()
+    if sf is not None:
+        sf.zero_()
     step(); torch.cuda.synchronize()
     t0 = time.perf_counter()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -409,6 +433,9 @@ def run_e2e(res, steps, device, kind=None, shape=None, chunks=8):
     for p in plans:
         p.check(); p.destroy()
     checksum = float(hC.view(-1)[:1024].float().abs().sum())       # the host copy is read
+    arrived = bool(torch.equal(A.cpu(), hA)) and (sf is None or bool(torch.equal(sf.cpu(), hS)))
+    if not arrived:
+        raise RuntimeError("end-to-end step: the activations on the device differ from the host copy")
     return ms, h2d, d2h, checksum, chunks, wall_ms
 
 
@@ -615,7 +642,7 @@ def main() -> int:
                 "algorithmic_bytes_per_launch": res["op_bytes"] + res["out_bytes"],
                 "hbm_gbs_at_this_rate": (res["op_bytes"] + res["out_bytes"]) / (ms_local * 1e-3) / 1e9}
 
-    e2e_ms, h2d, d2h, _, e2e_chunks, e2e_wall = run_e2e(res, max(3, min(args.steps, 10)), device, kind=kind, shape=(M, n_local, K))
+    e2e_ms, h2d, d2h, _, e2e_chunks, e2e_wall = run_e2e(res, max(3, min(args.steps, 10)), device, kind=kind, shape=(M, n_local, K), world=world, rank=rank)
     if world > 1:
         t = torch.tensor([e2e_ms], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -623,7 +650,8 @@ def main() -> int:
     e2e = {"value": flops_total / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "ms_per_step": e2e_ms, "host_clock_ms_per_step": e2e_wall, "row_blocks": e2e_chunks,
            "note": "pinned host activations in, whole bf16 output back to pinned host memory, every step; weights resident; "
-                   "within a step the copy back of one row block overlaps the copy in and the GEMM of the next, steps do not overlap"}
+                   "within a step the copy back of one row block overlaps the copy in and the GEMM of the next, steps do not overlap"
+                   + ("; each rank copies in 1/%d of a row block's activations and the ranks all-gather it over NVLink (NCCL)" % world if world > 1 else "")}
 
     launches = args.steps * res["info"]["launches"]
     line = {"metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
