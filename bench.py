@@ -328,7 +328,7 @@ def run_e2e(res, steps, device, kind=None, shape=None, chunks=8, world=1, rank=0
     copy back of block i overlaps the copy in and the GEMM of block i+1 (three streams).  Steps do not
     overlap each other: a step's first copy in waits for the previous step's last copy back.
     With several ranks the host link is shared (the activations are replicated on every GPU), so each
-    rank copies in only its 1/world share of a row block and the ranks all-gather the block over NVLink."""
+    rank copies in only its 1/world share of the rows and the ranks all-gather them over NVLink first."""
     import torch
     from blaze_b200 import GemmPlan
     plan, C, A, kw = res["plan"], res["C"], res["A"], res["kw"]
@@ -356,8 +356,7 @@ def run_e2e(res, steps, device, kind=None, shape=None, chunks=8, world=1, rank=0
     else:
         _, N, K = shape
         Mc = M // chunks
-        share = world > 1 and Mc % (world * 128) == 0        # the same decision on every rank
-        part = Mc // world if share else Mc
+        share = world > 1 and M % (world * 128) == 0          # the same decision on every rank
         if share:
             import torch.distributed as dist
             h2d = h2d // world
@@ -373,33 +372,40 @@ def run_e2e(res, steps, device, kind=None, shape=None, chunks=8, world=1, rank=0
                 sfv, hsv = sf.view(-1)[blk], hS.view(-1)[blk]
                 k2["A_sf"] = sfv
             plans.append(GemmPlan(kind, Mc, N, K, A[rows], res["B"], out_dtype=plan.out_dtype, **k2))
-            if share:
-                mine = slice(i * Mc + rank * part, i * Mc + (rank + 1) * part)
-                sf_mine = sf_mine_h = None
-                if sf is not None:
-                    b0 = (i * (Mc // 128) + rank * (part // 128)) * sf_per_block
-                    sf_mine, sf_mine_h = sf.view(-1)[b0:b0 + (part // 128) * sf_per_block], hS.view(-1)[b0:b0 + (part // 128) * sf_per_block]
-                views.append((A[mine], hA[mine], sf_mine, sf_mine_h, C[rows], hC[rows], A[rows], sfv))
-            else:
-                views.append((A[rows], hA[rows], sfv, hsv, C[rows], hC[rows], None, None))
+            views.append((A[rows], hA[rows], sfv, hsv, C[rows], hC[rows]))
+        if share:
+            # this rank's 1/world of all rows (and of the tiled scale blocks, contiguous per 128 rows)
+            mine = slice(rank * (M // world), (rank + 1) * (M // world))
+            a_mine, a_mine_h = A[mine], hA[mine]
+            sf_mine = sf_mine_h = None
+            if sf is not None:
+                n_sf = sf.numel() // world
+                sf_mine, sf_mine_h = sf.view(-1)[rank * n_sf:(rank + 1) * n_sf], hS.view(-1)[rank * n_sf:(rank + 1) * n_sf]
         done_prev = [torch.cuda.Event()]
         done_prev[0].record()
 
         def step():
             s_in.wait_event(done_prev[0])
-            for i in range(chunks):
-                a_d, a_h, s_d, s_h, c_d, c_h, a_all, s_all = views[i]
+            if share:
                 with torch.cuda.stream(s_in):
-                    a_d.copy_(a_h, non_blocking=True)
-                    if s_d is not None:
-                        s_d.copy_(s_h, non_blocking=True)
-                    if a_all is not None:
-                        # in place: every rank's share already sits at its offset of the gathered block
-                        dist.all_gather_into_tensor(a_all.view(-1), a_d.view(-1))
-                        if s_all is not None:
-                            dist.all_gather_into_tensor(s_all, s_d)
-                    ev_in = torch.cuda.Event(); ev_in.record(s_in)
-                s_cmp.wait_event(ev_in)
+                    a_mine.copy_(a_mine_h, non_blocking=True)
+                    if sf_mine is not None:
+                        sf_mine.copy_(sf_mine_h, non_blocking=True)
+                    # in place: every rank's share already sits at its offset of the gathered tensor
+                    dist.all_gather_into_tensor(A.view(-1), a_mine.view(-1))
+                    if sf_mine is not None:
+                        dist.all_gather_into_tensor(sf.view(-1), sf_mine)
+                    ev_all = torch.cuda.Event(); ev_all.record(s_in)
+                s_cmp.wait_event(ev_all)
+            for i in range(chunks):
+                a_d, a_h, s_d, s_h, c_d, c_h = views[i]
+                if not share:
+                    with torch.cuda.stream(s_in):
+                        a_d.copy_(a_h, non_blocking=True)
+                        if s_d is not None:
+                            s_d.copy_(s_h, non_blocking=True)
+                        ev_in = torch.cuda.Event(); ev_in.record(s_in)
+                    s_cmp.wait_event(ev_in)
                 with torch.cuda.stream(s_cmp):
                     plans[i].execute(c_d, stream=s_cmp.cuda_stream)
                     ev_c = torch.cuda.Event(); ev_c.record(s_cmp)
@@ -413,6 +419,7 @@ def run_e2e(res, steps, device, kind=None, shape=None, chunks=8, world=1, rank=0
     A.zero_()
     if sf is not None:
         sf.zero_()
+    torch.cuda.synchronize()
     step(); torch.cuda.synchronize()
     t0 = time.perf_counter()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -651,7 +658,7 @@ def main() -> int:
            "ms_per_step": e2e_ms, "host_clock_ms_per_step": e2e_wall, "row_blocks": e2e_chunks,
            "note": "pinned host activations in, whole bf16 output back to pinned host memory, every step; weights resident; "
                    "within a step the copy back of one row block overlaps the copy in and the GEMM of the next, steps do not overlap"
-                   + ("; each rank copies in 1/%d of a row block's activations and the ranks all-gather it over NVLink (NCCL)" % world if world > 1 else "")}
+                   + ("; each rank copies in 1/%d of the activations and the ranks all-gather them over NVLink (NCCL) before the first row block" % world if world > 1 else "")}
 
     launches = args.steps * res["info"]["launches"]
     line = {"metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
