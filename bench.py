@@ -244,7 +244,7 @@ def run_gemm_workload(kind, M, N, K, device, steps, warmup, flusher, out_dtype="
 
 
 def run_decode(device, steps, warmup, peaks, kind="nvfp4"):
-    """BASELINE config 3: M=16 decode projections (NVFP4; the same shapes for the other kinds on
+    """BASELINE.json config 3: M=16 decode projections (NVFP4; the same shapes for the other kinds on
     request).  Enough distinct weight copies to exceed twice the L2 are cycled inside one CUDA graph
     so that every launch streams its weights from HBM."""
     import torch
@@ -532,7 +532,7 @@ def main() -> int:
     ap.add_argument("--workload", default="nvfp4_8192x28672x8192", choices=list(WORKLOADS) + ["decode"])
     ap.add_argument("--variant", default="auto")
     ap.add_argument("--decode-kind", default="nvfp4", choices=["nvfp4", "fp8", "w4a16_bf16", "w4a16_f16"],
-                    help="operand kind of --workload decode (BASELINE config 3 is nvfp4)")
+                    help="operand kind of --workload decode (BASELINE.json config 3 is nvfp4)")
     ap.add_argument("--no-others", action="store_true", help="skip the secondary workloads reported under 'others'")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
@@ -573,7 +573,7 @@ def main() -> int:
         best = max(dec, key=lambda d: d["hbm_gbs"])
         line = {"metric": "%s_decode_hbm_gbs" % args.decode_kind, "value": best["hbm_gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": best["us_per_gemm"] / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.decode_kind,
-                "data": "synthetic", "config": {"workload": "%s decode M=16, Llama-7B projections (BASELINE configs[2])" % args.decode_kind, "l2": "weight copies > 2x L2 cycled in one CUDA graph"},
+                "data": "synthetic", "config": {"workload": "%s decode M=16, Llama-7B projections (BASELINE.json configs[2])" % args.decode_kind, "l2": "weight copies > 2x L2 cycled in one CUDA graph"},
                 "roofline": {"bound": "hbm", "achieved": best["hbm_gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": best["hbm_gbs"] / peaks["hbm_gbs"],
                              "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get("decode_%dx%d" % (best["N"], best["K"])) if args.decode_kind == "nvfp4" else None, "peak_source": peaks["source"]},
                 "shapes": dec, "worst": worst, "clocks": clk.summary(), "gpu_launches": sum(d["launches"] for d in dec)}
