@@ -469,13 +469,8 @@ blz_status decode_setup(blz_gemm_plan* p) {
     // the accumulator columns hold (two for M <= 16): 86 CTAs x 2 tiles, 22.2 us.  Combining this with
     // a K split (58 clusters of 2 x 3 tiles) measured 26.1 us -- the reduction over the cluster runs once
     // per tile -- so the automatic choice never splits; BLZ_DECODE_TILES_PER_CTA with BLZ_DECODE_SPLIT forces both.
-    dp.tiles_per_cta = 1;
-    if (is_w4a16(d) && dc.mma_n <= 32) {
-        const int t_max = dc.mma_n <= 16 ? 2 : 1;      // DecodeW4A16Config::MAX_TILES
-        int t = env_int("BLZ_DECODE_TILES_PER_CTA", 0);
-        if (t <= 0) t = (dp.split == 1 && dp.n_tiles > p->num_sms) ? static_cast<int>(ceil_div(dp.n_tiles, p->num_sms)) : 1;
-        dp.tiles_per_cta = t > t_max ? t_max : t;
-    }
+    dp.tiles_per_cta = (is_w4a16(d) && dc.mma_n <= 32)
+                     ? decode_tiles_per_cta(dp.n_tiles, p->num_sms, dc.mma_n, dp.split, env_int("BLZ_DECODE_TILES_PER_CTA", 0)) : 1;
     const uint32_t fmt16 = d.kind == BLZ_GEMM_BF16 || d.kind == BLZ_GEMM_W4A16_BF16 ? 1u : 0u;
     // operands are swapped: the instruction's A is the weight tile, its B the activations
     dp.idesc = p->mma_kind == MMA_NVF4 ? make_idesc_nvf4(128, static_cast<uint32_t>(dc.mma_n))

@@ -21,4 +21,15 @@ inline int decode_pick_split(int n_tiles, int k_stages_total, int num_sms, int m
     return s;
 }
 
+// W4A16 skinny-M kernel: consecutive weight tiles one CTA takes.  The kernel holds one CTA per SM, so a
+// grid beyond one wave costs a second kernel time; without a K split the CTAs then share the tiles evenly,
+// up to what the accumulator columns hold (two tiles for an instruction N of 16, one above).  `forced` > 0
+// overrides the choice (still clamped to what the kernel supports).
+inline int decode_tiles_per_cta(int n_tiles, int num_sms, int mma_n, int split, int forced) {
+    const int t_max = mma_n <= 16 ? 2 : 1;
+    int t = forced;
+    if (t <= 0) t = (split == 1 && n_tiles > num_sms) ? (n_tiles + num_sms - 1) / num_sms : 1;
+    return t > t_max ? t_max : t;
+}
+
 }  // namespace blz

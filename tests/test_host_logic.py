@@ -22,6 +22,12 @@ int main() {
                 for (int forced : {0, 1, 2, 3, 8})
                     std::printf("%d %d %d %d %d\n", n_tiles, k_stages, max_split, forced,
                                 blz::decode_pick_split(n_tiles, k_stages, sms, max_split, forced));
+    // tiles per CTA of the W4A16 kernel: (tiles, instruction N, split, forced)
+    for (int n_tiles : {96, 148, 149, 172, 300, 1000})
+        for (int mma_n : {16, 32})
+            for (int split : {1, 2})
+                for (int forced : {0, 1, 2, 5})
+                    std::printf("tiles %d %d %d %d %d\n", n_tiles, mma_n, split, forced, blz::decode_tiles_per_cta(n_tiles, sms, mma_n, split, forced));
     std::printf("max %d %d %d %d\n", blz::decode_max_split(16), blz::decode_max_split(32), blz::decode_max_split(64), blz::decode_max_split(128));
     return 0;
 }
@@ -39,8 +45,10 @@ def split_table(tmp_path_factory):
     exe = d / "split"
     subprocess.run([gxx, "-std=c++17", "-O1", "-I", CSRC, "-o", str(exe), str(src)], check=True)
     out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines()
-    rows = [tuple(int(x) for x in l.split()) for l in out if not l.startswith("max")]
+    rows = [tuple(int(x) for x in l.split()) for l in out if not l.startswith(("max", "tiles"))]
     limits = [int(x) for x in out[-1].split()[1:]]
+    global TILES
+    TILES = {tuple(int(x) for x in l.split()[1:5]): int(l.split()[5]) for l in out if l.startswith("tiles")}
     return rows, limits
 
 
@@ -76,3 +84,15 @@ def test_split_fills_the_device_when_tiles_are_few(split_table):
 def test_max_split_by_activation_tile(split_table):
     _, limits = split_table
     assert limits == [8, 4, 2, 2]
+
+
+TILES = {}
+
+
+def test_tiles_per_cta_of_the_w4a16_kernel(split_table):
+    assert TILES[(96, 16, 1, 0)] == 1 and TILES[(148, 16, 1, 0)] == 1      # one wave: one tile per CTA
+    assert TILES[(149, 16, 1, 0)] == 2 and TILES[(172, 16, 1, 0)] == 2    # beyond one wave: two (86 CTAs for 172 tiles)
+    assert TILES[(1000, 16, 1, 0)] == 2                                   # never more than the accumulator columns hold
+    assert TILES[(172, 32, 1, 0)] == 1                                    # instruction N 32: one tile
+    assert TILES[(172, 16, 2, 0)] == 1                                    # not combined with a K split by itself
+    assert TILES[(96, 16, 2, 2)] == 2 and TILES[(96, 16, 1, 5)] == 2 and TILES[(96, 32, 1, 5)] == 1   # forced, clamped
