@@ -47,13 +47,12 @@ def split_table(tmp_path_factory):
     out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines()
     rows = [tuple(int(x) for x in l.split()) for l in out if not l.startswith(("max", "tiles"))]
     limits = [int(x) for x in out[-1].split()[1:]]
-    global TILES
-    TILES = {tuple(int(x) for x in l.split()[1:5]): int(l.split()[5]) for l in out if l.startswith("tiles")}
-    return rows, limits
+    tiles = {tuple(int(x) for x in l.split()[1:5]): int(l.split()[5]) for l in out if l.startswith("tiles")}
+    return rows, limits, tiles
 
 
 def test_split_is_a_power_of_two_within_limits(split_table):
-    rows, _ = split_table
+    rows, _, _ = split_table
     for n_tiles, k_stages, max_split, forced, s in rows:
         assert s >= 1 and s & (s - 1) == 0, (n_tiles, k_stages, max_split, forced, s)
         assert s <= max_split
@@ -62,7 +61,7 @@ def test_split_is_a_power_of_two_within_limits(split_table):
 
 
 def test_no_split_is_empty_and_every_split_has_two_stages(split_table):
-    rows, _ = split_table
+    rows, _, _ = split_table
     for n_tiles, k_stages, max_split, forced, s in rows:
         per = -(-k_stages // s)
         assert (s - 1) * per < k_stages, "an empty split would leave a CTA of the cluster without work"
@@ -71,7 +70,7 @@ def test_no_split_is_empty_and_every_split_has_two_stages(split_table):
 
 
 def test_split_fills_the_device_when_tiles_are_few(split_table):
-    rows, _ = split_table
+    rows, _, _ = split_table
     table = {(a, b, c, d): s for a, b, c, d, s in rows}
     assert table[(96, 16, 8, 0)] == 1          # 96 tiles: 0.65 CTAs per SM is enough
     assert table[(32, 16, 8, 0)] == 4          # 32 tiles of 16 stages: 128 CTAs
@@ -82,14 +81,12 @@ def test_split_fills_the_device_when_tiles_are_few(split_table):
 
 
 def test_max_split_by_activation_tile(split_table):
-    _, limits = split_table
+    _, limits, _ = split_table
     assert limits == [8, 4, 2, 2]
 
 
-TILES = {}
-
-
 def test_tiles_per_cta_of_the_w4a16_kernel(split_table):
+    _, _, TILES = split_table
     assert TILES[(96, 16, 1, 0)] == 1 and TILES[(148, 16, 1, 0)] == 1      # one wave: one tile per CTA
     assert TILES[(149, 16, 1, 0)] == 2 and TILES[(172, 16, 1, 0)] == 2    # beyond one wave: two (86 CTAs for 172 tiles)
     assert TILES[(1000, 16, 1, 0)] == 2                                   # never more than the accumulator columns hold
