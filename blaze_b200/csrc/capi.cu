@@ -413,6 +413,11 @@ DecodeChoice decode_choice_w4a16_for(int M) {
     if (M > 64) return decode_choice_w4a16_wide<BF16, 3, 4>();
     return M <= 16 ? decode_choice_w4a16<BF16, 16, 6>() : M <= 32 ? decode_choice_w4a16<BF16, 32, 6>() : decode_choice_w4a16<BF16, 64, 3>();
 }
+// The allocation-free entry point (decode_static.cu) cuts K by decode_max_split() alone: the NVFP4
+// stream kernels must support at least that much, or the two paths would partition K differently.
+static_assert(DecodeStreamConfig<MMA_NVF4, 16, 5>::MAX_SPLIT >= 8 && DecodeStreamConfig<MMA_NVF4, 32, 4>::MAX_SPLIT >= 4 &&
+              DecodeStreamConfig<MMA_NVF4, 64, 3>::MAX_SPLIT >= 2, "decode_max_split() exceeds what the NVFP4 stream kernels hold");
+
 DecodeChoice pick_decode_kernel(int mma_kind, bool w4a16, bool bf16, int M) {
     if (w4a16) return bf16 ? decode_choice_w4a16_for<true>(M) : decode_choice_w4a16_for<false>(M);
     switch (mma_kind) {
@@ -462,7 +467,7 @@ blz_status decode_setup(blz_gemm_plan* p) {
     dp.M = d.M; dp.N = d.N;
     dp.n_tiles = static_cast<int>(ceil_div(d.N, 128));
     const int max_split = decode_max_split(dc.mma_n) < dc.max_split ? decode_max_split(dc.mma_n) : dc.max_split;
-    dp.split = decode_pick_split(dp.n_tiles, dp.k_stages_total, p->num_sms, max_split, env_int("BLZ_DECODE_SPLIT", 0));
+    dp.split = decode_pick_split(dp.n_tiles, dp.k_stages_total, p->num_sms, max_split, decode_split_override());
     dp.stages_per_split = static_cast<int>(ceil_div(dp.k_stages_total, dp.split));
     // W4A16, M <= 32: one CTA per SM, so a grid beyond one wave costs a whole second kernel time
     // (22016 x 4096: 172 tiles, 24.6 us).  The CTAs then take several consecutive tiles each, up to what

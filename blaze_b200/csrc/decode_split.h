@@ -2,11 +2,19 @@
 // allocation-free entry point so that both partition K identically (bit-identical results).
 #pragma once
 
+#include <cstdlib>
+
 namespace blz {
 
 // largest K split the skinny-M kernel supports for an instruction N of 16 / 32 / 64 (the partial
 // sums of the other splits must fit the leader's stage buffers)
 inline int decode_max_split(int mma_n) { return mma_n <= 16 ? 8 : mma_n <= 32 ? 4 : 2; }
+
+// BLZ_DECODE_SPLIT=n forces the K split of every skinny-M launch (tuning); 0 / unset = the rule below.
+inline int decode_split_override() {
+    const char* v = getenv("BLZ_DECODE_SPLIT");
+    return (v && *v) ? atoi(v) : 0;
+}
 
 // Smallest power-of-two split that gives at least 0.6 CTAs per SM (measured: 96 CTAs of 16 stages
 // beat 192 of 8 on 148 SMs; 32 CTAs lose to 128), capped by `max_split`, by two

@@ -4,16 +4,26 @@
 // Who that is: serving runtimes that hand every byte of HBM to their own arena when they start
 // (weights, KV cache, activation pools) and then forbid cudaMalloc for the rest of the process --
 // a late allocation there either fails or forces the arena to shrink -- and latency-critical loops
-// in which an allocation's implicit device synchronisation is not acceptable.  The plan API owns
-// its split-K workspace through cudaMalloc; this entry point keeps the same workspace in a
-// fixed array that is part of the library image instead.
+// in which an allocation's implicit device synchronisation is not acceptable.  Plans own their
+// device memory through cudaMalloc (status word, repacked operands, the tiled kernel's split-K
+// partial sums); this entry point keeps its split-K workspace in a fixed array that is part of the
+// library image instead.
 //
-// The kernel is decode_nvf4_kernel from decode_kernel.cuh, unchanged; only where its partial sums,
-// tile counters and error word live differs.
+// The kernel is decode_nvf4_kernel (decode_kernel.cuh): K splits write fp32 partial sums to global
+// memory and the CTA that arrives last at a tile (an atomic ticket) adds them in split order.  It
+// is NOT the kernel a plan with BLZ_VARIANT_DECODE runs (decode_stream_kernel reduces its splits
+// through distributed shared memory and needs no scratch); both cut K with the same rule
+// (decode_split.h) and add the splits in the same order, so their results agree bit for bit.
+//
+// The array is part of the module image: the driver places it in device memory when the module is
+// loaded, which with lazy module loading happens at the first call on a device (the symbol lookup
+// below).  A caller whose arena takes all of HBM must therefore make its first call on each
+// device -- any small shape -- BEFORE it sizes the arena; later calls touch no allocator.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 
@@ -39,7 +49,9 @@ static __device__ __align__(256) unsigned char g_decode_scratch[SCRATCH_BYTES];
 
 constexpr int MAX_DEVICES = 64;
 std::mutex g_setup_mutex;
-unsigned char* g_scratch_ptr[MAX_DEVICES] = {};           // device address of g_decode_scratch, per device
+// Per-device state, written once under the mutex; the pointer is published last (release) and read
+// with acquire, so a thread that sees it also sees the SM count.
+std::atomic<unsigned char*> g_scratch_ptr[MAX_DEVICES];   // device address of g_decode_scratch, per device
 int g_num_sms[MAX_DEVICES] = {};
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -58,16 +70,19 @@ Choice pick(int M) { return M <= 16 ? choice<16, 5>() : M <= 32 ? choice<32, 4>(
 // the kernels' dynamic shared-memory limit and look up the tensor-map encoder.
 blz_status setup_device(int dev) {
     std::lock_guard<std::mutex> lock(g_setup_mutex);
-    if (g_scratch_ptr[dev]) return BLZ_OK;
+    if (g_scratch_ptr[dev].load(std::memory_order_acquire)) return BLZ_OK;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) { (void)cudaGetLastError(); return BLZ_ERR_NO_DEVICE; }
     if (prop.major != 10) return BLZ_ERR_NO_DEVICE;
     void* ptr = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&ptr, g_decode_scratch);
+    // loading the module places the array in device memory: the one implicit allocation of this entry point
+    if (e == cudaErrorMemoryAllocation) { (void)cudaGetLastError(); return BLZ_ERR_OUT_OF_MEMORY; }
     if (e != cudaSuccess || ptr == nullptr) { (void)cudaGetLastError(); return BLZ_ERR_CUDA; }
     for (int m : {16, 32, 64}) {
         const Choice c = pick(m);
-        if (cudaFuncSetAttribute(c.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, c.smem) != cudaSuccess) { (void)cudaGetLastError(); return BLZ_ERR_CUDA; }
+        e = cudaFuncSetAttribute(c.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, c.smem);
+        if (e != cudaSuccess) { (void)cudaGetLastError(); return e == cudaErrorMemoryAllocation ? BLZ_ERR_OUT_OF_MEMORY : BLZ_ERR_CUDA; }
     }
     if (!g_encode) {
         void* f = nullptr;
@@ -79,7 +94,7 @@ blz_status setup_device(int dev) {
         g_encode = reinterpret_cast<EncodeFn>(f);
     }
     g_num_sms[dev] = prop.multiProcessorCount;
-    g_scratch_ptr[dev] = static_cast<unsigned char*>(ptr);
+    g_scratch_ptr[dev].store(static_cast<unsigned char*>(ptr), std::memory_order_release);
     return BLZ_OK;
 }
 
@@ -108,11 +123,12 @@ extern "C" blz_status blz_gemm_nvfp4_decode_static(const void* A, const void* A_
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) { (void)cudaGetLastError(); return BLZ_ERR_NO_DEVICE; }
     if (dev < 0 || dev >= MAX_DEVICES) return BLZ_ERR_UNSUPPORTED;
-    if (!g_scratch_ptr[dev]) {
+    unsigned char* scratch = g_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (!scratch) {
         blz_status s = setup_device(dev);
         if (s) return s;
+        scratch = g_scratch_ptr[dev].load(std::memory_order_acquire);
     }
-    unsigned char* scratch = g_scratch_ptr[dev];
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
     const Choice kc = pick(M);
@@ -121,8 +137,8 @@ extern "C" blz_status blz_gemm_nvfp4_decode_static(const void* A, const void* A_
     dp.n_tiles = (N + 127) / 128;
     const int64_t row_bytes = K / 2;
     dp.k_stages_total = static_cast<int>((row_bytes + 127) / 128);
-    // the same K partition as the plan path, so both give bit-identical sums
-    dp.split = decode_pick_split(dp.n_tiles, dp.k_stages_total, g_num_sms[dev], decode_max_split(kc.mma_n), 0);
+    // the same K partition as the plan path (same rule, same BLZ_DECODE_SPLIT override), so both give bit-identical sums
+    dp.split = decode_pick_split(dp.n_tiles, dp.k_stages_total, g_num_sms[dev], decode_max_split(kc.mma_n), decode_split_override());
     dp.stages_per_split = (dp.k_stages_total + dp.split - 1) / dp.split;
     if (static_cast<size_t>(dp.n_tiles) > MAX_TILES) return BLZ_ERR_TOO_LARGE;
     const size_t partial_need = dp.split > 1 ? static_cast<size_t>(dp.split) * kc.mma_n * dp.n_tiles * 128 * sizeof(float) : 0;
@@ -140,6 +156,8 @@ extern "C" blz_status blz_gemm_nvfp4_decode_static(const void* A, const void* A_
     dp.sf_katoms = static_cast<int>(katoms);
     dp.partial = reinterpret_cast<float*>(scratch + PARTIAL_OFF);
     dp.counters = reinterpret_cast<int*>(scratch + COUNTER_OFF);
+    // Without a status word from the caller a give-up on a bounded wait is NOT reported: the word then
+    // lands in the shared array, where the next call clears it.
     dp.status = d_status ? d_status : reinterpret_cast<int*>(scratch + STATUS_OFF);
     EpilogueParams& e = dp.epi;
     e.C = C; e.bias = nullptr; e.residual = nullptr;

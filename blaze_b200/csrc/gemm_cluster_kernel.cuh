@@ -32,6 +32,10 @@
 
 #include "common.cuh"
 
+#ifndef BLZ_NVF4_OVERLAP
+#define BLZ_NVF4_OVERLAP 0
+#endif
+
 namespace blz {
 
 struct ClusterGemmParams {
@@ -124,16 +128,39 @@ struct ClusterGemmConfig {
     static constexpr uint32_t TX_BYTES = HAS_EXPAND ? A_BYTES + PK_BYTES + 512 : STAGE_BYTES;   // what TMA delivers per stage
     static constexpr uint32_t OUT_BUF_BYTES = 128 * 128;               // 128 rows x 128 bytes
     static constexpr uint32_t OUT_BYTES = 2 * OUT_BUF_BYTES;
-    static constexpr uint32_t ACC_COLS = ACC_BUFS * BN;
+    // NVFP4 pairs with 256-wide tiles: one 256-column accumulator plus a scale-factor slot per stage
+    // fill tensor memory, which leaves the tensor pipe idle while the epilogue drains.  OVERLAP
+    // keeps two accumulators that share 160 columns -- buffer 0 in columns [0, 256), buffer 1 in
+    // [96, 352) -- and three scale-factor slots behind them.  Tiles alternate between the buffers;
+    // the epilogue drains the shared columns first (buffer 0 from its top, buffer 1 from its
+    // bottom) and hands the accumulator back as soon as they are in registers, so the next
+    // tile's MMAs run beside the rest of the drain.
+    static constexpr bool OVERLAP = BLZ_NVF4_OVERLAP && HAS_SF && !WIDE && CG == 2 && BN == 256 && ACC_BUFS == 1;
+    static constexpr uint32_t ACC_OVL_OFF = 96;                         // first column of buffer 1
+    static constexpr uint32_t OVL_COLS = OVERLAP ? BN - ACC_OVL_OFF : BN;  // columns of a tile the next tile's accumulator also uses
+    static constexpr uint32_t ACC_COLS = OVERLAP ? ACC_OVL_OFF + BN : ACC_BUFS * BN;
     static constexpr uint32_t SF_COLS = HAS_SF ? 16 + 4 * (BN / 32) : 0;  // per stage: A 4 per atom, B BN/32 per atom
     static constexpr uint32_t SF_BASE = ACC_COLS;
-    static constexpr int SF_SLOTS = WIDE ? 2 : STAGES;
+    // Scale-factor slots in tensor memory.  One per stage when they fit; otherwise a shorter ring whose
+    // slot s is rewritten once the MMAs that read it (SF_SLOTS stages earlier) have completed.  Two slots
+    // leave one stage time (520 cycles) for "MMA done -> helper sees it -> tcgen05.st -> ready -> MMA
+    // thread sees it", which is not enough; three leave two stage times.
+    static constexpr int SF_SLOTS = OVERLAP ? 3 : WIDE ? 2 : STAGES;
     static constexpr uint32_t TMEM_NEED = ACC_COLS + SF_SLOTS * SF_COLS;
     static constexpr uint32_t TMEM_COLS = tmem_cols_pow2(TMEM_NEED);
     static constexpr uint32_t NUM_BARS = (SHARE == 2 ? 5 : 3) * STAGES + 2 * ACC_BUFS;
     static constexpr uint32_t BAR_BYTES = 8 * NUM_BARS + 16;
     static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BYTES + BAR_BYTES + 1024;
     static constexpr uint32_t READY_COUNT = HAS_SF ? 4 * CG : HAS_EXPAND ? 4 * CG : CG;      // arrivals that make a stage ready for the MMA
+    // DIRECT: the MMA thread waits on ONE barrier per stage, the leader's full barrier.  The operand tiles of
+    // every CTA of the group report their bytes there (CTA pairs: cp.async.bulk.tensor.cta_group::2 with the
+    // leader's barrier), and so do the scale-factor warps once a stage's scale factors sit in tensor memory.
+    // The scale factors land on a barrier of their own (the ready barrier's slot), so their way into tensor
+    // memory runs while the much larger operand tiles are still in flight.  No relay hop, no second poll:
+    // what is left between "tiles landed" and "MMA issued" is one barrier round trip.
+    static constexpr bool DIRECT = (SHARE == 1) && !HAS_EXPAND;
+    static constexpr uint32_t FULL_COUNT = DIRECT ? 1 + (HAS_SF ? 4 * CG : 0) : 1;
+    static constexpr uint32_t AB_TX_BYTES = CG * (A_BYTES + B_BYTES);                          // DIRECT: operand bytes of the whole group per stage
     static_assert(CG == 1 || CG == 2, "CTA group of 1 or 2");
     static_assert(SHARE == 1 || (SHARE == 2 && CG == 2), "B sharing needs CTA pairs");
     static_assert(!HAS_EXPAND || (SHARE == 1 && B_ROWS == 128), "W4A16: every CTA expands one 128-row block of weights per stage");
@@ -179,8 +206,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full_bar(s), 1);
-            mbar_init(ready_bar(s), Cfg::READY_COUNT);
+            mbar_init(full_bar(s), Cfg::FULL_COUNT);
+            mbar_init(ready_bar(s), Cfg::DIRECT ? 1 : Cfg::READY_COUNT);   // DIRECT + scale factors: "this CTA's scale factors landed"
             mbar_init(empty_bar(s), 1);
             if constexpr (SHARE == 2) { mbar_init(bpart_bar(s), 1); mbar_init(partner_ready_bar(s), 1); }
         }
@@ -211,6 +238,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (elect_one()) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
+            [[maybe_unused]] const uint32_t leader_full0 = (Cfg::CLUSTER > 1) ? mapa_shared(full_bar(0), leader_rank) : full_bar(0);
             BLZ_T_DECL(t_wait_empty);
             [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
             for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
@@ -228,12 +256,23 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     BLZ_T_ADD(t_wait_empty, te);
                     const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
+                    // where this stage's bytes report: DIRECT -> the leader's full barrier (operands) and my own
+                    // scale-factor barrier; otherwise my own full barrier
+                    [[maybe_unused]] const uint32_t ab_bar = (Cfg::DIRECT && CG == 2) ? leader_full0 + 8u * stage : full_bar(stage);
+                    const uint32_t sf_tx_bar = Cfg::DIRECT ? ready_bar(stage) : full_bar(stage);
+                    auto load_ab = [&](uint32_t dst, const CUtensorMap* m, int c0, int c1) {
+                        if constexpr (Cfg::DIRECT && CG == 2) tma_load_2d_pair(dst, m, c0, c1, ab_bar);
+                        else tma_load_2d(dst, m, c0, c1, full_bar(stage));
+                    };
                     if constexpr (SHARE == 2) {
                         // everything but my own part of B completes on full_bar: A, scale factors and
                         // the part the partner forwards; my own part has its own barrier so that the
                         // forwarder can pass it on the moment it lands
                         mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES - Cfg::B_LOAD_BYTES);
                         mbar_arrive_cluster(partner_ready_bar(stage), partner);    // my stage is free and armed: send
+                    } else if constexpr (Cfg::DIRECT) {
+                        if constexpr (Cfg::HAS_SF) mbar_arrive_expect_tx(sf_tx_bar, Cfg::SFA_BYTES + Cfg::SFB_BYTES);
+                        if (leader) mbar_arrive_expect_tx(full_bar(stage), Cfg::AB_TX_BYTES);
                     } else {
                         mbar_arrive_expect_tx(full_bar(stage), Cfg::TX_BYTES);
                     }
@@ -243,15 +282,15 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         const uint32_t ssfb = ssfa + Cfg::SFA_BYTES;
                         const size_t katom = static_cast<size_t>(ks) * 4;
                         const size_t a_blk = (static_cast<size_t>(m_tile) * SHARE + pair) * CG + prank;
-                        bulk_load_1d(ssfa, p.sfa + (a_blk * p.sf_katoms + katom) * 512, Cfg::SF_BLOCK_BYTES, full_bar(stage));
+                        bulk_load_1d(ssfa, p.sfa + (a_blk * p.sf_katoms + katom) * 512, Cfg::SF_BLOCK_BYTES, sf_tx_bar);
 #pragma unroll
                         for (int blk = 0; blk < static_cast<int>(Cfg::SFB_BLOCKS); ++blk) {
                             // a ragged last tile may reach past the last block: any valid block will do, those columns are never stored
                             const size_t rb = static_cast<size_t>(min(n_tile * static_cast<int>(Cfg::SFB_BLOCKS) + blk, p.sfb_row_blocks - 1));
-                            bulk_load_1d(ssfb + blk * Cfg::SF_BLOCK_BYTES, p.sfb + (rb * p.sf_katoms + katom) * 512, Cfg::SF_BLOCK_BYTES, full_bar(stage));
+                            bulk_load_1d(ssfb + blk * Cfg::SF_BLOCK_BYTES, p.sfb + (rb * p.sf_katoms + katom) * 512, Cfg::SF_BLOCK_BYTES, sf_tx_bar);
                         }
                     }
-                    tma_load_2d(sa, &tm_a, ks * 128, a_row, full_bar(stage));
+                    load_ab(sa, &tm_a, ks * 128, a_row);
                     if constexpr (SHARE == 2) {
                         // The partner's "ready" for this round also says that it has consumed what I
                         // forwarded last round, so my part of the stage may be overwritten now.
@@ -269,11 +308,11 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     } else if constexpr (Cfg::WIDE) {
                         // this CTA's share of the 256-wide instruction (128 rows, two boxes of 64) and of the 128-wide one (64 rows)
                         const int n0 = n_tile * BN;
-                        tma_load_2d(sb, &tm_b, ks * 128, n0 + static_cast<int>(prank) * 128, full_bar(stage));
-                        tma_load_2d(sb + 8192, &tm_b, ks * 128, n0 + static_cast<int>(prank) * 128 + 64, full_bar(stage));
-                        tma_load_2d(sb + 16384, &tm_b, ks * 128, n0 + 256 + static_cast<int>(prank) * 64, full_bar(stage));
+                        load_ab(sb, &tm_b, ks * 128, n0 + static_cast<int>(prank) * 128);
+                        load_ab(sb + 8192, &tm_b, ks * 128, n0 + static_cast<int>(prank) * 128 + 64);
+                        load_ab(sb + 16384, &tm_b, ks * 128, n0 + 256 + static_cast<int>(prank) * 64);
                     } else {
-                        tma_load_2d(sb, &tm_b, ks * 128, b_row, full_bar(stage));
+                        load_ab(sb, &tm_b, ks * 128, b_row);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -286,7 +325,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (leader && elect_one()) {
             int stage = 0; uint32_t phase = 0;
             int it = 0;
-            [[maybe_unused]] uint32_t g = 0;       // stages issued so far (384-wide tiles: scale-factor slot = g % 2)
+            [[maybe_unused]] uint32_t sslot = 0;   // scale-factor slot of the next stage (a ring of SF_SLOTS)
             bool ok = true;
             BLZ_T_DECL(t_wait_ready); BLZ_T_DECL(t_wait_acc);
             [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
@@ -299,21 +338,21 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 }
                 BLZ_T_ADD(t_wait_acc, ta);
                 tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + buf * BN;
+                const uint32_t d_tmem = tmem_base + (Cfg::OVERLAP ? static_cast<uint32_t>(it & 1) * Cfg::ACC_OVL_OFF : static_cast<uint32_t>(buf) * BN);
                 int ks0, ks1;
                 if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
                 else { int m_e, n_e, m_r; tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_e, n_e); tile_k_range(p, m_e, m_r, ks0, ks1); }
                 for (int ks = ks0; ks < ks1; ++ks) {
                     [[maybe_unused]] const long long tr = BLZ_T_NOW();
-                    if (!mbar_wait(ready_bar(stage), phase, abort_flag)) {
+                    if (!mbar_wait(Cfg::DIRECT ? full_bar(stage) : ready_bar(stage), phase, abort_flag)) {
                         atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
                     }
                     BLZ_T_ADD(t_wait_ready, tr);
                     tc_fence_after_sync();
                     const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
-                    const uint32_t sf_cols = tmem_base + Cfg::SF_BASE + (Cfg::WIDE ? (g & 1u) : static_cast<uint32_t>(stage)) * Cfg::SF_COLS;
-                    ++g;
+                    const uint32_t sf_cols = tmem_base + Cfg::SF_BASE + (Cfg::SF_SLOTS == STAGES ? static_cast<uint32_t>(stage) : sslot) * Cfg::SF_COLS;
+                    if (++sslot == static_cast<uint32_t>(Cfg::SF_SLOTS)) sslot = 0;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         const uint64_t ad = make_desc_k_sw128(sa + k * 32);
@@ -345,7 +384,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         __syncwarp();
     } else if (warp == 2) {
         // ----------------------------------- relay for kinds without scale factors (every CTA)
-        if constexpr (!Cfg::HAS_SF && !Cfg::HAS_EXPAND) {
+        if constexpr (!Cfg::HAS_SF && !Cfg::HAS_EXPAND && !Cfg::DIRECT) {
             if (lane == 0) {
                 int stage = 0; uint32_t phase = 0;
                 bool ok = true;
@@ -419,28 +458,33 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             tc_fence_after_sync();
             const int row0 = ((m_tile * SHARE + static_cast<int>(pair)) * CG + static_cast<int>(prank)) * 128;
             const int r_local = q * 32 + lane;
-            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (Cfg::OVERLAP ? static_cast<uint32_t>(it & 1) * Cfg::ACC_OVL_OFF : static_cast<uint32_t>(buf) * BN);
             if (p.use_tma_store) {
                 if constexpr (Cfg::EPI_SETS == 2) {
-                // (single accumulator buffer: the epilogue is on the tensor pipe's critical path)
-                // The accumulator reads run one chunk ahead of the staging: the columns of chunk i+1
-                // are taken into registers before the store of chunk i is even issued, and the
-                // accumulator goes back to the MMA role right after the last read -- no wait for a
-                // staging buffer or a TMA store sits between "accumulator full" and "accumulator free".
-                const int step = chunk_cols * Cfg::EPI_SETS;
-                const bool two = chunk_cols == 64;                         // 16-bit outputs: 64 columns per chunk
+                // (single accumulator barrier pair: the epilogue is on the tensor pipe's critical path until
+                // it hands the accumulator back)
+                // The two sets take alternate chunks of the drain order.  The accumulator reads run ahead of
+                // the staging: the next chunk's columns are taken into registers as soon as the registers of
+                // the current chunk's halves have been staged, and the accumulator goes back to the MMA role
+                // right after this warp's last read of columns the next tile needs -- no wait for a staging
+                // buffer or a TMA store sits between "accumulator full" and "accumulator free".
+                // With overlapping accumulators those columns are the first OVL_COLS of the drain order:
+                // buffer 0 (even tiles) drains from its top, buffer 1 from its bottom.
+                const bool two = chunk_cols == 64;                         // 16-bit outputs: 64 columns per chunk, read as two halves of 32
+                const int n_chunks = BN / chunk_cols;
+                const bool down = Cfg::OVERLAP && (it & 1) == 0;
+                auto chunk_col = [&](int j) { return down ? BN - (j + 1) * chunk_cols : j * chunk_cols; };
+                const int hf = (two && down) ? 32 : 0;                     // the half of a chunk that comes first in drain order
+                const int n_ov = (static_cast<int>(Cfg::OVL_COLS) + chunk_cols - 1) / chunk_cols;     // chunks that hold shared columns
+                const int j_rel = ((n_ov - 1 - eset) / 2) * 2 + eset;      // this set's last such chunk
+                // the shared columns end inside the first half of that chunk: release without waiting for the second
+                const bool rel_first = two && static_cast<int>(Cfg::OVL_COLS) - j_rel * chunk_cols <= 32;
                 uint32_t acc0[32], acc1[32];
-                auto load_chunk = [&](int c) {
-                    tmem_ld32(t_row + c, acc0);
-                    if (two) tmem_ld32(t_row + c + 32, acc1);
-                    tmem_ld_wait();
-                    if (c + step >= BN) {
-                        // that was this warp's last read of the accumulator
-                        tc_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) {
-                            if constexpr (CG == 1) mbar_arrive(acc_empty_bar(buf)); else mbar_arrive_cluster(acc_empty_bar(buf), leader_rank);
-                        }
+                auto release = [&]() {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (CG == 1) mbar_arrive(acc_empty_bar(buf)); else mbar_arrive_cluster(acc_empty_bar(buf), leader_rank);
                     }
                 };
                 auto stage32 = [&](const uint32_t (&a)[32], uint32_t sbuf, int c, int h) {
@@ -465,19 +509,36 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         }
                     }
                 };
-                int c0 = eset * chunk_cols;
-                if (ok) load_chunk(c0);
-                for (; c0 < BN; c0 += step) {
-                    // One set: the two staging buffers alternate, buffer `obuf` was handed to a TMA
-                    // store two chunks ago.  Two sets: each set owns one buffer and waits for its own
-                    // previous store.  Either way: wait until that store has finished reading it.
-                    if (epi_tid == 0) { if constexpr (Cfg::EPI_SETS == 2) tma_store_wait_read<0>(); else tma_store_wait_read<1>(); }
+                if (ok) {
+                    const int c = chunk_col(eset);
+                    tmem_ld32(t_row + c + hf, acc0);
+                    if (two) tmem_ld32(t_row + c + (hf ^ 32), acc1);
+                    tmem_ld_wait();
+                    if (eset == j_rel) release();
+                }
+                for (int j = eset; j < n_chunks; j += Cfg::EPI_SETS) {
+                    const int c0 = chunk_col(j);
+                    const int jn = j + Cfg::EPI_SETS;
+                    const bool more = ok && jn < n_chunks;
+                    const int cn = more ? chunk_col(jn) : 0;
+                    // each set owns one staging buffer: wait until its previous TMA store has finished reading it
+                    if (epi_tid == 0) tma_store_wait_read<0>();
                     named_barrier_sync(bar_id, 128);
-                    const uint32_t sbuf = out_base + (Cfg::EPI_SETS == 2 ? eset : obuf) * Cfg::OUT_BUF_BYTES;
+                    const uint32_t sbuf = out_base + eset * Cfg::OUT_BUF_BYTES;
                     if (ok) {
-                        stage32(acc0, sbuf, c0, 0);
-                        if (two) stage32(acc1, sbuf, c0, 32);
-                        if (c0 + step < BN) load_chunk(c0 + step);
+                        stage32(acc0, sbuf, c0, hf);
+                        if (more) {
+                            tmem_ld32(t_row + cn + hf, acc0);
+                            if (jn == j_rel && rel_first) { tmem_ld_wait(); release(); }
+                        }
+                        if (two) {
+                            stage32(acc1, sbuf, c0, hf ^ 32);
+                            if (more) tmem_ld32(t_row + cn + (hf ^ 32), acc1);
+                        }
+                        if (more) {
+                            tmem_ld_wait();
+                            if (jn == j_rel && !rel_first) release();
+                        }
                     }
                     fence_proxy_async_smem();
                     named_barrier_sync(bar_id, 128);
@@ -487,7 +548,6 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         }
                         tma_store_commit();
                     }
-                    obuf ^= 1;
                 }
                 } else {
                 // two accumulator buffers: the epilogue overlaps the next tile's MMAs; chunk by chunk
@@ -609,14 +669,15 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
                 else { int m_e, n_e, m_r; tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_e, n_e); tile_k_range(p, m_e, m_r, ks0, ks1); }
                 for (int ks = ks0; ks < ks1; ++ks) {
-                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+                    // DIRECT: only this CTA's scale factors have to have landed, the operand tiles may still be in flight
+                    if (!mbar_wait(Cfg::DIRECT ? ready_bar(stage) : full_bar(stage), phase, abort_flag)) {
                         atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
                     }
-                    if constexpr (Cfg::WIDE) {
-                        // Two scale-factor slots alternate: slot g % 2 was read by the MMAs of stage g - 2,
-                        // whose completion the MMA role committed to that stage's empty barrier.
-                        if (g >= 2) {
-                            const uint32_t gp = g - 2;
+                    if constexpr (Cfg::SF_SLOTS < STAGES) {
+                        // A ring of fewer slots than stages: slot g % SF_SLOTS was read by the MMAs of stage
+                        // g - SF_SLOTS, whose completion the MMA role committed to that stage's empty barrier.
+                        if (g >= static_cast<uint32_t>(Cfg::SF_SLOTS)) {
+                            const uint32_t gp = g - Cfg::SF_SLOTS;
                             if (!mbar_wait(empty_bar(static_cast<int>(gp % STAGES)), (gp / STAGES) & 1u, abort_flag)) {
                                 atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
                             }
@@ -625,7 +686,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     }
                     const uint8_t* ssfa = gen_base + stage * Cfg::STAGE_BYTES + Cfg::A_BYTES + Cfg::B_BYTES;
                     const uint8_t* ssfb = ssfa + Cfg::SFA_BYTES;
-                    const uint32_t t_sf = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::SF_BASE + (Cfg::WIDE ? (g & 1u) : static_cast<uint32_t>(stage)) * Cfg::SF_COLS;
+                    const uint32_t t_sf = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::SF_BASE + (Cfg::SF_SLOTS == STAGES ? static_cast<uint32_t>(stage) : g % Cfg::SF_SLOTS) * Cfg::SF_COLS;
                     ++g;
                     {
                         uint32_t r[16];
@@ -676,7 +737,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     }
                     __syncwarp();
                     if (lane == 0) {
-                        if constexpr (CG == 1) mbar_arrive(ready_bar(stage)); else mbar_arrive_cluster(ready_bar(stage), leader_rank);
+                        const uint32_t done_bar = Cfg::DIRECT ? full_bar(stage) : ready_bar(stage);
+                        if constexpr (CG == 1) mbar_arrive(done_bar); else mbar_arrive_cluster(done_bar, leader_rank);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }

@@ -170,6 +170,24 @@ __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(bar), "l"(policy) : "memory");
 }
+// CTA-pair form: the data goes to this CTA's shared memory, the completion bytes to `bar_cluster`, a
+// shared::cluster address that may name a barrier of the other CTA of the pair (the leader's), so the
+// pair's MMA thread sees both CTAs' tiles land on one barrier.  One source, one destination: no multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, int c0, int c1, uint32_t bar_cluster) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(bar_cluster) : "memory");
+}
+// shared::cluster address of the same shared-memory offset in CTA `cta` of this cluster
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta));
+    return r;
+}
+// arrive on a barrier given by its shared::cluster address
+__device__ __forceinline__ void mbar_arrive_cluster_addr(uint32_t bar_cluster) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
 // Hints: bring a 2-D tile / a contiguous range into L2 without a destination (nothing to wait for).
 // Same alignment rules as the loads: c0 * element size and `src` multiples of 16 bytes, `bytes` too.
 __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* m, int c0, int c1) {
