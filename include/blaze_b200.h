@@ -242,23 +242,29 @@ blz_status blz_gemm_execute_gather(blz_gemm_plan* plan, int32_t n_dst, void* con
  *
  * The skinny-M NVFP4 GEMM (M <= 64) for callers that must not allocate device memory: serving
  * runtimes that gave all of HBM to their own arena at start-up, and loops that cannot afford an
- * allocation's implicit synchronisation.  Same kernel and same result as a plan with
- * BLZ_VARIANT_DECODE; its split-K workspace is a fixed array inside the library image
- * (8 MiB + 8 KiB per GPU, held by every GPU that loads the library until the process exits)
- * instead of plan-owned memory.  The call performs no cudaMalloc / cudaFree and uses no
- * allocating library routine.
+ * allocation's implicit synchronisation.  It runs a split-K kernel of its own (partial sums in
+ * global memory, the last CTA to arrive at a tile adds them in split order) whose workspace is a
+ * fixed array inside the library image (8 MiB + 8 KiB per GPU, held by every GPU that loads the
+ * library until the process exits) instead of plan-owned memory.  It cuts K exactly as a plan with
+ * BLZ_VARIANT_DECODE does and adds the splits in the same order, so the two give bit-identical
+ * results.  The call performs no cudaMalloc / cudaFree and uses no allocating library routine.
  *
  *   A, A_sf_tiled : activations, packed E2M1 [M, K/2] and their scales in the TILED layout
  *   B, B_sf_tiled : weights, packed E2M1 [N, K/2] (K-major) and their TILED scales
  *   C             : [M, ldc] of out_dtype (ldc 0 = N); no bias / activation / residual
  *   d_status      : optional device int the kernel sets non-zero if it gives up on a bounded
- *                   wait (caller clears and reads it); may be null
+ *                   wait (caller clears and reads it).  With a null pointer such a give-up is
+ *                   NOT reported: the word then goes to the shared array and the next call clears it
  *
  * Limits: M <= 64; ceil(N/128) <= 1024; split * rows * ceil(N/128)*128 * 4 bytes of partial sums
  * <= 8 MiB (rows = 16, 32 or 64 for M <= 16, 32, 64).  Anything larger returns
  * BLZ_ERR_TOO_LARGE and launches nothing.
  * The first call on each device resolves the array's device address and raises the kernels'
  * shared-memory limit (with that device current); make that first call before any stream capture.
+ * That first call is also when the driver loads the module that contains the array, i.e. when the
+ * 8 MiB are taken from device memory: a caller whose arena claims all free memory must make one
+ * call per device (any small shape) BEFORE it sizes the arena; if the memory is already gone the
+ * call returns BLZ_ERR_OUT_OF_MEMORY.  Later calls leave the device's free memory untouched.
  * All calls on a device share the one array: the tile counters are cleared at the start of each
  * call, and two calls whose kernels overlap on the GPU (different streams) race on it. */
 blz_status blz_gemm_nvfp4_decode_static(const void* A, const void* A_sf_tiled, float a_scale,
