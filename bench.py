@@ -32,7 +32,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # name: (kind, M, N, K) -- BASELINE.json configs
+    # name: (kind, M, N, K) -- the reference's benchmark configurations
     "nvfp4_8192x28672x8192": ("nvfp4", 8192, 28672, 8192),
     "fp8_4096": ("fp8", 4096, 4096, 4096),
     "w4a16_4096x22016x4096": ("w4a16_bf16", 4096, 22016, 4096),
@@ -43,11 +43,29 @@ WORKLOADS = {
 }
 DECODE_SHAPES = [(16, 12288, 4096), (16, 4096, 4096), (16, 22016, 4096), (16, 4096, 11008)]
 NOMINAL_TFLOPS = {"nvfp4": 9000.0, "fp8": 4500.0, "f16": 2250.0, "bf16": 2250.0, "w4a16_bf16": 2250.0, "w4a16_f16": 2250.0}
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, one ncu capture each on one B200
-# (commands and full figures in profiles/): the default workload read 269.7 MB and wrote 447.5 MB
-# (algorithmic: 169.9 MB of operands, 469.8 MB of output); the decode shape read its weights once.
-NCU_DRAM_BYTES_PER_LAUNCH = {"nvfp4_8192x28672x8192": 717144320, "nvfp4_4096x12288x4096": 87164928, "decode_12288x4096": 28418304}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch come from ncu captures kept in a tracked data
+# file: per workload the bytes, the kernel instance that was captured and the commit it was captured at.
+NCU_TRAFFIC_FILE = os.path.join(ROOT, "profiles", "ncu_dram_traffic.json")
 PEAK_MULT_OVER_BF16 = {"nvfp4": 4.0, "fp8": 2.0, "f16": 1.0, "bf16": 1.0, "w4a16_bf16": 1.0, "w4a16_f16": 1.0}
+
+
+def ncu_traffic(key: str, kernel_info: dict | None) -> tuple:
+    """(bytes per launch or None, provenance dict).  `stale` is set when the kernel that runs now is not the
+    instance the capture was taken from (tile, stages, split or variant differ)."""
+    try:
+        with open(NCU_TRAFFIC_FILE) as f:
+            rec = json.load(f).get(key)
+    except Exception:
+        rec = None
+    if not rec:
+        return None, {"source": "no ncu capture on record for this workload"}
+    prov = {"source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch", "kernel": rec.get("kernel"), "commit": rec.get("commit")}
+    if kernel_info is not None and rec.get("plan"):
+        now = {k: kernel_info.get(k) for k in rec["plan"]}
+        if now != rec["plan"]:
+            prov["stale"] = True
+            prov["plan_now"] = now
+    return rec.get("bytes"), prov
 
 
 def measured_peaks() -> dict:
@@ -243,8 +261,77 @@ def run_gemm_workload(kind, M, N, K, device, steps, warmup, flusher, out_dtype="
                 flops=2.0 * M * N * K, out_bytes=M * N * C.element_size())
 
 
+def run_sustained(plan, C, flops, seconds, device_index, peaks, mult):
+    """The same plan launched back to back (no L2 flush, no gaps) for `seconds`: the rate under the power
+    limit, beside the burst figure of single launches.  SM clock sampled during the region."""
+    import torch
+    for _ in range(3):
+        plan.execute(C)
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record(); plan.execute(C); e.record(); torch.cuda.synchronize()
+    one = max(s.elapsed_time(e), 1e-3)
+    n = max(10, int(seconds * 1e3 / one))
+    with ClockSampler(device_index, period_s=0.02) as clk:
+        s.record()
+        for _ in range(n):
+            plan.execute(C)
+        e.record()
+        torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / n
+    c = clk.summary()
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"launches": n, "seconds": round(ms * n / 1e3, 3), "ms_per_step": ms, "tflops": tf,
+            "frac_of_measured_sustained": tf / (peaks["bf16_tflops_sustained"] * mult),
+            "peak": "%s sustained dense bf16 (%.1f TFLOP/s) x %g" % (peaks["source"], peaks["bf16_tflops_sustained"], mult),
+            "sm_mhz_median": c["sm_mhz"], "ms_times_sm_mhz": (ms * c["sm_mhz"]) if c["sm_mhz"] else None, "reasons": c["reasons"]}, n
+
+
+def run_comparator(kind, M, N, K, device, steps, flusher):
+    """cuBLASLt's own scaled matmul (through torch) on the same operands, same events, same flush: a measured
+    reference point for the block-scaled rates.  A comparator only -- nothing of the library calls it."""
+    import torch
+    import torch.nn.functional as F
+    from blaze_b200 import GemmPlan
+    try:
+        kw, _ = make_operands(kind, M, N, K, device)
+        A, B = kw.pop("A"), kw.pop("B")
+        C = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+        plan = GemmPlan(kind, M, N, K, A, B, out_dtype="bf16", **kw)
+        ours_ms, _ = time_steps(lambda: plan.execute(C), steps, 3, flusher)
+        plan.check()
+        alpha = 1.0
+        if kind == "nvfp4":
+            from torch.nn.functional import ScalingType, SwizzleType
+            a4, b4 = A.view(torch.float4_e2m1fn_x2), B.view(torch.float4_e2m1fn_x2).t()
+            sa, sb = kw["A_sf"].view(torch.float8_e4m3fn), kw["B_sf"].view(torch.float8_e4m3fn)
+            # block scales only (the fp32 tensor scales are applied to its result below): the one-kernel form
+            alpha = kw["a_scale"] * kw["b_scale"]
+            fn = lambda: F.scaled_mm(a4, b4, sa, ScalingType.BlockWise1x16, sb, ScalingType.BlockWise1x16,
+                                     swizzle_a=SwizzleType.SWIZZLE_32_4_4, swizzle_b=SwizzleType.SWIZZLE_32_4_4, output_dtype=torch.bfloat16)
+        elif kind == "fp8":
+            a8, b8 = A.view(torch.float8_e4m3fn), B.view(torch.float8_e4m3fn).t()
+            sa = torch.tensor([kw["a_scale"]], dtype=torch.float32, device=device)
+            sb = torch.tensor([kw["b_scale"]], dtype=torch.float32, device=device)
+            fn = lambda: torch._scaled_mm(a8, b8, sa, sb, out_dtype=torch.bfloat16)
+        else:
+            return {"unavailable": "no comparator for kind %s" % kind}
+        D = fn()
+        torch.cuda.synchronize()
+        lib_ms, _ = time_steps(fn, steps, 3, flusher)
+        rel = float(((D.float() * alpha - C.float()).abs() / C.float().abs().clamp_min(1.0)).max().item())
+        plan.destroy()
+        flops = 2.0 * M * N * K
+        return {"ours_ms": ours_ms, "ours_tflops": flops / ours_ms / 1e9, "cublaslt_ms": lib_ms, "cublaslt_tflops": flops / lib_ms / 1e9,
+                "ours_over_cublaslt": lib_ms / ours_ms, "max_rel_diff": rel}
+    except Exception as ex:
+        return {"unavailable": str(ex)[:200]}
+    finally:
+        torch.cuda.empty_cache()
+
+
 def run_decode(device, steps, warmup, peaks, kind="nvfp4"):
-    """BASELINE.json config 3: M=16 decode projections (NVFP4; the same shapes for the other kinds on
+    """M=16 decode projections of a Llama-7B layer (NVFP4 in the reference's benchmark ; the same shapes for the other kinds on
     request).  Enough distinct weight copies to exceed twice the L2 are cycled inside one CUDA graph
     so that every launch streams its weights from HBM."""
     import torch
@@ -523,6 +610,19 @@ def reference_arm(args, kind, M, N, K, workload_name):
 
 # ---------------------------------------------------------------------------------- main
 
+class GatherMismatch(Exception):
+    """The fused GEMM + all-gather left a block in some rank's output that differs from GEMM + NCCL all-gather."""
+
+
+def compact_decode(dec: list) -> dict:
+    """The decode sweep in a few numbers per shape: [N, K, us per GEMM, GB/s, fraction of the measured HBM rate, us with the weights in L2]."""
+    worst = min(dec, key=lambda d: d["frac_of_measured_hbm"])
+    best = max(dec, key=lambda d: d["frac_of_measured_hbm"])
+    return {"M": dec[0]["M"], "columns": ["N", "K", "us", "GB/s", "frac_of_measured_hbm", "us_weights_in_l2", "split_k", "grid"],
+            "shapes": [[d["N"], d["K"], d["us_per_gemm"], d["hbm_gbs"], d["frac_of_measured_hbm"], d["us_per_gemm_weights_in_l2"], d["split_k"], d["grid"]] for d in dec],
+            "worst_frac": worst["frac_of_measured_hbm"], "best_frac": best["frac_of_measured_hbm"]}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -532,9 +632,10 @@ def main() -> int:
     ap.add_argument("--workload", default="nvfp4_8192x28672x8192", choices=list(WORKLOADS) + ["decode"])
     ap.add_argument("--variant", default="auto")
     ap.add_argument("--decode-kind", default="nvfp4", choices=["nvfp4", "fp8", "w4a16_bf16", "w4a16_f16"],
-                    help="operand kind of --workload decode (BASELINE.json config 3 is nvfp4)")
-    ap.add_argument("--no-others", action="store_true", help="skip the secondary workloads reported under 'others'")
+                    help="operand kind of --workload decode (the reference's decode configuration is nvfp4)")
+    ap.add_argument("--no-others", action="store_true", help="skip the secondary workloads (decode, comparator, others)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--sustained-seconds", type=float, default=1.5, help="length of the back-to-back region (0 = skip)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -566,17 +667,24 @@ def main() -> int:
     peaks = measured_peaks()
     flusher = L2Flusher(device)
 
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     if name == "decode":
         with ClockSampler(local) as clk:
             dec = run_decode(device, args.steps, args.warmup, peaks, kind=args.decode_kind)
-        worst = min(dec, key=lambda d: d["hbm_gbs"])
         best = max(dec, key=lambda d: d["hbm_gbs"])
+        traffic, prov = ncu_traffic("decode_%dx%d" % (best["N"], best["K"]), None) if args.decode_kind == "nvfp4" else (None, {})
         line = {"metric": "%s_decode_hbm_gbs" % args.decode_kind, "value": best["hbm_gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": best["us_per_gemm"] / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.decode_kind,
-                "data": "synthetic", "config": {"workload": "%s decode M=16, Llama-7B projections (BASELINE.json configs[2])" % args.decode_kind, "l2": "weight copies > 2x L2 cycled in one CUDA graph"},
+                "data": "synthetic", "config": {"workload": "%s decode M=16, Llama-7B projections" % args.decode_kind, "l2": "weight copies > 2x L2 cycled in one CUDA graph"},
                 "roofline": {"bound": "hbm", "achieved": best["hbm_gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": best["hbm_gbs"] / peaks["hbm_gbs"],
-                             "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get("decode_%dx%d" % (best["N"], best["K"])) if args.decode_kind == "nvfp4" else None, "peak_source": peaks["source"]},
-                "shapes": dec, "worst": worst, "clocks": clk.summary(), "gpu_launches": sum(d["launches"] for d in dec)}
+                             "traffic": traffic, "traffic_source": prov, "peak_source": peaks["source"]},
+                "decode": compact_decode(dec), "clocks": clk.summary(), "gpu_launches": sum(d["launches"] for d in dec)}
         print(json.dumps(line))
         return 0
 
@@ -587,12 +695,23 @@ def main() -> int:
         res = run_gemm_workload(kind, M, n_local, K, device, args.steps, args.warmup, flusher, barrier=barrier, variant=args.variant,
                                 seed_b=123 + 1000 * rank)
     ms_local = res["ms"]
-    ms = ms_local
+    ms = max_over_ranks(ms_local)
+    launches = args.steps * res["info"]["launches"]
+    mult = PEAK_MULT_OVER_BF16[kind]
+
+    sustained = None
+    if args.sustained_seconds > 0:
+        if barrier:
+            barrier()
+        sustained, n_s = run_sustained(res["plan"], res["C"], 2.0 * M * n_local * K, args.sustained_seconds, local, peaks, mult)
+        launches += n_s
+        s_ms = max_over_ranks(sustained["ms_per_step"])
+        sustained["ms_per_step"] = s_ms
+        sustained["tflops"] = 2.0 * M * N * K / (s_ms * 1e-3) / 1e12
+        sustained["frac_of_measured_sustained"] = sustained["tflops"] / world / (peaks["bf16_tflops_sustained"] * mult)
+
     gather = None
     if world > 1:
-        t = torch.tensor([ms_local], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
         # optional exchange step, timed beside the GEMM: NCCL all-gather of the bf16 output,
         # result layout [world][M][N/world]
         full = torch.empty((world * M, n_local), dtype=res["C"].dtype, device=device)
@@ -601,18 +720,18 @@ def main() -> int:
             res["plan"].execute(res["C"])
             dist.all_gather_into_tensor(full, res["C"])
         g_ms, _ = time_steps(step_gather, max(5, args.steps // 3), 3, flusher, barrier)
-        t = torch.tensor([g_ms], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        g_ms = float(t.item())
+        g_ms = max_over_ranks(g_ms)
         gather = {"ms_per_step_gemm_plus_allgather": g_ms, "tflops": 2.0 * M * N * K / (g_ms * 1e-3) / 1e12,
                   "allgather_bytes_received_per_rank": (world - 1) * M * n_local * 2, "layout": "[world][M][N/world] bf16"}
-        del full
         # the same exchange fused into the GEMM: every epilogue stores its tiles into every rank's
         # full-width output (TMA stores to peer memory over NVLink), then the ranks meet at a
         # one-element all-reduce; result layout [M][N] row-major on every rank
         try:
             from blaze_b200 import sharded
             out = sharded.PeerOutput(M, N, res["C"].dtype)
+            out.local.fill_(-7.0)                    # a block that never arrives stays visible
+            torch.cuda.synchronize()
+            barrier()
             flag = torch.zeros(1, dtype=torch.float32, device=device)
 
             def step_fused():
@@ -620,86 +739,119 @@ def main() -> int:
                 dist.all_reduce(flag)
             f_ms, _ = time_steps(step_fused, max(5, args.steps // 3), 3, flusher, barrier)
             res["plan"].check()
-            t = torch.tensor([f_ms], dtype=torch.float64, device=device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            f_ms = float(t.item())
-            # the fused result must equal the local block, everywhere
-            same = bool(torch.equal(out.local[:, rank * n_local:(rank + 1) * n_local], res["C"]))
+            f_ms = max_over_ranks(f_ms)
+            # Every block of the full-width output -- the one this rank wrote and the ones its peers stored over
+            # NVLink -- must equal what the local GEMMs plus the NCCL all-gather give (the ranks hold
+            # different weights, so a misplaced or stale block cannot pass).
+            step_gather()
+            torch.cuda.synchronize()
+            barrier()
+            want = sharded.gathered_to_full(full.view(world, M, n_local))
+            same_local = bool(torch.equal(out.local[:, rank * n_local:(rank + 1) * n_local], res["C"]))
+            same_all = bool(torch.equal(out.local, want))
+            del want
+            t = torch.tensor([1.0 if same_all else 0.0], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            same_all_ranks = bool(t.item() == 1.0)
             gather["fused"] = {"ms_per_step_gemm_with_peer_stores": f_ms, "tflops": 2.0 * M * N * K / (f_ms * 1e-3) / 1e12,
                                "nvlink_bytes_sent_per_rank": (world - 1) * M * n_local * 2, "layout": "[M][N] row-major on every rank",
-                               "local_block_matches": same}
+                               "local_block_matches": same_local, "all_blocks_match": same_all_ranks}
             out.close()
-        except Exception as ex:   # the exchange variants are reported beside the headline, never instead of it
+            if not same_all_ranks:
+                raise GatherMismatch("fused GEMM + all-gather: the full-width output differs from GEMM + NCCL all-gather on some rank")
+        except GatherMismatch:
+            raise
+        except Exception as ex:   # an unavailable exchange variant is reported beside the headline, never instead of it
             gather["fused"] = {"error": str(ex)[:300]}
+        del full
     flops_total = 2.0 * M * N * K
     value = flops_total / (ms * 1e-3) / 1e12
 
     # roofline of the dominant (only) kernel, per launch on this rank
     flops_launch = 2.0 * M * n_local * K
     achieved = flops_launch / (ms_local * 1e-3) / 1e12
-    peak = peaks["bf16_tflops"] * PEAK_MULT_OVER_BF16[kind]
-    # DRAM bytes per launch from one ncu capture of this exact workload on one GPU
-    # (dram__bytes_read.sum + dram__bytes_write.sum; profiles/gemm_cluster_kernel.md); other
-    # workloads and shard sizes were not captured
-    traffic = NCU_DRAM_BYTES_PER_LAUNCH.get(name) if world == 1 else None
-    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
-                "peak_source": "%s dense bf16 burst (%.1f TFLOP/s) x %g, the nominal %s : bf16 ratio" % (peaks["source"], peaks["bf16_tflops"], PEAK_MULT_OVER_BF16[kind], kind),
+    peak = peaks["bf16_tflops"] * mult
+    plan_key = {k: res["info"][k] for k in ("variant", "tile_m", "tile_n", "stages", "split_k")}
+    traffic, prov = ncu_traffic(name, plan_key) if world == 1 else (None, {"source": "shard sizes were not captured"})
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic, "traffic_source": prov,
+                "peak_source": "%s dense bf16 burst (%.1f TFLOP/s) x %g, the nominal %s : bf16 ratio" % (peaks["source"], peaks["bf16_tflops"], mult, kind),
                 "frac_of_nominal_peak": achieved / NOMINAL_TFLOPS[kind], "nominal_peak": NOMINAL_TFLOPS[kind],
                 "algorithmic_flops_per_launch": flops_launch,
                 "algorithmic_bytes_per_launch": res["op_bytes"] + res["out_bytes"],
                 "hbm_gbs_at_this_rate": (res["op_bytes"] + res["out_bytes"]) / (ms_local * 1e-3) / 1e9}
 
     e2e_ms, h2d, d2h, _, e2e_chunks, e2e_wall = run_e2e(res, max(3, min(args.steps, 10)), device, kind=kind, shape=(M, n_local, K), world=world, rank=rank)
-    if world > 1:
-        t = torch.tensor([e2e_ms], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_ms = max_over_ranks(e2e_ms)
     e2e = {"value": flops_total / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "ms_per_step": e2e_ms, "host_clock_ms_per_step": e2e_wall, "row_blocks": e2e_chunks,
            "note": "pinned host activations in, whole bf16 output back to pinned host memory, every step; weights resident; "
                    "within a step the copy back of one row block overlaps the copy in and the GEMM of the next, steps do not overlap"
                    + ("; each rank copies in 1/%d of the activations and the ranks all-gather them over NVLink (NCCL) before the first row block" % world if world > 1 else "")}
 
-    launches = args.steps * res["info"]["launches"]
     line = {"metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": kind, "data": "synthetic",
             "config": {"workload": name, "kind": kind, "M": M, "N": N, "K": K, "out": "bf16", "accumulate": "fp32",
                        "sharding": "weights split by output columns, %d per rank; activations replicated" % n_local,
                        "l2": "256 MiB write between timed steps", "timing": "CUDA events per step on the launching stream, max over ranks",
                        "kernel": res["info"]},
-            "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clk.summary()}
+            "roofline": roofline, "e2e": e2e, "clocks": clk.summary()}
+    if sustained:
+        line["sustained"] = sustained
     if gather:
         line["gather"] = gather
 
     if rank == 0 and world == 1 and not args.no_others:
+        # the second half of the metric: decode HBM GB/s on the M = 16 projections (NVFP4), compact
+        try:
+            dec = run_decode(device, 5, 3, peaks, kind="nvfp4")
+            line["decode"] = compact_decode(dec)
+            launches += sum(d["launches"] for d in dec)
+        except Exception as ex:
+            line["decode"] = {"error": str(ex)[:200]}
+        # cuBLASLt's scaled matmuls on the same box: what "the peak" is worth for these dtypes in practice
+        comp = {}
+        for w in (name, "nvfp4_4096x12288x4096", "fp8_4096"):
+            k2, m2, n2, kk2 = WORKLOADS[w]
+            comp[w] = run_comparator(k2, m2, n2, kk2, device, min(args.steps, 20), flusher)
+            launches += 23 if "ours_ms" in comp[w] else 0
+        line["comparator"] = comp
+        if "cublaslt_tflops" in comp.get(name, {}):
+            roofline["cublaslt_tflops_same_box"] = comp[name]["cublaslt_tflops"]
+            roofline["frac_of_cublaslt"] = achieved / comp[name]["cublaslt_tflops"]
         others = {}
-        for w in ("fp8_4096", "w4a16_4096x22016x4096", "nvfp4_4096x12288x4096", "bf16_8192", "fp16_256"):
+        for w in ("fp8_4096", "w4a16_4096x22016x4096", "nvfp4_4096x12288x4096", "nvfp4_4096x22016x4096", "bf16_8192", "fp16_256"):
             k2, m2, n2, kk2 = WORKLOADS[w]
             try:
                 r2 = run_gemm_workload(k2, m2, n2, kk2, device, min(args.steps, 20), 3, flusher, out_dtype="f32" if w == "fp16_256" else "bf16")
                 tf = r2["flops"] / (r2["ms"] * 1e-3) / 1e12
-                others[w] = {"ms": r2["ms"], "tflops": tf, "frac_of_nominal_peak": tf / NOMINAL_TFLOPS[k2],
-                             "frac_of_measured_bf16_scaled": tf / (peaks["bf16_tflops"] * PEAK_MULT_OVER_BF16[k2]), "kernel": r2["info"]}
+                i2 = r2["info"]
+                others[w] = {"ms": round(r2["ms"], 5), "tflops": round(tf, 1), "frac_of_nominal_peak": round(tf / NOMINAL_TFLOPS[k2], 4),
+                             "frac_of_measured_bf16_scaled": round(tf / (peaks["bf16_tflops"] * PEAK_MULT_OVER_BF16[k2]), 4),
+                             "tile": "%dx%d" % (i2["tile_m"], i2["tile_n"]), "grid": i2["grid"], "launches_per_execute": i2["launches"]}
                 launches += min(args.steps, 20) * r2["info"]["launches"]
                 r2["plan"].destroy()
                 del r2
                 torch.cuda.empty_cache()
             except Exception as ex:   # a secondary workload must not lose the headline line
                 others[w] = {"error": str(ex)[:200]}
-        for dk in ("nvfp4", "fp8", "w4a16_bf16"):
+        for dk in ("fp8", "w4a16_bf16"):
             try:
-                others["%s_decode_M16" % dk] = run_decode(device, 5, 3, peaks, kind=dk)
+                d2 = run_decode(device, 5, 3, peaks, kind=dk)
+                others["%s_decode_M16" % dk] = compact_decode(d2)["shapes"]
+                launches += sum(d["launches"] for d in d2)
             except Exception as ex:
                 others["%s_decode_M16" % dk] = {"error": str(ex)[:200]}
         for m2 in (16, 512, 2048):
             try:
                 gu = run_gate_up(m2, 11008, 4096, device, 10, 3, flusher)
                 launches += gu.pop("launches")
-                others["w4a16_bf16_gate_up_M%d" % m2] = gu
+                gu.pop("kernel", None)
+                others["w4a16_bf16_gate_up_M%d" % m2] = {k: (round(v, 5) if isinstance(v, float) else v) for k, v in gu.items()}
                 torch.cuda.empty_cache()
             except Exception as ex:
                 others["w4a16_bf16_gate_up_M%d" % m2] = {"error": str(ex)[:200]}
         line["others"] = others
+    line["gpu_launches"] = launches
 
     if rank == 0 and world == 1 and not args.no_cpu:
         ref = cpu_reference_gemm(kind, M, N, K, 12.0)
