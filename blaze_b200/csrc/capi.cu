@@ -816,6 +816,11 @@ blz_status blz_debug_read_timing(unsigned long long* out, int n_words) {
     BLZ_CUDA(cudaMemcpyFromSymbol(out, g_blz_timing, sizeof(unsigned long long) * static_cast<size_t>(n_words)));
     return BLZ_OK;
 }
+blz_status blz_debug_read_trace(unsigned long long* out, int n_words) {
+    BLZ_CUDA(cudaDeviceSynchronize());
+    BLZ_CUDA(cudaMemcpyFromSymbol(out, g_blz_trace, sizeof(unsigned long long) * static_cast<size_t>(n_words)));
+    return BLZ_OK;
+}
 #endif
 
 // ------------------------------------------------------------ bounded-wait self test

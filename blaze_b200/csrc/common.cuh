@@ -41,7 +41,11 @@ __device__ unsigned long long g_blz_timing[1024 * 16];
 #define BLZ_T_NOW() clock64()
 #define BLZ_T_ADD(acc, t0) acc += clock64() - (t0)
 #define BLZ_T_STORE(slot, v) g_blz_timing[(blockIdx.x & 1023) * 16 + (slot)] = static_cast<unsigned long long>(v)
+// event trace of CTA 0: region r (0 = MMA thread per stage, 1..3 = epilogue events), entry i
+__device__ unsigned long long g_blz_trace[4 * 4096];
+#define BLZ_TRACE(region, i) do { if (blockIdx.x == 0 && (i) < 4096) g_blz_trace[(region) * 4096 + (i)] = clock64(); } while (0)
 #else
+#define BLZ_TRACE(region, i)
 #define BLZ_T_DECL(name)
 #define BLZ_T_NOW() 0
 #define BLZ_T_ADD(acc, t0)

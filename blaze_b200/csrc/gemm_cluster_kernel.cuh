@@ -33,7 +33,7 @@
 #include "common.cuh"
 
 #ifndef BLZ_NVF4_OVERLAP
-#define BLZ_NVF4_OVERLAP 0
+#define BLZ_NVF4_OVERLAP 1
 #endif
 
 namespace blz {
@@ -158,6 +158,12 @@ struct ClusterGemmConfig {
     // The scale factors land on a barrier of their own (the ready barrier's slot), so their way into tensor
     // memory runs while the much larger operand tiles are still in flight.  No relay hop, no second poll:
     // what is left between "tiles landed" and "MMA issued" is one barrier round trip.
+    // The 512-thread NVFP4 kernels are launched with 128 registers per thread (the whole register file).
+    // The single-thread roles and the scale-factor warps need far fewer, the epilogue warps want three
+    // 32-column groups of the accumulator in flight: the budgets are re-cut per warpgroup at kernel start.
+    static constexpr bool REG_SPLIT = HAS_SF && EPI_SETS == 2;
+    static constexpr int REGS_ROLES = 48, REGS_SF = 72, REGS_EPI = 192;      // warps 0-3 / 8-11 / 4-7 and 12-15
+    static_assert(!REG_SPLIT || (THREADS == 512 && 128 * (REGS_ROLES + REGS_SF + 2 * REGS_EPI) <= 512 * 128), "register budgets exceed the launch-time pool");
     static constexpr bool DIRECT = (SHARE == 1) && !HAS_EXPAND;
     static constexpr uint32_t FULL_COUNT = DIRECT ? 1 + (HAS_SF ? 4 * CG : 0) : 1;
     static constexpr uint32_t AB_TX_BYTES = CG * (A_BYTES + B_BYTES);                          // DIRECT: operand bytes of the whole group per stage
@@ -233,8 +239,10 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int total_tiles = p.m_tiles * p.n_tiles;
     const int group = blockIdx.x / Cfg::CLUSTER, num_groups = gridDim.x / Cfg::CLUSTER;   // a cluster walks tiles of (128*CG*SHARE) x BN
 
+
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (every CTA)
+        if constexpr (Cfg::REG_SPLIT) warpgroup_regs_dec<Cfg::REGS_ROLES>();
         if (elect_one()) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
@@ -322,10 +330,12 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         __syncwarp();
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer (leader CTA)
+        if constexpr (Cfg::REG_SPLIT) warpgroup_regs_dec<Cfg::REGS_ROLES>();
         if (leader && elect_one()) {
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             [[maybe_unused]] uint32_t sslot = 0;   // scale-factor slot of the next stage (a ring of SF_SLOTS)
+            [[maybe_unused]] int tr_n = 0;
             bool ok = true;
             BLZ_T_DECL(t_wait_ready); BLZ_T_DECL(t_wait_acc);
             [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
@@ -337,6 +347,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_ACC); *abort_flag = 1; ok = false; break;
                 }
                 BLZ_T_ADD(t_wait_acc, ta);
+                BLZ_TRACE(1, it);
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (Cfg::OVERLAP ? static_cast<uint32_t>(it & 1) * Cfg::ACC_OVL_OFF : static_cast<uint32_t>(buf) * BN);
                 int ks0, ks1;
@@ -348,6 +359,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
                     }
                     BLZ_T_ADD(t_wait_ready, tr);
+                    BLZ_TRACE(0, tr_n); ++tr_n;
                     tc_fence_after_sync();
                     const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
                     const uint32_t sb = sa + Cfg::A_BYTES;
@@ -384,6 +396,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         __syncwarp();
     } else if (warp == 2) {
         // ----------------------------------- relay for kinds without scale factors (every CTA)
+        if constexpr (Cfg::REG_SPLIT) warpgroup_regs_dec<Cfg::REGS_ROLES>();
         if constexpr (!Cfg::HAS_SF && !Cfg::HAS_EXPAND && !Cfg::DIRECT) {
             if (lane == 0) {
                 int stage = 0; uint32_t phase = 0;
@@ -407,6 +420,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
     } else if (warp == 3) {
         // ------------------- B sharing: pass my part of every B stage on to the other pair's CTA
+        if constexpr (Cfg::REG_SPLIT) warpgroup_regs_dec<Cfg::REGS_ROLES>();
         if constexpr (SHARE == 2) {
             if (elect_one()) {
                 int stage = 0; uint32_t phase = 0;
@@ -431,6 +445,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
     } else if ((warp >= 4 && warp < 8) || (Cfg::EPI_SETS == 2 && warp >= 12)) {
         // ---------------------------------------------------------------- epilogue (every CTA)
+        if constexpr (Cfg::REG_SPLIT) warpgroup_regs_inc<Cfg::REGS_EPI>();      // waits for what the other warpgroups hand back
         const int q = warp & 3;
         const int eset = warp >= 12 ? 1 : 0;                       // which set of four epilogue warps
         const int epi_tid = threadIdx.x - (eset ? 384 : 128);
@@ -452,6 +467,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_EPILOGUE); *abort_flag = 1; ok = false;
             }
             BLZ_T_ADD(t_wait, tw);
+            if (epi_tid == 0 && eset == 0) BLZ_TRACE(2, 8 * it);
             [[maybe_unused]] const long long tk = BLZ_T_NOW();
             // After a give-up the warps still walk the same named-barrier sequence (without touching
             // tensor memory or C) so that no epilogue warp is left waiting for another.
@@ -481,17 +497,37 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 const bool rel_first = two && static_cast<int>(Cfg::OVL_COLS) - j_rel * chunk_cols <= 32;
                 uint32_t acc0[32], acc1[32];
                 auto release = [&]() {
+                    if (epi_tid == 0) BLZ_TRACE(3, 2 * it + eset);
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) {
                         if constexpr (CG == 1) mbar_arrive(acc_empty_bar(buf)); else mbar_arrive_cluster(acc_empty_bar(buf), leader_rank);
                     }
                 };
+                const float alpha = p.epi.alpha;
+                const bool plain16 = p.epi.mode == EPI_NONE && out_esize == 2;   // scale and narrow only: no temporaries, a handful of instructions per column pair
+                const bool plain_bf16 = plain16 && p.epi.out_type == OUT_BF16;
                 auto stage32 = [&](const uint32_t (&a)[32], uint32_t sbuf, int c, int h) {
-                    float v[32];
-                    epilogue_math32(p.epi, a, v, row0 + r_local, n_tile * BN + c + h, p.M, p.N);
                     // 128-byte swizzle: 16-byte unit j of row r lives at unit (j ^ (r % 8))
                     const uint32_t srow = sbuf + r_local * 128;
+                    if (plain16) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t w[4];
+                            if (plain_bf16) {
+#pragma unroll
+                                for (int t = 0; t < 4; ++t) w[t] = pack_bf16x2(__uint_as_float(a[8 * j + 2 * t]) * alpha, __uint_as_float(a[8 * j + 2 * t + 1]) * alpha);
+                            } else {
+#pragma unroll
+                                for (int t = 0; t < 4; ++t) w[t] = pack2_out(OUT_F16, __uint_as_float(a[8 * j + 2 * t]) * alpha, __uint_as_float(a[8 * j + 2 * t + 1]) * alpha);
+                            }
+                            const uint32_t dst = srow + (((h / 8 + j) ^ (r_local & 7)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                        }
+                        return;
+                    }
+                    float v[32];
+                    epilogue_math32(p.epi, a, v, row0 + r_local, n_tile * BN + c + h, p.M, p.N);
                     if (out_esize == 4) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
@@ -509,36 +545,15 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         }
                     }
                 };
-                if (ok) {
-                    const int c = chunk_col(eset);
-                    tmem_ld32(t_row + c + hf, acc0);
-                    if (two) tmem_ld32(t_row + c + (hf ^ 32), acc1);
-                    tmem_ld_wait();
-                    if (eset == j_rel) release();
-                }
-                for (int j = eset; j < n_chunks; j += Cfg::EPI_SETS) {
-                    const int c0 = chunk_col(j);
-                    const int jn = j + Cfg::EPI_SETS;
-                    const bool more = ok && jn < n_chunks;
-                    const int cn = more ? chunk_col(jn) : 0;
-                    // each set owns one staging buffer: wait until its previous TMA store has finished reading it
+                // one staged chunk: wait for the set's staging buffer, stage both halves, hand the buffer to a store
+                auto emit = [&](int c0, const uint32_t (&first)[32], const uint32_t (&second)[32], auto&& between) {
                     if (epi_tid == 0) tma_store_wait_read<0>();
                     named_barrier_sync(bar_id, 128);
                     const uint32_t sbuf = out_base + eset * Cfg::OUT_BUF_BYTES;
                     if (ok) {
-                        stage32(acc0, sbuf, c0, hf);
-                        if (more) {
-                            tmem_ld32(t_row + cn + hf, acc0);
-                            if (jn == j_rel && rel_first) { tmem_ld_wait(); release(); }
-                        }
-                        if (two) {
-                            stage32(acc1, sbuf, c0, hf ^ 32);
-                            if (more) tmem_ld32(t_row + cn + (hf ^ 32), acc1);
-                        }
-                        if (more) {
-                            tmem_ld_wait();
-                            if (jn == j_rel && !rel_first) release();
-                        }
+                        stage32(first, sbuf, c0, hf);
+                        stage32(second, sbuf, c0, hf ^ 32);
+                        between();
                     }
                     fence_proxy_async_smem();
                     named_barrier_sync(bar_id, 128);
@@ -548,6 +563,87 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         }
                         tma_store_commit();
                     }
+                };
+                bool drained = false;
+                if constexpr (Cfg::OVERLAP) {
+                    if (two) {
+                        // 16-bit output, four chunks of 64 columns; the next tile's accumulator shares the first 160
+                        // columns of the drain order = chunks 0, 1 and the first half of chunk 2.  Set 1 takes chunks
+                        // 1 and 3, set 0 chunks 0 and 2 -- and set 0 reads that first half of chunk 2 together with
+                        // chunk 0 (a third group of 32 registers), so both sets release right after their first
+                        // tcgen05.wait::ld: the tensor pipe waits for two loads, not for any arithmetic.
+                        drained = true;
+                        const int ca = chunk_col(eset), cb = chunk_col(eset + 2);
+                        if (eset == 0) {
+                            uint32_t acc2[32];
+                            if (ok) {
+                                tmem_ld32(t_row + ca + hf, acc0);
+                                tmem_ld32(t_row + ca + (hf ^ 32), acc1);
+                                tmem_ld32(t_row + cb + hf, acc2);
+                                tmem_ld_wait();
+                                if (epi_tid == 0) BLZ_TRACE(2, 8 * it + 2);
+                                release();
+                            }
+                            emit(ca, acc0, acc1, [&]() { tmem_ld32(t_row + cb + (hf ^ 32), acc0); tmem_ld_wait(); });
+                            emit(cb, acc2, acc0, [&]() {});
+                        } else {
+                            if (ok) {
+                                tmem_ld32(t_row + ca + hf, acc0);
+                                tmem_ld32(t_row + ca + (hf ^ 32), acc1);
+                                tmem_ld_wait();
+                                release();
+                            }
+                            uint32_t acc2[32];
+                            emit(ca, acc0, acc1, [&]() { tmem_ld32(t_row + cb + hf, acc2); tmem_ld32(t_row + cb + (hf ^ 32), acc0); tmem_ld_wait(); });
+                            emit(cb, acc2, acc0, [&]() {});
+                        }
+                    }
+                }
+                if (!drained && ok) {
+                    const int c = chunk_col(eset);
+                    tmem_ld32(t_row + c + hf, acc0);
+                    if (two) tmem_ld32(t_row + c + (hf ^ 32), acc1);
+                    tmem_ld_wait();
+                    if (epi_tid == 0 && eset == 0) BLZ_TRACE(2, 8 * it + 2);
+                    if (eset == j_rel) release();
+                }
+                for (int j = eset; !drained && j < n_chunks; j += Cfg::EPI_SETS) {
+                    const int c0 = chunk_col(j);
+                    const int jn = j + Cfg::EPI_SETS;
+                    const bool more = ok && jn < n_chunks;
+                    const int cn = more ? chunk_col(jn) : 0;
+                    // each set owns one staging buffer: wait until its previous TMA store has finished reading it
+                    if (epi_tid == 0) tma_store_wait_read<0>();
+                    named_barrier_sync(bar_id, 128);
+                    const uint32_t sbuf = out_base + eset * Cfg::OUT_BUF_BYTES;
+                    if (epi_tid == 0 && eset == 0 && j == eset) BLZ_TRACE(2, 8 * it + 3);
+                    if (ok) {
+                        stage32(acc0, sbuf, c0, hf);
+                        if (epi_tid == 0 && eset == 0 && j == eset) BLZ_TRACE(2, 8 * it + 4);
+                        if (more) {
+                            tmem_ld32(t_row + cn + hf, acc0);
+                            if (jn == j_rel && rel_first) { tmem_ld_wait(); release(); }
+                        }
+                        if (two) {
+                            stage32(acc1, sbuf, c0, hf ^ 32);
+                            if (epi_tid == 0 && eset == 0 && j == eset) BLZ_TRACE(2, 8 * it + 5);
+                            if (more) tmem_ld32(t_row + cn + (hf ^ 32), acc1);
+                        }
+                        if (more) {
+                            tmem_ld_wait();
+                            if (jn == j_rel && !rel_first) release();
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    named_barrier_sync(bar_id, 128);
+                    if (epi_tid == 0 && eset == 0 && j == eset) BLZ_TRACE(2, 8 * it + 6);
+                    if (epi_tid == 0) {
+                        if (ok) {
+                            for (int d = 0; d < p.n_dst; ++d) tma_store_2d(&out.m[d], sbuf, (n_tile * BN + c0) * out_esize, row0);
+                        }
+                        tma_store_commit();
+                    }
+                    if (epi_tid == 0 && eset == 0 && j == eset) BLZ_TRACE(2, 8 * it + 7);
                 }
                 } else {
                 // two accumulator buffers: the epilogue overlaps the next tile's MMAs; chunk by chunk
@@ -621,6 +717,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 if constexpr (CG == 1) mbar_arrive(acc_empty_bar(buf)); else mbar_arrive_cluster(acc_empty_bar(buf), leader_rank);
             }
             BLZ_T_ADD(t_work, tk);
+            if (epi_tid == 0 && eset == 0) BLZ_TRACE(2, 8 * it + 1);
         }
         if (epi_tid == 0 && eset == 0) { BLZ_T_STORE(5, t_wait); BLZ_T_STORE(6, t_work); BLZ_T_STORE(7, BLZ_T_NOW() - t_begin); }
         if (epi_tid == 0) tma_store_wait_all<0>();     // staging memory must outlive the last store's reads
@@ -659,6 +756,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
     } else if (warp >= 8 && warp < 12) {
         // -------------------------------- NVFP4: scale factors smem -> registers -> tensor memory
+        if constexpr (Cfg::REG_SPLIT) warpgroup_regs_dec<Cfg::REGS_SF>();
         if constexpr (Cfg::HAS_SF) {
             const int q = warp & 3;
             int stage = 0; uint32_t phase = 0;

@@ -58,6 +58,13 @@ __device__ __forceinline__ bool elect_one() {
 #define BLZ_POLL_SLEEP_NS 32
 #endif
 
+// Register budget of a warpgroup (four consecutive warps; every warp of the group must execute the same
+// call).  `dec` hands registers back to the CTA's pool, `inc` takes them and waits until the pool holds
+// enough -- so the new budgets of all warpgroups together must not exceed what the CTA was launched with
+// (threads x registers per thread of the launch bound), or `inc` never returns.
+template <int N> __device__ __forceinline__ void warpgroup_regs_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void warpgroup_regs_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+
 // ---------------------------------------------------------------- mbarrier
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
