@@ -660,8 +660,8 @@ def main() -> int:
     device = torch.device("cuda", local)
     barrier = None
     if world > 1:
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"          # keep NCCL's version banner off stdout: one JSON line only
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "WARN"):
+            os.environ.pop("NCCL_DEBUG")               # these levels print NCCL's version banner to stdout: one JSON line only
         dist.init_process_group("nccl", device_id=device)
         barrier = lambda: dist.barrier(device_ids=[local])
     peaks = measured_peaks()
