@@ -19,6 +19,7 @@ F16, BF16, F32 = range(3)
 EPI_NONE, EPI_BIAS, EPI_SILU, EPI_BIAS_SILU, EPI_RESIDUAL_ADD, EPI_SWIGLU = range(6)
 B_KMAJOR, B_NMAJOR = range(2)
 SF_ROWMAJOR, SF_TILED = range(2)
+FLAG_CLC_SCHEDULER = 1
 VARIANT_AUTO, VARIANT_TILE_128x128, VARIANT_PAIR_256x256, VARIANT_DECODE, VARIANT_QUAD_512x256, VARIANT_PAIR_256x384 = range(6)
 
 KINDS = {"f16": GEMM_F16, "bf16": GEMM_BF16, "fp8": GEMM_FP8, "nvfp4": GEMM_NVFP4,
@@ -47,7 +48,7 @@ class GemmDesc(ctypes.Structure):
         ("A", ctypes.c_void_p), ("A_sf", ctypes.c_void_p), ("B", ctypes.c_void_p), ("B_sf", ctypes.c_void_p),
         ("a_scale", ctypes.c_float), ("b_scale", ctypes.c_float),
         ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("ldc", ctypes.c_int64),
-        ("b_scale2", ctypes.c_float), ("reserved", ctypes.c_int32),
+        ("b_scale2", ctypes.c_float), ("flags", ctypes.c_int32),
     ]
 
 
@@ -55,7 +56,7 @@ class PlanInfo(ctypes.Structure):
     _fields_ = [
         ("variant", ctypes.c_int32), ("tile_m", ctypes.c_int32), ("tile_n", ctypes.c_int32), ("stages", ctypes.c_int32),
         ("split_k", ctypes.c_int32), ("grid", ctypes.c_int32), ("smem_bytes", ctypes.c_int32), ("tmem_cols", ctypes.c_int32),
-        ("launches", ctypes.c_int32), ("workspace_bytes", ctypes.c_int64),
+        ("launches", ctypes.c_int32), ("scheduler", ctypes.c_int32), ("workspace_bytes", ctypes.c_int64),
     ]
 
 

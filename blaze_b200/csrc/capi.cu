@@ -170,6 +170,7 @@ struct blz_gemm_plan {
     int decode_smem = 0, decode_stages = 0, decode_split = 1, decode_mma_n = 0, decode_tmem = 0, decode_threads = 0;
     const void* decode_fn = nullptr;
     int launches = 1;
+    int clc = 0;
 };
 
 namespace {
@@ -363,6 +364,15 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1, bool wide = fa
     }
     const int64_t groups = tiles < max_groups ? tiles : max_groups;
     p->grid = static_cast<int>(groups) * csize;
+    // Dynamic scheduling: one cluster per tile in the grid; clusters that are running take over the tiles of
+    // clusters that have not started (cluster launch control).  On request (desc.flags / BLZ_SCHEDULER=clc);
+    // not for the variants whose roles walk a fixed tile sequence (B sharing, in-kernel W4A16 expansion).
+    const char* sched_env = getenv("BLZ_SCHEDULER");
+    bool want_clc = (d.flags & BLZ_FLAG_CLC_SCHEDULER) != 0;
+    if (sched_env && *sched_env) want_clc = strcmp(sched_env, "clc") == 0;
+    cp.clc = (want_clc && share == 1 && !fused_w4 && tiles * csize <= 0x7FFFFFFF) ? 1 : 0;
+    if (cp.clc) p->grid = static_cast<int>(tiles) * csize;
+    p->clc = cp.clc;
     return BLZ_OK;
 }
 
@@ -786,6 +796,7 @@ blz_status blz_gemm_plan_info(const blz_gemm_plan* p, blz_plan_info* info) {
         info->grid = p->grid; info->smem_bytes = p->cc.smem; info->tmem_cols = p->cc.tmem_cols;
     }
     info->launches = p->launches;
+    info->scheduler = p->clc ? 1 : 0;
     info->workspace_bytes = p->owned_bytes;
     return BLZ_OK;
 }

@@ -55,6 +55,7 @@ struct ClusterGemmParams {
     int sf_katoms;
     int use_tma_store;       // C (and its pitch) 16-byte aligned: epilogue stores through the output maps
     int n_dst;               // output maps in use: 1, or one per GPU for the fused all-gather
+    int clc;                 // tiles come from the hardware's launch queue (cluster launch control) instead of a fixed stride
     EpilogueParams epi;
     int* status;
 };
@@ -148,8 +149,16 @@ struct ClusterGemmConfig {
     static constexpr int SF_SLOTS = OVERLAP ? 3 : WIDE ? 2 : STAGES;
     static constexpr uint32_t TMEM_NEED = ACC_COLS + SF_SLOTS * SF_COLS;
     static constexpr uint32_t TMEM_COLS = tmem_cols_pow2(TMEM_NEED);
-    static constexpr uint32_t NUM_BARS = (SHARE == 2 ? 5 : 3) * STAGES + 2 * ACC_BUFS;
-    static constexpr uint32_t BAR_BYTES = 8 * NUM_BARS + 16;
+    // Dynamic tile scheduling (cluster launch control): the grid holds one cluster per tile; a running cluster
+    // that finishes a tile cancels a cluster that has not started yet and takes its tile.  One scheduler thread
+    // (leader CTA, warp 3) talks to the hardware and hands tile indices to every role of every CTA of the
+    // cluster through a ring of SCHED_SLOTS slots in shared memory.
+    static constexpr int SCHED_SLOTS = 2;
+    static constexpr bool CLC_OK = (SHARE == 1) && !HAS_EXPAND;               // kernels that can run with p.clc
+    // roles that take tile indices, per CTA: producer, epilogue warps, scale-factor warps; plus the MMA thread once
+    static constexpr uint32_t SCHED_CONSUMERS = CG * (1 + 4 * EPI_SETS + (HAS_SF ? 4 : 0)) + 1;
+    static constexpr uint32_t NUM_BARS = (SHARE == 2 ? 5 : 3) * STAGES + 2 * ACC_BUFS + 2 * SCHED_SLOTS + 1;
+    static constexpr uint32_t BAR_BYTES = 8 * NUM_BARS + 16 + 16 + 16;          // + launch-control answer (16-byte aligned) + tile slots
     static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BYTES + BAR_BYTES + 1024;
     static constexpr uint32_t READY_COUNT = HAS_SF ? 4 * CG : HAS_EXPAND ? 4 * CG : CG;      // arrivals that make a stage ready for the MMA
     // DIRECT: the MMA thread waits on ONE barrier per stage, the leader's full barrier.  The operand tiles of
@@ -197,9 +206,15 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // B sharing only: "my own part of B landed" and "the other pair's CTA can take my part"
     auto bpart_bar = [&](int s) { return bar_base + 8u * (3 * STAGES + 2 * ACC_BUFS + s); };
     auto partner_ready_bar = [&](int s) { return bar_base + 8u * (4 * STAGES + 2 * ACC_BUFS + s); };
+    constexpr uint32_t SCHED_BAR0 = (SHARE == 2 ? 5 : 3) * STAGES + 2 * ACC_BUFS;
+    auto sched_full_bar = [&](int s) { return bar_base + 8u * (SCHED_BAR0 + s); };
+    auto sched_empty_bar = [&](int s) { return bar_base + 8u * (SCHED_BAR0 + Cfg::SCHED_SLOTS + s); };
+    const uint32_t clc_bar = bar_base + 8u * (SCHED_BAR0 + 2 * Cfg::SCHED_SLOTS);
     const uint32_t slot_off = STAGES * Cfg::STAGE_BYTES + Cfg::OUT_BYTES + 8u * Cfg::NUM_BARS;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen_base + slot_off);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + slot_off + 4);
+    const uint32_t clc_response = (base + slot_off + 16u + 15u) & ~15u;          // 16 bytes, written by the hardware
+    const uint32_t sched_tile0 = clc_response + 16u;                            // SCHED_SLOTS x int
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = (Cfg::CLUSTER == 1) ? 0u : cluster_cta_rank();
@@ -218,6 +233,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             if constexpr (SHARE == 2) { mbar_init(bpart_bar(s), 1); mbar_init(partner_ready_bar(s), 1); }
         }
         for (int b = 0; b < ACC_BUFS; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 4 * CG * Cfg::EPI_SETS); }
+        for (int s = 0; s < Cfg::SCHED_SLOTS; ++s) { mbar_init(sched_full_bar(s), 1); mbar_init(sched_empty_bar(s), Cfg::SCHED_CONSUMERS); }
+        mbar_init(clc_bar, 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -238,6 +255,36 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
     const int total_tiles = p.m_tiles * p.n_tiles;
     const int group = blockIdx.x / Cfg::CLUSTER, num_groups = gridDim.x / Cfg::CLUSTER;   // a cluster walks tiles of (128*CG*SHARE) x BN
+    const bool use_clc = Cfg::CLC_OK && p.clc != 0;
+
+    // Where a role gets its tiles from.  Static: tile = group, group + num_groups, ...  Dynamic: the scheduler's
+    // ring; every role of the cluster reads every slot (the tile index, -1 = no more) and then frees it with one
+    // arrive on the leader's empty barrier -- warp-wide roles through lane 0 once all lanes have read.
+    struct TileFeed {
+        int tile, stride, total, n;
+        bool dyn, warp_wide;
+        uint32_t full0, empty0_leader, tile0;
+        const volatile int* abort_flag;
+        __device__ __forceinline__ int take() {
+            if (!dyn) { const int t = tile; tile += stride; return t < total ? t : -1; }
+            const int s = n % Cfg::SCHED_SLOTS;
+            const uint32_t par = static_cast<uint32_t>(n / Cfg::SCHED_SLOTS) & 1u;
+            ++n;
+            if (!mbar_wait_acquire_cluster(full0 + 8u * s, par, abort_flag)) return -1;
+            int t;
+            asm volatile("ld.shared.b32 %0, [%1];" : "=r"(t) : "r"(tile0 + 4u * s) : "memory");
+            if (warp_wide) __syncwarp();
+            if (!warp_wide || (threadIdx.x & 31) == 0) mbar_arrive_cluster_addr(empty0_leader + 8u * s);
+            return t;
+        }
+    };
+    auto make_feed = [&](bool warp_wide) {
+        TileFeed f;
+        f.tile = group; f.stride = num_groups; f.total = total_tiles; f.n = 0; f.dyn = use_clc; f.warp_wide = warp_wide;
+        f.full0 = sched_full_bar(0); f.tile0 = sched_tile0; f.abort_flag = abort_flag;
+        f.empty0_leader = (Cfg::CLUSTER > 1) ? mapa_shared(sched_empty_bar(0), leader_rank) : sched_empty_bar(0);
+        return f;
+    };
 
 
     if (warp == 0) {
@@ -249,7 +296,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             [[maybe_unused]] const uint32_t leader_full0 = (Cfg::CLUSTER > 1) ? mapa_shared(full_bar(0), leader_rank) : full_bar(0);
             BLZ_T_DECL(t_wait_empty);
             [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
-            for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
+            TileFeed feed = make_feed(false);
+            for (int tile = feed.take(); ok && tile >= 0; tile = feed.take()) {
                 int m_tile, n_tile;
                 int m_ext, ks0, ks1;
                 tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_ext, n_tile);
@@ -339,7 +387,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             bool ok = true;
             BLZ_T_DECL(t_wait_ready); BLZ_T_DECL(t_wait_acc);
             [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
-            for (int tile = group; ok && tile < total_tiles; tile += num_groups, ++it) {
+            TileFeed feed = make_feed(false);
+            for (int tile = feed.take(); ok && tile >= 0; tile = feed.take(), ++it) {
                 const int buf = it % ACC_BUFS;
                 const uint32_t use = static_cast<uint32_t>(it / ACC_BUFS);
                 [[maybe_unused]] const long long ta = BLZ_T_NOW();
@@ -443,6 +492,38 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
             __syncwarp();
         }
+        if constexpr (Cfg::CLC_OK) {
+            // ------------------------------------- tile scheduler (leader CTA, dynamic scheduling only)
+            if (use_clc && leader && elect_one()) {
+                int tile = group;                      // the tile this cluster was launched for
+                bool ok = true;
+#pragma unroll 1
+                for (uint32_t n = 0; ok; ++n) {
+                    const int s = static_cast<int>(n % Cfg::SCHED_SLOTS);
+                    // the slot is free once every role of every CTA has read what it held
+                    if (n >= static_cast<uint32_t>(Cfg::SCHED_SLOTS) &&
+                        !mbar_wait(sched_empty_bar(s), ((n / Cfg::SCHED_SLOTS) - 1u) & 1u, abort_flag)) {
+                        atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_PRODUCER); *abort_flag = 1; break;
+                    }
+#pragma unroll
+                    for (uint32_t c = 0; c < static_cast<uint32_t>(CG); ++c) {
+                        const uint32_t cta = leader_rank + c;
+                        st_shared_cluster_u32(Cfg::CLUSTER > 1 ? mapa_shared(sched_tile0 + 4u * s, cta) : sched_tile0 + 4u * s, static_cast<uint32_t>(tile));
+                        mbar_arrive_release_cluster_addr(Cfg::CLUSTER > 1 ? mapa_shared(sched_full_bar(s), cta) : sched_full_bar(s));
+                    }
+                    if (tile < 0) break;
+                    // ask the launch queue for a cluster that has not started; its first CTA's x index names the tile
+                    mbar_arrive_expect_tx(clc_bar, 16);
+                    clc_try_cancel(clc_response, clc_bar);
+                    if (!mbar_wait(clc_bar, n & 1u, abort_flag)) {
+                        atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_PRODUCER); *abort_flag = 1; break;
+                    }
+                    const int x = clc_query(clc_response);
+                    tile = x < 0 ? -1 : x / Cfg::CLUSTER;
+                }
+            }
+            __syncwarp();
+        }
     } else if ((warp >= 4 && warp < 8) || (Cfg::EPI_SETS == 2 && warp >= 12)) {
         // ---------------------------------------------------------------- epilogue (every CTA)
         if constexpr (Cfg::REG_SPLIT) warpgroup_regs_inc<Cfg::REGS_EPI>();      // waits for what the other warpgroups hand back
@@ -457,7 +538,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         bool ok = true;
         BLZ_T_DECL(t_wait); BLZ_T_DECL(t_work);
         [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
-        for (int tile = group; tile < total_tiles; tile += num_groups, ++it) {
+        TileFeed feed = make_feed(true);
+        for (int tile = feed.take(); tile >= 0; tile = feed.take(), ++it) {
             int m_tile, n_tile;
             tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_tile, n_tile);
             const int buf = it % ACC_BUFS;
@@ -762,7 +844,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             int stage = 0; uint32_t phase = 0;
             [[maybe_unused]] uint32_t g = 0;       // stages handled so far
             bool ok = true;
-            for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
+            TileFeed feed = make_feed(true);
+            for (int tile = feed.take(); ok && tile >= 0; tile = feed.take()) {
                 int ks0, ks1;
                 if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
                 else { int m_e, n_e, m_r; tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_e, n_e); tile_k_range(p, m_e, m_r, ks0, ks1); }

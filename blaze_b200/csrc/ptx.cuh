@@ -251,6 +251,58 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
     return p;
 }
 
+// ------------------------------------------------------- cluster launch control
+// Work stealing from the grid's own launch queue: try_cancel asks the hardware to cancel a cluster of this
+// grid that has not started yet; the 16-byte answer lands in shared memory at `response` (16-byte aligned)
+// and completes 16 bytes on `bar`.  One thread per cluster issues it.  If a cluster was cancelled the caller
+// owns its work: clc_query returns the x index of that cluster's first CTA, otherwise -1 (nothing left to
+// take).  Blaze sketches the same helpers (include/gemm/tmem_utils.cuh:273-305) and never calls them.
+__device__ __forceinline__ void clc_try_cancel(uint32_t response, uint32_t bar) {
+    asm volatile("clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.b128 [%0], [%1];"
+                 ::"r"(response), "r"(bar) : "memory");
+}
+__device__ __forceinline__ int clc_query(uint32_t response) {
+    uint32_t ok, x;
+    asm volatile(
+        "{\n\t.reg .b128 rr;\n\t.reg .pred p;\n\t"
+        "ld.shared.b128 rr, [%2];\n\t"
+        "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 p, rr;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "mov.u32 %1, 0;\n\t"
+        "@p clusterlaunchcontrol.query_cancel.get_first_ctaid::x.b32.b128 %1, rr;\n\t}"
+        : "=r"(ok), "=r"(x) : "r"(response) : "memory");
+    return ok ? static_cast<int>(x) : -1;
+}
+// cluster-scope forms for data handed between the CTAs of a cluster through shared memory: the writer
+// stores with st.shared::cluster and arrives with release, the reader's wait acquires
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t addr_cluster, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr_cluster), "r"(v) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_release_cluster_addr(uint32_t bar_cluster) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_acquire_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded, like mbar_wait
+__device__ __forceinline__ bool mbar_wait_acquire_cluster(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+    for (int i = 0;; ++i) {
+        if (mbar_try_wait_acquire_cluster(bar, parity)) return true;
+        if ((i & 127) == 127) {
+            if (*abort_flag != 0) return false;
+            if (global_timer_ns() - t0 > BLZ_WAIT_LIMIT_NS) return false;
+        }
+    }
+}
+
 // ------------------------------------------------------------ tensor memory
 
 // Whole-warp calls.  The base address is written to shared memory at `dst`.

@@ -37,7 +37,7 @@ class GemmPlan:
     def __init__(self, kind: str, M: int, N: int, K: int, A, B, *, A_sf=None, B_sf=None, a_scale: float = 1.0,
                  b_scale: float = 1.0, out_dtype: str = "bf16", epilogue: str = "none", bias=None, residual=None,
                  b_layout: str = "kmajor", a_sf_layout: str = "rowmajor", b_sf_layout: str = "rowmajor",
-                 variant: str = "auto", ldc: int = 0, b_scale2: float = 0.0):
+                 variant: str = "auto", ldc: int = 0, b_scale2: float = 0.0, scheduler: str = "static"):
         L = nv.lib()
         d = nv.GemmDesc()
         d.kind = nv.KINDS[kind]
@@ -52,7 +52,8 @@ class GemmPlan:
         d.a_scale, d.b_scale = float(a_scale), float(b_scale)
         d.bias, d.residual = _ptr(bias), _ptr(residual)
         d.ldc = int(ldc)
-        d.b_scale2, d.reserved = float(b_scale2), 0
+        d.b_scale2 = float(b_scale2)
+        d.flags = nv.FLAG_CLC_SCHEDULER if scheduler == "clc" else 0
         self._keep = (A, B, A_sf, B_sf, bias, residual)   # operands must outlive the plan
         self._handle = ctypes.c_void_p()
         self.kind, self.M, self.N, self.K, self.out_dtype = kind, int(M), int(N), int(K), out_dtype

@@ -99,6 +99,16 @@ typedef enum blz_variant {
                                      instruction per K step), fewer L2 bytes per FLOP */
 } blz_variant;
 
+typedef enum blz_gemm_flags {
+    BLZ_FLAG_CLC_SCHEDULER = 1 /* tiled variants: dynamic tile scheduling through cluster launch control
+                                  (clusterlaunchcontrol.try_cancel) -- the grid holds one cluster per tile and
+                                  running clusters take over the tiles of clusters that have not started --
+                                  instead of the static persistent schedule.  What Blaze sketches in
+                                  include/gemm/tmem_utils.cuh:251-305 and never wires (its persistent kernel
+                                  claims tiles with atomicAdd, src/kernels/gemm_fp4_blkscaled_sm100.cu:555-563).
+                                  Ignored by the 512x256 variant and by in-kernel W4A16 expansion. */
+} blz_gemm_flags;
+
 typedef struct blz_gemm_desc {
     int32_t kind;         /* blz_gemm_kind */
     int32_t out_dtype;    /* blz_dtype of C, bias and residual (bias is fp32 when C is fp32) */
@@ -118,7 +128,7 @@ typedef struct blz_gemm_desc {
     const void* residual; /* [M, ldc] or null */
     int64_t ldc;          /* row pitch of C and residual in elements; 0 = N (N/2 for BLZ_EPI_SWIGLU) */
     float b_scale2;       /* BLZ_EPI_SWIGLU: dequantisation multiplier of the up rows; 0 = b_scale */
-    int32_t reserved;     /* set to 0 */
+    int32_t flags;        /* blz_gemm_flags, 0 = defaults */
 } blz_gemm_desc;
 
 typedef struct blz_plan_info {
@@ -130,6 +140,7 @@ typedef struct blz_plan_info {
     int32_t smem_bytes;       /* dynamic shared memory per CTA */
     int32_t tmem_cols;        /* tensor-memory columns per CTA */
     int32_t launches;         /* kernels one blz_gemm_execute launches */
+    int32_t scheduler;        /* 0 = static persistent schedule, 1 = cluster launch control */
     int64_t workspace_bytes;  /* device memory the plan owns */
 } blz_plan_info;
 

@@ -798,6 +798,59 @@ def test_set_a_other_kinds(oracle, cuda_device, kind, M):
     plan.destroy()
 
 
+# ------------------------------------------------------------ dynamic tile scheduler (cluster launch control)
+
+@pytest.mark.parametrize("kind,variant,shape", [
+    ("nvfp4", "256x256", (2048, 2304, 1024)),     # 72 tiles over the pairs that are resident
+    ("nvfp4", "256x256", (4096, 8192, 512)),      # 512 tiles of 256x256 on 74 pairs: most tiles are taken over by running clusters
+    ("nvfp4", "128x128", (1100, 4000, 416)),      # ragged M, N and K stage; 288 tiles of 128x128
+    ("nvfp4", "256x384", (1024, 1536, 512)),
+    ("fp8", "256x256", (4096, 4096, 256)),
+    ("fp8", "128x128", (300, 5000, 144)),
+    ("bf16", "256x256", (3000, 2304, 136)),
+    ("f16", "128x128", (2048, 2176, 64)),
+    ("fp8", "128x128", (128, 512, 8192)),         # with the tiled kernel's K split (tiles = splits x tiles)
+])
+def test_clc_scheduler(oracle, cuda_device, kind, variant, shape):
+    """Every tile the hardware hands out is computed exactly once: the result equals the oracle and, bit for bit,
+    what the static persistent schedule gives.  Counterpart of the scheduler Blaze sketches in
+    include/gemm/tmem_utils.cuh:251-305."""
+    from blaze_b200 import GemmPlan
+    torch = _torch()
+    M, N, K = shape
+    if kind == "nvfp4":
+        qa, qb = _nvfp4_inputs(oracle, M, N, K)
+        want = _nvfp4_ref(oracle, qa, qb)
+        (ad, asf, ga), (bd, bsf, gb) = qa, qb
+        args = (_u8(ad, cuda_device), _u8(bd, cuda_device))
+        kw = dict(A_sf=_u8(asf, cuda_device), B_sf=_u8(bsf, cuda_device), a_scale=ga, b_scale=gb)
+    elif kind == "fp8":
+        qa, da, qb, db = _fp8_inputs(oracle, M, N, K)
+        acc = oracle.gemm_f32(oracle.e4m3_to_f32(qa), oracle.e4m3_to_f32(qb))
+        want = oracle.widen(oracle.narrow(oracle.epilogue(acc, float(np.float32(da) * np.float32(db))), "bf16"), "bf16")
+        args = (_u8(qa, cuda_device), _u8(qb, cuda_device))
+        kw = dict(a_scale=da, b_scale=db)
+    else:
+        A, Bt = _dense_inputs(oracle, kind, M, N, K)
+        want = oracle.widen(oracle.narrow(oracle.gemm_dense16(A, Bt, kind), "bf16"), "bf16")
+        args = (bits16_to_torch(A, kind, cuda_device), bits16_to_torch(Bt, kind, cuda_device))
+        kw = {}
+    outs = {}
+    for sched in ("clc", "static"):
+        C = _out_tensor(M, N, "bf16", cuda_device)
+        plan = GemmPlan(kind, M, N, K, *args, out_dtype="bf16", variant=variant, scheduler=sched, **kw)
+        info = plan.info()
+        assert info["scheduler"] == (1 if sched == "clc" else 0), info
+        for _ in range(2):                                     # twice: the launch queue is consumed anew by every launch
+            C.fill_(-7.0)
+            _run(plan, C)
+        outs[sched] = C
+        if sched == "clc":
+            assert_close(torch_to_f32(C, oracle, "bf16"), want, "clc %s %s %s %s" % (kind, variant, shape, info))
+        plan.destroy()
+    assert torch.equal(outs["clc"], outs["static"])
+
+
 @pytest.mark.parametrize("kind,shape,mode", [
     ("bf16", (128, 512, 8192), "none"), ("bf16", (200, 300, 4104), "bias_silu"), ("fp8", (100, 384, 8192), "residual"),
     ("nvfp4", (128, 512, 16384), "none"), ("nvfp4", (300, 264, 8224), "bias"), ("w4a16_f16", (200, 384, 4096), "none"),
