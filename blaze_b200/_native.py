@@ -19,7 +19,7 @@ F16, BF16, F32 = range(3)
 EPI_NONE, EPI_BIAS, EPI_SILU, EPI_BIAS_SILU, EPI_RESIDUAL_ADD, EPI_SWIGLU = range(6)
 B_KMAJOR, B_NMAJOR = range(2)
 SF_ROWMAJOR, SF_TILED = range(2)
-FLAG_CLC_SCHEDULER = 1
+FLAG_CLC_SCHEDULER, FLAG_STATIC_WEIGHTS = 1, 2
 VARIANT_AUTO, VARIANT_TILE_128x128, VARIANT_PAIR_256x256, VARIANT_DECODE, VARIANT_QUAD_512x256, VARIANT_PAIR_256x384 = range(6)
 
 KINDS = {"f16": GEMM_F16, "bf16": GEMM_BF16, "fp8": GEMM_FP8, "nvfp4": GEMM_NVFP4,
@@ -32,12 +32,16 @@ VARIANTS = {"auto": VARIANT_AUTO, "128x128": VARIANT_TILE_128x128, "256x256": VA
 EXPORTS = (
     "blz_version", "blz_status_string", "blz_last_cuda_error", "blz_last_cuda_error_string",
     "blz_gemm_plan_create", "blz_gemm_execute", "blz_gemm_plan_set_a", "blz_gemm_plan_check",
-    "blz_gemm_plan_info", "blz_gemm_plan_destroy", "blz_gemm_launch",
+    "blz_gemm_plan_info", "blz_gemm_plan_refresh_weights", "blz_gemm_plan_destroy", "blz_gemm_launch",
     "blz_amax", "blz_quantize_fp8", "blz_quantize_nvfp4", "blz_tiled_scales_bytes", "blz_tile_scales", "blz_interleave_gate_up",
     "blz_gemm_nvfp4_decode_static",
     "blz_peer_buffer_create", "blz_peer_buffer_open", "blz_peer_buffer_close", "blz_peer_buffer_destroy", "blz_gemm_execute_gather",
     "blz_wait_probe",
+    "blz_shard_bounds", "blz_nccl_unique_id", "blz_sharded_plan_create", "blz_sharded_plan_info", "blz_sharded_plan_output_handle",
+    "blz_sharded_plan_connect", "blz_sharded_plan_execute", "blz_sharded_plan_check", "blz_sharded_plan_destroy", "blz_sharded_last_error",
 )
+EXCHANGE_NONE, EXCHANGE_NCCL, EXCHANGE_PEER_STORES = range(3)
+EXCHANGES = {"none": EXCHANGE_NONE, "nccl": EXCHANGE_NCCL, "peer_stores": EXCHANGE_PEER_STORES}
 
 
 class GemmDesc(ctypes.Structure):
@@ -58,6 +62,16 @@ class PlanInfo(ctypes.Structure):
         ("split_k", ctypes.c_int32), ("grid", ctypes.c_int32), ("smem_bytes", ctypes.c_int32), ("tmem_cols", ctypes.c_int32),
         ("launches", ctypes.c_int32), ("scheduler", ctypes.c_int32), ("workspace_bytes", ctypes.c_int64),
     ]
+
+
+class ShardedDesc(ctypes.Structure):
+    _fields_ = [("gemm", GemmDesc), ("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("exchange", ctypes.c_int32),
+                ("reserved", ctypes.c_int32), ("nccl_id", ctypes.c_char_p)]
+
+
+class ShardedInfo(ctypes.Structure):
+    _fields_ = [("col_lo", ctypes.c_int64), ("col_hi", ctypes.c_int64), ("exchange", ctypes.c_int32), ("world", ctypes.c_int32),
+                ("rank", ctypes.c_int32), ("reserved", ctypes.c_int32), ("own_output", ctypes.c_void_p), ("gemm", PlanInfo)]
 
 
 class BlazeError(RuntimeError):
@@ -92,6 +106,8 @@ def lib() -> ctypes.CDLL:
     L.blz_gemm_plan_set_a.argtypes = [vp, vp, vp, ctypes.c_float]
     L.blz_gemm_plan_check.argtypes = [vp, vp]
     L.blz_gemm_plan_info.argtypes = [vp, ctypes.POINTER(PlanInfo)]
+    L.blz_gemm_plan_refresh_weights.argtypes = [vp, vp]
+    L.blz_gemm_plan_refresh_weights.restype = ctypes.c_int
     L.blz_gemm_plan_destroy.argtypes = [vp]
     L.blz_gemm_launch.argtypes = [ctypes.POINTER(GemmDesc), vp, vp]
     L.blz_amax.argtypes = [vp, i32, i64, vp, vp]
@@ -115,6 +131,19 @@ def lib() -> ctypes.CDLL:
         getattr(L, name).restype = ctypes.c_int
     for name in ("blz_gemm_plan_create", "blz_gemm_execute", "blz_gemm_plan_set_a", "blz_gemm_plan_check", "blz_gemm_plan_info",
                  "blz_gemm_plan_destroy", "blz_gemm_launch", "blz_amax", "blz_quantize_fp8", "blz_quantize_nvfp4", "blz_tile_scales"):
+        getattr(L, name).restype = ctypes.c_int
+    L.blz_shard_bounds.argtypes = [i64, i32, i32, i32, ctypes.POINTER(i64), ctypes.POINTER(i64)]
+    L.blz_nccl_unique_id.argtypes = [ctypes.c_char_p]
+    L.blz_sharded_plan_create.argtypes = [ctypes.POINTER(ShardedDesc), ctypes.POINTER(vp)]
+    L.blz_sharded_plan_info.argtypes = [vp, ctypes.POINTER(ShardedInfo)]
+    L.blz_sharded_plan_output_handle.argtypes = [vp, ctypes.c_char_p]
+    L.blz_sharded_plan_connect.argtypes = [vp, ctypes.c_char_p]
+    L.blz_sharded_plan_execute.argtypes = [vp, vp, vp]
+    L.blz_sharded_plan_check.argtypes = [vp, vp]
+    L.blz_sharded_plan_destroy.argtypes = [vp]
+    L.blz_sharded_last_error.restype = ctypes.c_char_p
+    for name in ("blz_shard_bounds", "blz_nccl_unique_id", "blz_sharded_plan_create", "blz_sharded_plan_info", "blz_sharded_plan_output_handle",
+                 "blz_sharded_plan_connect", "blz_sharded_plan_execute", "blz_sharded_plan_check", "blz_sharded_plan_destroy"):
         getattr(L, name).restype = ctypes.c_int
     _ = f32p
     _LIB = L

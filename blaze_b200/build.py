@@ -15,7 +15,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libblaze_b200.so")
 NVCC = os.environ.get("NVCC", shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc")
 
-SOURCES = ["capi.cu", "blaze_compat.cu", "decode_static.cu"]
+SOURCES = ["capi.cu", "blaze_compat.cu", "decode_static.cu", "sharded.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 
@@ -47,7 +47,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if r.returncode != 0:
             raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, r.stdout, r.stderr))
         objs.append(obj)
-    r = subprocess.run([NVCC, "-shared", "-o", OUT, *objs], capture_output=True, text=True)
+    r = subprocess.run([NVCC, "-shared", "-o", OUT, *objs, "-ldl"], capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
     return OUT

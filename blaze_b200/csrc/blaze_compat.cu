@@ -119,7 +119,11 @@ void launch_gemm_mixed(const half* A, const Fp4WeightTensor& B, half* C, int M, 
     run_once(mixed_desc(A, B, M, N, K, static_cast<int>(epilogue), bias, residual), C, stream, "launch_gemm_mixed");
 }
 MixedGemmPlan* create_mixed_gemm_plan(const half* A, const Fp4WeightTensor& B, int M, int N, int K, const half* bias, const half* residual, MixedEpilogue epilogue) {
-    return make_plan<MixedGemmPlan>(mixed_desc(A, B, M, N, K, static_cast<int>(epilogue), bias, residual), "create_mixed_gemm_plan");
+    // Blaze's plan converts its operands once, at creation (src/kernels/gemm_mixed_sm100.cu:412-470): the weights handed
+    // to a plan are static for the plan's life, so the 16-bit copy of larger problems is made here and not per execute
+    blz_gemm_desc d = mixed_desc(A, B, M, N, K, static_cast<int>(epilogue), bias, residual);
+    d.flags |= BLZ_FLAG_STATIC_WEIGHTS;
+    return make_plan<MixedGemmPlan>(d, "create_mixed_gemm_plan");
 }
 void execute_mixed_gemm(MixedGemmPlan* plan, half* C, cudaStream_t stream) { run_plan(plan, C, stream, "execute_mixed_gemm"); }
 void destroy_mixed_gemm_plan(MixedGemmPlan* plan) { blz_gemm_plan_destroy(reinterpret_cast<blz_gemm_plan*>(plan)); }

@@ -150,7 +150,8 @@ struct blz_gemm_plan {
     void* own_b = nullptr;
     void* own_sfa = nullptr;
     void* own_sfb = nullptr;
-    void* own_w16 = nullptr;      // W4A16: weights expanded to 16 bit, refreshed by every execute
+    void* own_w16 = nullptr;      // W4A16: weights expanded to 16 bit, refreshed by every execute -- or only at creation
+    bool w16_static = false;      //   (BLZ_FLAG_STATIC_WEIGHTS)
     float* own_partial = nullptr; // split-K of the tiled kernel: [splits][m_tiles*128][partial_pitch] fp32
     int split_k = 1;
     int64_t partial_pitch = 0, partial_rows = 0;
@@ -537,17 +538,25 @@ blz_status decode_launch(blz_gemm_plan* p, void* C, cudaStream_t stream) {
     return BLZ_OK;
 }
 
+// W4A16 with a 16-bit copy of the weights: packed E2M1 x block scale -> fp16 / bf16 (exact), the tensor scale stays in alpha.
+blz_status expand_weights(blz_gemm_plan* p, cudaStream_t stream) {
+    const blz_gemm_desc& d = p->desc;
+    const int64_t blocks16 = static_cast<int64_t>(d.N) * (d.K / 8);     // one thread per 8 values
+    if (d.kind == BLZ_GEMM_W4A16_F16)
+        dequant_nvfp4_kernel<false><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<uint16_t*>(p->own_w16));
+    else
+        dequant_nvfp4_kernel<true><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<uint16_t*>(p->own_w16));
+    BLZ_CUDA(cudaGetLastError());
+    return BLZ_OK;
+}
+
 // Launches the cluster kernel.  `dst` are the bases of n_dst output matrices with row pitch `ld`
 // (elements); the tile block goes to columns [col_offset, col_offset + N) of each.
 blz_status launch_cluster(blz_gemm_plan* p, int n_dst, void* const* dst, int64_t ld, int64_t col_offset, cudaStream_t stream) {
     const blz_gemm_desc& d = p->desc;
-    if (p->own_w16) {
-        const int64_t blocks16 = static_cast<int64_t>(d.N) * (d.K / 8);     // one thread per 8 values
-        if (d.kind == BLZ_GEMM_W4A16_F16)
-            dequant_nvfp4_kernel<false><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<uint16_t*>(p->own_w16));
-        else
-            dequant_nvfp4_kernel<true><<<grid_for(blocks16, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(p->b_used), p->sfb_used, sf_katoms(d.K), d.N, d.K, static_cast<uint16_t*>(p->own_w16));
-        BLZ_CUDA(cudaGetLastError());
+    if (p->own_w16 && !p->w16_static) {
+        blz_status s = expand_weights(p, stream);
+        if (s) return s;
     }
     const int eb = elem_bytes_out(d.out_dtype);
     ClusterGemmParams cp = p->cp;
@@ -690,17 +699,20 @@ blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_p
     const bool w4_tiled_split = w4a16 && desc->M > 64 && ceil_div(desc->N, 128) * 4 <= p->num_sms && desc->K >= 8192 && desc->epilogue != BLZ_EPI_SWIGLU;
     const int decode_auto_m = (w4a16 && !w4_tiled_split) ? 128 : 64;
     const bool want_decode = desc->variant == BLZ_VARIANT_DECODE || (desc->variant == BLZ_VARIANT_AUTO && desc->M <= decode_auto_m);
-    // M > 128: up to 2048 rows the tiled kernel expands the packed weights stage by stage in shared
-    // memory (no 16-bit copy; every CTA re-expands the tiles it uses).  Beyond that, expanding all
-    // weights once per call into a plan-owned 16-bit copy costs less than the slower main loop
-    // (measured: 4096 x 22016 x 4096 bf16 1556 against 1427 TFLOP/s).  BLZ_W4A16_PREPASS=0 / 1 forces one.
-    const int prepass_knob = env_int("BLZ_W4A16_PREPASS", -1);
-    const bool prepass = prepass_knob >= 0 ? prepass_knob != 0 : desc->M > 2048;
-    if (w4a16 && !want_decode && (prepass || desc->variant == BLZ_VARIANT_QUAD_512x256)) {
-        // The tiled kernels consume 16-bit weights: every execute expands the packed weights into
-        // this buffer (q * block scale, exact in 16 bits); the fp32 tensor scale goes into alpha.
+    // M > 128: the tiled kernel expands the packed weights stage by stage in shared memory (no 16-bit copy, one
+    // launch; every CTA re-expands the tiles it uses, which costs 8 % at 4096 x 22016 x 4096: 1427 against 1556
+    // TFLOP/s).  Callers whose weights are static ask for a plan-owned 16-bit copy made once
+    // (BLZ_FLAG_STATIC_WEIGHTS).  BLZ_W4A16_PREPASS=1 forces the copy to be re-made by every execute (tuning).
+    const bool prepass = env_int("BLZ_W4A16_PREPASS", 0) != 0;
+    const bool static_w = w4a16 && !want_decode && (desc->flags & BLZ_FLAG_STATIC_WEIGHTS) != 0;
+    if (w4a16 && !want_decode && (prepass || static_w || desc->variant == BLZ_VARIANT_QUAD_512x256)) {
+        // The tiled kernels consume 16-bit weights: the packed weights are expanded into this buffer
+        // (q * block scale, exact in 16 bits; the fp32 tensor scale goes into alpha) -- by every execute,
+        // or once, here, when the caller declared them static.
         if ((s = dev_alloc(p, &p->own_w16, static_cast<int64_t>(desc->N) * desc->K * 2, false))) return fail(s);
-        p->launches = 2;
+        p->w16_static = static_w;
+        p->launches = static_w ? 1 : 2;
+        if (static_w && (s = expand_weights(p, nullptr))) return fail(s);
     }
 
     if (want_decode) {
@@ -799,6 +811,12 @@ blz_status blz_gemm_plan_info(const blz_gemm_plan* p, blz_plan_info* info) {
     info->scheduler = p->clc ? 1 : 0;
     info->workspace_bytes = p->owned_bytes;
     return BLZ_OK;
+}
+
+blz_status blz_gemm_plan_refresh_weights(blz_gemm_plan* p, void* stream_v) {
+    if (!p) return BLZ_ERR_INVALID_ARGUMENT;
+    if (!p->own_w16 || !p->w16_static) return BLZ_OK;
+    return expand_weights(p, static_cast<cudaStream_t>(stream_v));
 }
 
 blz_status blz_gemm_plan_destroy(blz_gemm_plan* p) {

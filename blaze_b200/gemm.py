@@ -31,29 +31,41 @@ def _stream(stream=None):
     return torch.cuda.current_stream().cuda_stream
 
 
+def make_desc(kind: str, M: int, N: int, K: int, A, B, *, A_sf=None, B_sf=None, a_scale: float = 1.0, b_scale: float = 1.0,
+              out_dtype: str = "bf16", epilogue: str = "none", bias=None, residual=None, b_layout: str = "kmajor",
+              a_sf_layout: str = "rowmajor", b_sf_layout: str = "rowmajor", variant: str = "auto", ldc: int = 0, b_scale2: float = 0.0,
+              scheduler: str = "static", static_weights: bool = False):
+    """blz_gemm_desc from keyword arguments (field meanings: include/blaze_b200.h)."""
+    d = nv.GemmDesc()
+    d.kind = nv.KINDS[kind]
+    d.out_dtype = nv.DTYPES[out_dtype]
+    d.epilogue = nv.EPILOGUES[epilogue]
+    d.variant = nv.VARIANTS[variant]
+    d.M, d.N, d.K = int(M), int(N), int(K)
+    d.b_layout = nv.B_NMAJOR if b_layout == "nmajor" else nv.B_KMAJOR
+    d.a_sf_layout = nv.SF_TILED if a_sf_layout == "tiled" else nv.SF_ROWMAJOR
+    d.b_sf_layout = nv.SF_TILED if b_sf_layout == "tiled" else nv.SF_ROWMAJOR
+    d.A, d.A_sf, d.B, d.B_sf = _ptr(A), _ptr(A_sf), _ptr(B), _ptr(B_sf)
+    d.a_scale, d.b_scale = float(a_scale), float(b_scale)
+    d.bias, d.residual = _ptr(bias), _ptr(residual)
+    d.ldc = int(ldc)
+    d.b_scale2 = float(b_scale2)
+    d.flags = (nv.FLAG_CLC_SCHEDULER if scheduler == "clc" else 0) | (nv.FLAG_STATIC_WEIGHTS if static_weights else 0)
+    return d
+
+
 class GemmPlan:
     """One planned GEMM: C[M,N] = epilogue(a_scale*b_scale * A[M,K] x B^T) -- see blz_gemm_desc."""
 
     def __init__(self, kind: str, M: int, N: int, K: int, A, B, *, A_sf=None, B_sf=None, a_scale: float = 1.0,
                  b_scale: float = 1.0, out_dtype: str = "bf16", epilogue: str = "none", bias=None, residual=None,
                  b_layout: str = "kmajor", a_sf_layout: str = "rowmajor", b_sf_layout: str = "rowmajor",
-                 variant: str = "auto", ldc: int = 0, b_scale2: float = 0.0, scheduler: str = "static"):
+                 variant: str = "auto", ldc: int = 0, b_scale2: float = 0.0, scheduler: str = "static",
+                 static_weights: bool = False):
         L = nv.lib()
-        d = nv.GemmDesc()
-        d.kind = nv.KINDS[kind]
-        d.out_dtype = nv.DTYPES[out_dtype]
-        d.epilogue = nv.EPILOGUES[epilogue]
-        d.variant = nv.VARIANTS[variant]
-        d.M, d.N, d.K = int(M), int(N), int(K)
-        d.b_layout = nv.B_NMAJOR if b_layout == "nmajor" else nv.B_KMAJOR
-        d.a_sf_layout = nv.SF_TILED if a_sf_layout == "tiled" else nv.SF_ROWMAJOR
-        d.b_sf_layout = nv.SF_TILED if b_sf_layout == "tiled" else nv.SF_ROWMAJOR
-        d.A, d.A_sf, d.B, d.B_sf = _ptr(A), _ptr(A_sf), _ptr(B), _ptr(B_sf)
-        d.a_scale, d.b_scale = float(a_scale), float(b_scale)
-        d.bias, d.residual = _ptr(bias), _ptr(residual)
-        d.ldc = int(ldc)
-        d.b_scale2 = float(b_scale2)
-        d.flags = nv.FLAG_CLC_SCHEDULER if scheduler == "clc" else 0
+        d = make_desc(kind, M, N, K, A, B, A_sf=A_sf, B_sf=B_sf, a_scale=a_scale, b_scale=b_scale, out_dtype=out_dtype, epilogue=epilogue,
+                      bias=bias, residual=residual, b_layout=b_layout, a_sf_layout=a_sf_layout, b_sf_layout=b_sf_layout, variant=variant,
+                      ldc=ldc, b_scale2=b_scale2, scheduler=scheduler, static_weights=static_weights)
         self._keep = (A, B, A_sf, B_sf, bias, residual)   # operands must outlive the plan
         self._handle = ctypes.c_void_p()
         self.kind, self.M, self.N, self.K, self.out_dtype = kind, int(M), int(N), int(K), out_dtype
@@ -72,6 +84,10 @@ class GemmPlan:
     def set_a(self, A, A_sf=None, a_scale: float = 0.0) -> None:
         nv.check("blz_gemm_plan_set_a", nv.lib().blz_gemm_plan_set_a(self._handle, _ptr(A), _ptr(A_sf), float(a_scale)))
         self._keep = (A, A_sf) + self._keep[1:]
+
+    def refresh_weights(self, stream=None) -> None:
+        """static_weights plans: expand the packed weights again after they changed in place."""
+        nv.check("blz_gemm_plan_refresh_weights", nv.lib().blz_gemm_plan_refresh_weights(self._handle, _stream(stream)))
 
     def check(self, stream=None) -> None:
         """Synchronises the stream and raises if a kernel of this plan gave up on a device-side wait."""
@@ -116,7 +132,7 @@ create_fp4_blkscaled_persistent_gemm_plan = create_fp4_blkscaled_gemm_plan
 def create_mixed_gemm_plan(A, B: dict, M, N, K, bias=None, residual=None, epilogue: str = "none") -> GemmPlan:
     """fp16 activations A [M,K] x NVFP4 weights B (Fp4WeightTensor fields, [K,N] convention)."""
     return GemmPlan("w4a16_f16", M, N, K, A, B["data"], B_sf=B["block_scales"], b_scale=B["tensor_scale"], out_dtype="f16",
-                    epilogue=epilogue, bias=bias, residual=residual, b_layout="nmajor")
+                    epilogue=epilogue, bias=bias, residual=residual, b_layout="nmajor", static_weights=True)
 
 
 def interleave_gate_up(gate, up, group_bytes: int, stream=None):

@@ -100,13 +100,21 @@ typedef enum blz_variant {
 } blz_variant;
 
 typedef enum blz_gemm_flags {
-    BLZ_FLAG_CLC_SCHEDULER = 1 /* tiled variants: dynamic tile scheduling through cluster launch control
+    BLZ_FLAG_CLC_SCHEDULER = 1, /* tiled variants: dynamic tile scheduling through cluster launch control
                                   (clusterlaunchcontrol.try_cancel) -- the grid holds one cluster per tile and
                                   running clusters take over the tiles of clusters that have not started --
                                   instead of the static persistent schedule.  What Blaze sketches in
                                   include/gemm/tmem_utils.cuh:251-305 and never wires (its persistent kernel
                                   claims tiles with atomicAdd, src/kernels/gemm_fp4_blkscaled_sm100.cu:555-563).
                                   Ignored by the 512x256 variant and by in-kernel W4A16 expansion. */
+    BLZ_FLAG_STATIC_WEIGHTS = 2 /* W4A16, M > 128: the caller promises that the packed weights and their scales
+                                  do not change while the plan lives (or calls blz_gemm_plan_refresh_weights
+                                  after changing them).  The plan then expands them ONCE, at creation, into a
+                                  plan-owned 16-bit copy (N*K*2 bytes) and every execute is one launch of the
+                                  dense 16-bit kernel -- instead of expanding inside the kernel (M <= 2048) or
+                                  re-expanding all weights on every execute (M > 2048).  Blaze's own mixed plan
+                                  has the same contract: its create call converts operands once
+                                  (src/kernels/gemm_mixed_sm100.cu:412-470). */
 } blz_gemm_flags;
 
 typedef struct blz_gemm_desc {
@@ -171,6 +179,11 @@ blz_status blz_gemm_plan_set_a(blz_gemm_plan* plan, const void* A, const void* A
 blz_status blz_gemm_plan_check(blz_gemm_plan* plan, void* stream);
 
 blz_status blz_gemm_plan_info(const blz_gemm_plan* plan, blz_plan_info* info);
+
+/* BLZ_FLAG_STATIC_WEIGHTS plans: expands the packed weights into the plan's 16-bit copy again (asynchronous
+ * on `stream`); call it after the weights or their scales changed in place.  BLZ_OK and nothing to do for
+ * every other plan. */
+blz_status blz_gemm_plan_refresh_weights(blz_gemm_plan* plan, void* stream);
 
 /* Frees the plan and what it owns.  Null is accepted. */
 blz_status blz_gemm_plan_destroy(blz_gemm_plan* plan);
@@ -247,6 +260,62 @@ blz_status blz_peer_buffer_close(void* ptr);
 blz_status blz_peer_buffer_destroy(void* ptr);
 blz_status blz_gemm_execute_gather(blz_gemm_plan* plan, int32_t n_dst, void* const* dst, int64_t ld_total,
                                    int64_t col_offset, void* stream);
+
+/* ---- column-sharded GEMM across the GPUs of one box (no counterpart in the reference, which has no multi-GPU
+ *      code; the plan triple follows its create / execute / destroy plans,
+ *      include/gemm/fp4_blkscaled_gemm_sm100.cuh:198-208) ----
+ *
+ * Output columns are independent: rank r of `world` owns columns [lo, hi) = blz_shard_bounds(N, world, r, 128)
+ * -- rows [lo, hi) of the K-major weights and of their scales -- activations are replicated, and every rank
+ * runs the ordinary single-GPU plan on (M, hi - lo, K).  One process per GPU; each process creates its own
+ * sharded plan with the device it computes on current.  What follows the GEMM is chosen by `exchange`:
+ *
+ *   BLZ_EXCHANGE_NONE         nothing: execute writes this rank's [M, hi - lo] block to C
+ *   BLZ_EXCHANGE_NCCL         ncclAllGather of the blocks: execute writes [world][M][hi - lo] to C.  NCCL is
+ *                             loaded at run time (libnccl.so.2, or BLZ_NCCL_LIBRARY); rank 0 makes an id with
+ *                             blz_nccl_unique_id, every rank passes the same 128 bytes in desc.nccl_id, and
+ *                             plan creation is collective (ncclCommInitRank)
+ *   BLZ_EXCHANGE_PEER_STORES  fused into the GEMM: the plan owns a peer-visible row-major [M, N] output; after
+ *                             creation every rank publishes blz_sharded_plan_output_handle (64 bytes), collects
+ *                             all ranks' handles in rank order and calls blz_sharded_plan_connect; execute then
+ *                             stores every tile into every rank's output (C is ignored).  The ranks must meet at
+ *                             a barrier of their own before reading the output or reusing it.
+ *
+ * desc.gemm describes the FULL problem (N = all columns) with B / B_sf pointing at THIS RANK's rows of the
+ * K-major weights (row-major scales: its rows; tiled scales: tiled for the shard); residual-add and the fused
+ * gate / up epilogue are not supported here. */
+typedef enum blz_exchange { BLZ_EXCHANGE_NONE = 0, BLZ_EXCHANGE_NCCL = 1, BLZ_EXCHANGE_PEER_STORES = 2 } blz_exchange;
+
+typedef struct blz_sharded_desc {
+    blz_gemm_desc gemm;      /* see above */
+    int32_t world, rank;     /* 1 <= world <= 8 */
+    int32_t exchange;        /* blz_exchange */
+    int32_t reserved;        /* set to 0 */
+    const uint8_t* nccl_id;  /* BLZ_EXCHANGE_NCCL with world > 1: 128 bytes from blz_nccl_unique_id */
+} blz_sharded_desc;
+
+typedef struct blz_sharded_info {
+    int64_t col_lo, col_hi;  /* output columns of this rank */
+    int32_t exchange, world, rank, reserved;
+    void* own_output;        /* BLZ_EXCHANGE_PEER_STORES: this rank's [M, N] output (device pointer), else null */
+    blz_plan_info gemm;      /* the local plan */
+} blz_sharded_info;
+
+typedef struct blz_sharded_plan blz_sharded_plan;
+
+/* Host arithmetic only (no device needed): equal shards of whole `multiple`-column tiles, or
+ * BLZ_ERR_INVALID_ARGUMENT when N does not split that way. */
+blz_status blz_shard_bounds(int64_t n_total, int32_t world, int32_t rank, int32_t multiple, int64_t* lo, int64_t* hi);
+blz_status blz_nccl_unique_id(uint8_t* id128);
+blz_status blz_sharded_plan_create(const blz_sharded_desc* desc, blz_sharded_plan** out_plan);
+blz_status blz_sharded_plan_info(const blz_sharded_plan* plan, blz_sharded_info* info);
+blz_status blz_sharded_plan_output_handle(blz_sharded_plan* plan, uint8_t* handle64);
+blz_status blz_sharded_plan_connect(blz_sharded_plan* plan, const uint8_t* handles /* world x 64 bytes, rank order */);
+blz_status blz_sharded_plan_execute(blz_sharded_plan* plan, void* C, void* stream);
+blz_status blz_sharded_plan_check(blz_sharded_plan* plan, void* stream);
+blz_status blz_sharded_plan_destroy(blz_sharded_plan* plan);
+/* text of the last NCCL-side failure on this thread */
+const char* blz_sharded_last_error(void);
 
 /* ---- allocation-free entry point (no counterpart in the reference: Blaze's launchers and plans
  *      all call cudaMalloc, e.g. src/kernels/gemm_fp4_blkscaled_sm100.cu:840-920) ----

@@ -61,3 +61,38 @@ def test_tiled_scale_size(native_lib):
     assert native_lib.blz_tiled_scales_bytes(16, 4096) == 2 * 64 * 512
     assert native_lib.blz_tiled_scales_bytes(300, 64) == 4 * 4 * 512
     assert native_lib.blz_tiled_scales_bytes(0, 64) == 0
+
+
+def test_shard_arithmetic_and_sharded_plan_argument_errors_without_device(native_lib):
+    """The sharded wrapper's host logic through the C ABI: equal shards of whole 128-column tiles, refusals
+    for everything else, and descriptor errors caught before any device call."""
+    from blaze_b200 import _native as nv
+    L = native_lib
+    lo, hi = ctypes.c_int64(), ctypes.c_int64()
+    for world, per in ((1, 28672), (2, 14336), (4, 7168), (8, 3584)):
+        for rank in range(world):
+            assert L.blz_shard_bounds(28672, world, rank, 128, ctypes.byref(lo), ctypes.byref(hi)) == nv.OK
+            assert (lo.value, hi.value) == (rank * per, (rank + 1) * per)
+    assert L.blz_shard_bounds(28672, 3, 0, 128, ctypes.byref(lo), ctypes.byref(hi)) == nv.ERR_INVALID_ARGUMENT     # not divisible
+    assert L.blz_shard_bounds(1024, 16, 0, 128, ctypes.byref(lo), ctypes.byref(hi)) == nv.ERR_INVALID_ARGUMENT     # shards of 64 columns
+    assert L.blz_shard_bounds(1024, 2, 2, 128, ctypes.byref(lo), ctypes.byref(hi)) == nv.ERR_INVALID_ARGUMENT      # rank outside the world
+    assert L.blz_shard_bounds(1024, 2, 0, 128, None, ctypes.byref(hi)) == nv.ERR_INVALID_ARGUMENT
+    plan = ctypes.c_void_p()
+    assert L.blz_sharded_plan_create(None, ctypes.byref(plan)) == nv.ERR_INVALID_ARGUMENT
+    sd = nv.ShardedDesc()
+    sd.gemm.kind = nv.GEMM_FP8; sd.gemm.M, sd.gemm.N, sd.gemm.K = 256, 1024, 512
+    sd.gemm.A = 4096; sd.gemm.B = 4096
+    sd.world, sd.rank, sd.exchange = 2, 2, nv.EXCHANGE_NONE
+    assert L.blz_sharded_plan_create(ctypes.byref(sd), ctypes.byref(plan)) == nv.ERR_INVALID_ARGUMENT              # rank >= world
+    sd.rank, sd.exchange = 0, 7
+    assert L.blz_sharded_plan_create(ctypes.byref(sd), ctypes.byref(plan)) == nv.ERR_INVALID_ARGUMENT              # no such exchange
+    sd.exchange = nv.EXCHANGE_NCCL
+    assert L.blz_sharded_plan_create(ctypes.byref(sd), ctypes.byref(plan)) == nv.ERR_INVALID_ARGUMENT              # NCCL without an id
+    sd.exchange, sd.world = nv.EXCHANGE_NONE, 3
+    assert L.blz_sharded_plan_create(ctypes.byref(sd), ctypes.byref(plan)) == nv.ERR_INVALID_ARGUMENT              # 1024 columns over 3 ranks
+    sd.world = 2; sd.gemm.b_layout = nv.B_NMAJOR
+    assert L.blz_sharded_plan_create(ctypes.byref(sd), ctypes.byref(plan)) == nv.ERR_UNSUPPORTED                   # shards are rows of K-major weights
+    sd.gemm.b_layout = nv.B_KMAJOR; sd.gemm.epilogue = nv.EPI_RESIDUAL_ADD
+    assert L.blz_sharded_plan_create(ctypes.byref(sd), ctypes.byref(plan)) == nv.ERR_UNSUPPORTED
+    assert L.blz_sharded_plan_execute(None, None, None) == nv.ERR_INVALID_ARGUMENT
+    assert L.blz_sharded_plan_destroy(None) == nv.OK

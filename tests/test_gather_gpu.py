@@ -49,9 +49,33 @@ def _worker(rank, world, port, ret):
         plan.check()
         torch.cuda.synchronize(); dist.barrier()
         ok = bool(torch.equal(out.local, want))
-        ret[rank] = ok
         out.close()
         plan.destroy()
+        dist.barrier()
+        # the same three results through the C-level sharded plan (blz_sharded_plan_*): none / NCCL / peer stores
+        kw = dict(A_sf=asf, B_sf=bsf_r.contiguous(), a_scale=float(gA.item()), b_scale=float(gB.item()), a_sf_layout="tiled",
+                  out_dtype="bf16", variant="256x256")
+        sp = sharded.ShardedPlan("nvfp4", M, N, K, ad, bd_r.contiguous(), exchange="none", **kw)
+        assert (sp.col_lo, sp.col_hi) == (lo, hi)
+        c2 = torch.empty((M, n_local), dtype=torch.bfloat16, device=dev)
+        sp.execute(c2); sp.check()
+        ok = ok and bool(torch.equal(c2, c_local))
+        sp.destroy()
+        sp = sharded.ShardedPlan("nvfp4", M, N, K, ad, bd_r.contiguous(), exchange="nccl", **kw)
+        g2 = torch.full((world, M, n_local), -3.0, dtype=torch.bfloat16, device=dev)
+        sp.execute(g2); sp.check()
+        ok = ok and bool(torch.equal(sharded.gathered_to_full(g2), want))
+        sp.destroy()
+        dist.barrier()
+        sp = sharded.ShardedPlan("nvfp4", M, N, K, ad, bd_r.contiguous(), exchange="peer_stores", **kw)
+        sp.output.fill_(-3.0)
+        torch.cuda.synchronize(); dist.barrier()
+        sp.execute(); sp.check()
+        torch.cuda.synchronize(); dist.barrier()
+        ok = ok and bool(torch.equal(sp.output, want))
+        dist.barrier()
+        sp.destroy()
+        ret[rank] = ok
         dist.barrier()
     finally:
         dist.destroy_process_group()
