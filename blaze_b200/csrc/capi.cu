@@ -209,46 +209,56 @@ blz_status validate(const blz_gemm_desc* d) {
     return BLZ_OK;
 }
 
-// B in Blaze's [K, N] convention -> plan-owned K-major copy (and tiled scales).
+// Fills the plan-owned copies of B: K-major data from Blaze's [K, N] convention, tiled scales from row-major ones.
+blz_status convert_b(blz_gemm_plan* p, cudaStream_t stream) {
+    const blz_gemm_desc& d = p->desc;
+    const bool fp4_b = d.kind == BLZ_GEMM_NVFP4 || d.kind == BLZ_GEMM_W4A16_F16 || d.kind == BLZ_GEMM_W4A16_BF16;
+    const int64_t N = d.N, K = d.K;
+    if (p->own_b) {
+        if (fp4_b) {
+            repack_fp4_kn_to_nk_kernel<<<grid_for((N / 2) * (K / 2), 256), 256, 0, stream>>>(static_cast<const uint8_t*>(d.B), static_cast<uint8_t*>(p->own_b),
+                                                                                              static_cast<int>(K), static_cast<int>(N));
+        } else {
+            dim3 grid(static_cast<unsigned>(ceil_div(N, 32)), static_cast<unsigned>(ceil_div(K, 32))), block(32, 8);
+            if (d.kind == BLZ_GEMM_FP8) transpose_kn_to_nk_kernel<uint8_t><<<grid, block, 0, stream>>>(static_cast<const uint8_t*>(d.B), static_cast<uint8_t*>(p->own_b), static_cast<int>(K), static_cast<int>(N));
+            else transpose_kn_to_nk_kernel<uint16_t><<<grid, block, 0, stream>>>(static_cast<const uint16_t*>(d.B), static_cast<uint16_t*>(p->own_b), static_cast<int>(K), static_cast<int>(N));
+        }
+        BLZ_CUDA(cudaGetLastError());
+    }
+    if (p->own_sfb) {
+        BLZ_CUDA(cudaMemsetAsync(p->own_sfb, 0, static_cast<size_t>(blz_tiled_scales_bytes(N, K)), stream));
+        const int64_t kb = K / 16;
+        const int64_t row_stride = d.b_layout == BLZ_B_NMAJOR ? 1 : kb;
+        const int64_t blk_stride = d.b_layout == BLZ_B_NMAJOR ? N : 1;
+        tile_scales_kernel<<<grid_for(N * kb, 256), 256, 0, stream>>>(static_cast<const uint8_t*>(d.B_sf), N, kb, row_stride, blk_stride, sf_katoms(K),
+                                                                      static_cast<uint8_t*>(p->own_sfb));
+        BLZ_CUDA(cudaGetLastError());
+    }
+    return BLZ_OK;
+}
+
+// B as the kernels consume it: K-major as is, or a plan-owned K-major copy; scales tiled as is, or a plan-owned tiled copy.
 blz_status prepare_b(blz_gemm_plan* p) {
     const blz_gemm_desc& d = p->desc;
     const bool fp4_b = d.kind == BLZ_GEMM_NVFP4 || d.kind == BLZ_GEMM_W4A16_F16 || d.kind == BLZ_GEMM_W4A16_BF16;
     const int64_t N = d.N, K = d.K;
     p->b_used = d.B;
     if (d.b_layout == BLZ_B_NMAJOR) {
-        if (fp4_b) {
-            blz_status s = dev_alloc(p, &p->own_b, N * K / 2, false);
-            if (s) return s;
-            repack_fp4_kn_to_nk_kernel<<<grid_for((N / 2) * (K / 2), 256), 256>>>(static_cast<const uint8_t*>(d.B), static_cast<uint8_t*>(p->own_b),
-                                                                                   static_cast<int>(K), static_cast<int>(N));
-        } else {
-            const int eb = d.kind == BLZ_GEMM_FP8 ? 1 : 2;
-            blz_status s = dev_alloc(p, &p->own_b, N * K * eb, false);
-            if (s) return s;
-            dim3 grid(static_cast<unsigned>(ceil_div(N, 32)), static_cast<unsigned>(ceil_div(K, 32))), block(32, 8);
-            if (eb == 1) transpose_kn_to_nk_kernel<uint8_t><<<grid, block>>>(static_cast<const uint8_t*>(d.B), static_cast<uint8_t*>(p->own_b), static_cast<int>(K), static_cast<int>(N));
-            else transpose_kn_to_nk_kernel<uint16_t><<<grid, block>>>(static_cast<const uint16_t*>(d.B), static_cast<uint16_t*>(p->own_b), static_cast<int>(K), static_cast<int>(N));
-        }
-        BLZ_CUDA(cudaGetLastError());
+        const int64_t bytes = fp4_b ? N * K / 2 : N * K * (d.kind == BLZ_GEMM_FP8 ? 1 : 2);
+        blz_status s = dev_alloc(p, &p->own_b, bytes, false);
+        if (s) return s;
         p->b_used = p->own_b;
     }
     if (fp4_b) {
         if (d.b_sf_layout == BLZ_SF_TILED && d.b_layout == BLZ_B_KMAJOR) {
             p->sfb_used = static_cast<const uint8_t*>(d.B_sf);
         } else {
-            const int64_t bytes = blz_tiled_scales_bytes(N, K);
-            blz_status s = dev_alloc(p, &p->own_sfb, bytes, true);
+            blz_status s = dev_alloc(p, &p->own_sfb, blz_tiled_scales_bytes(N, K), false);
             if (s) return s;
-            const int64_t kb = K / 16;
-            const int64_t row_stride = d.b_layout == BLZ_B_NMAJOR ? 1 : kb;
-            const int64_t blk_stride = d.b_layout == BLZ_B_NMAJOR ? N : 1;
-            tile_scales_kernel<<<grid_for(N * kb, 256), 256>>>(static_cast<const uint8_t*>(d.B_sf), N, kb, row_stride, blk_stride, sf_katoms(K),
-                                                                 static_cast<uint8_t*>(p->own_sfb));
-            BLZ_CUDA(cudaGetLastError());
             p->sfb_used = static_cast<const uint8_t*>(p->own_sfb);
         }
     }
-    return BLZ_OK;
+    return convert_b(p, nullptr);
 }
 
 blz_status prepare_a_scales(blz_gemm_plan* p) {
@@ -815,8 +825,11 @@ blz_status blz_gemm_plan_info(const blz_gemm_plan* p, blz_plan_info* info) {
 
 blz_status blz_gemm_plan_refresh_weights(blz_gemm_plan* p, void* stream_v) {
     if (!p) return BLZ_ERR_INVALID_ARGUMENT;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    blz_status s = convert_b(p, stream);                     // plan-owned K-major / tiled copies, where the plan made any
+    if (s) return s;
     if (!p->own_w16 || !p->w16_static) return BLZ_OK;
-    return expand_weights(p, static_cast<cudaStream_t>(stream_v));
+    return expand_weights(p, stream);
 }
 
 blz_status blz_gemm_plan_destroy(blz_gemm_plan* p) {

@@ -180,9 +180,10 @@ blz_status blz_gemm_plan_check(blz_gemm_plan* plan, void* stream);
 
 blz_status blz_gemm_plan_info(const blz_gemm_plan* plan, blz_plan_info* info);
 
-/* BLZ_FLAG_STATIC_WEIGHTS plans: expands the packed weights into the plan's 16-bit copy again (asynchronous
- * on `stream`); call it after the weights or their scales changed in place.  BLZ_OK and nothing to do for
- * every other plan. */
+/* Brings everything the plan derived from the weights at creation up to date (asynchronous on `stream`): the
+ * K-major copy of [K, N] weights, the tiled copy of row-major scales, the 16-bit copy of BLZ_FLAG_STATIC_WEIGHTS
+ * plans.  Call it after B or B_sf changed in place.  Nothing to do, BLZ_OK, for plans that read the caller's
+ * K-major weights and tiled scales directly. */
 blz_status blz_gemm_plan_refresh_weights(blz_gemm_plan* plan, void* stream);
 
 /* Frees the plan and what it owns.  Null is accepted. */
