@@ -14,6 +14,7 @@
 #include <new>
 #include <type_traits>
 
+#define BLZ_TUNING_ENTRY_POINTS        // tuning builds only: this translation unit carries the counter read-back calls
 #include "../../include/blaze_b200.h"
 #include "decode_split.h"
 #include "decode_stream_kernel.cuh"
@@ -850,20 +851,6 @@ blz_status blz_gemm_launch(const blz_gemm_desc* desc, void* C, void* stream) {
     blz_gemm_plan_destroy(p);
     return s;
 }
-
-#ifdef BLZ_KERNEL_TIMING
-// Tuning builds only: copies the per-CTA cycle counters of the last tiled-kernel launch to the host.
-blz_status blz_debug_read_timing(unsigned long long* out, int n_words) {
-    BLZ_CUDA(cudaDeviceSynchronize());
-    BLZ_CUDA(cudaMemcpyFromSymbol(out, g_blz_timing, sizeof(unsigned long long) * static_cast<size_t>(n_words)));
-    return BLZ_OK;
-}
-blz_status blz_debug_read_trace(unsigned long long* out, int n_words) {
-    BLZ_CUDA(cudaDeviceSynchronize());
-    BLZ_CUDA(cudaMemcpyFromSymbol(out, g_blz_trace, sizeof(unsigned long long) * static_cast<size_t>(n_words)));
-    return BLZ_OK;
-}
-#endif
 
 // ------------------------------------------------------------ bounded-wait self test
 

@@ -1,12 +1,25 @@
 // common.cuh -- what the GEMM kernels share: operand / epilogue enums, the epilogue parameter block
 // and its arithmetic (alpha -> bias -> SiLU / residual -> narrow, the order of Blaze's
-// src/kernels/gemm_mixed_sm100.cu:202-229), and the optional per-role cycle counters of tuning builds.
+// src/kernels/gemm_mixed_sm100.cu:202-229).
 #pragma once
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "ptx.cuh"
+
+// Per-role cycle counters and an event trace exist in tuning builds only (-DBLZ_KERNEL_TIMING pulls in
+// tuning_counters.cuh); in the library as shipped the hooks below expand to nothing.
+#ifdef BLZ_KERNEL_TIMING
+#include "tuning_counters.cuh"
+#else
+#define BLZ_T_DECL(name)
+#define BLZ_T_NOW() 0
+#define BLZ_T_ADD(acc, t0)
+#define BLZ_T_STORE(slot, v)
+#define BLZ_T_STORE_IF(cond, slot, v)
+#define BLZ_TRACE(region, i)
+#endif
 
 namespace blz {
 
@@ -31,26 +44,6 @@ struct EpilogueParams {
     int vec_ok;              // rows of C (and residual) are 16-byte aligned: wide stores allowed
 };
 
-
-// Optional per-role cycle accounting, compiled in only with -DBLZ_KERNEL_TIMING (a tuning build):
-// slot layout per CTA, 16 x u64: 0 producer wait-empty, 1 producer total, 2 mma wait-ready,
-// 3 mma wait-accumulator, 4 mma total, 5 epilogue wait-full, 6 epilogue work, 7 epilogue total, 8 tiles.
-#ifdef BLZ_KERNEL_TIMING
-__device__ unsigned long long g_blz_timing[1024 * 16];
-#define BLZ_T_DECL(name) long long name = 0
-#define BLZ_T_NOW() clock64()
-#define BLZ_T_ADD(acc, t0) acc += clock64() - (t0)
-#define BLZ_T_STORE(slot, v) g_blz_timing[(blockIdx.x & 1023) * 16 + (slot)] = static_cast<unsigned long long>(v)
-// event trace of CTA 0: region r (0 = MMA thread per stage, 1..3 = epilogue events), entry i
-__device__ unsigned long long g_blz_trace[4 * 4096];
-#define BLZ_TRACE(region, i) do { if (blockIdx.x == 0 && (i) < 4096) g_blz_trace[(region) * 4096 + (i)] = clock64(); } while (0)
-#else
-#define BLZ_TRACE(region, i)
-#define BLZ_T_DECL(name)
-#define BLZ_T_NOW() 0
-#define BLZ_T_ADD(acc, t0)
-#define BLZ_T_STORE(slot, v)
-#endif
 
 __device__ __forceinline__ float silu_f32(float v) { return v / (1.0f + __expf(-v)); }
 

@@ -84,9 +84,7 @@ decode_nvf4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     [[maybe_unused]] const long long t_entry = BLZ_T_NOW();
-#ifdef BLZ_KERNEL_TIMING
-    if (threadIdx.x == 0) BLZ_T_STORE(9, global_timer_ns());
-#endif
+    BLZ_T_STORE_IF(threadIdx.x == 0, 9, global_timer_ns());
     const int n_tile = blockIdx.x % p.n_tiles, split_idx = blockIdx.x / p.n_tiles;
     const int ks_begin = split_idx * p.stages_per_split;
     const int ks_end = min(p.k_stages_total, ks_begin + p.stages_per_split);
@@ -109,9 +107,7 @@ decode_nvf4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-#ifdef BLZ_KERNEL_TIMING
-    if (threadIdx.x == 0) BLZ_T_STORE(11, clock64() - t_entry);   // set-up
-#endif
+    BLZ_T_STORE_IF(threadIdx.x == 0, 11, clock64() - t_entry);   // set-up
 
     if (warp == 0) {
         if (elect_one()) {
@@ -151,9 +147,7 @@ decode_nvf4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
                 }
                 BLZ_T_ADD(t_wait_full, tf);
-#ifdef BLZ_KERNEL_TIMING
-                if (ks == ks_begin) BLZ_T_STORE(12, clock64() - t_entry);   // first stage landed
-#endif
+                BLZ_T_STORE_IF(ks == ks_begin, 12, clock64() - t_entry);   // first stage landed
                 tc_fence_after_sync();
                 const uint32_t sw = base + stage * Cfg::STAGE_BYTES;
                 const uint32_t sx = sw + Cfg::W_BYTES;
@@ -183,9 +177,7 @@ decode_nvf4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         // Every epilogue thread walks the same barrier sequence below whether or not its wait
         // succeeded, so a give-up in one warp can never strand the others at a named barrier.
         const bool ok = mbar_wait(acc_full_bar, 0u, abort_flag);
-#ifdef BLZ_KERNEL_TIMING
-        if (threadIdx.x == 128) BLZ_T_STORE(5, clock64() - t_entry);       // accumulator finished
-#endif
+        BLZ_T_STORE_IF(threadIdx.x == 128, 5, clock64() - t_entry);       // accumulator finished
         if (!ok) { atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_EPILOGUE); *abort_flag = 1; }
         float acc[MMA_N];
 #pragma unroll
@@ -236,9 +228,7 @@ decode_nvf4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         }
     }
 
-#ifdef BLZ_KERNEL_TIMING
-    if (threadIdx.x == 128) BLZ_T_STORE(7, clock64() - t_entry);           // epilogue finished
-#endif
+    BLZ_T_STORE_IF(threadIdx.x == 128, 7, clock64() - t_entry);           // epilogue finished
     tc_fence_before_sync();
     __syncthreads();
     if (*abort_flag != 0) {
@@ -250,9 +240,7 @@ decode_nvf4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
-#ifdef BLZ_KERNEL_TIMING
-    if (threadIdx.x == 0) { BLZ_T_STORE(10, global_timer_ns()); BLZ_T_STORE(8, clock64() - t_entry); }
-#endif
+    BLZ_T_STORE_IF(threadIdx.x == 0, 10, global_timer_ns()); BLZ_T_STORE_IF(threadIdx.x == 0, 8, clock64() - t_entry);
 }
 
 }  // namespace blz

@@ -151,9 +151,7 @@ __device__ __forceinline__ void decode_epilogue(const DecodeStreamParams& p, uin
     asm volatile("" ::"f"(e_alpha), "r"(e_mode), "r"(e_out), "r"(e_vec), "r"(p_M), "r"(p_N), "r"(p_split), "l"(e_ldc), "l"(e_ldr), "l"(e_C), "l"(e_bias), "l"(e_res));
     if (is_epi) {
         epi_ok = SLEEPY ? mbar_wait_sleepy(acc_full_bar, 0u, abort_flag) : mbar_wait(acc_full_bar, 0u, abort_flag);
-#ifdef BLZ_KERNEL_TIMING
-        if (threadIdx.x == 128) BLZ_T_STORE(5, clock64() - t_entry);
-#endif
+        BLZ_T_STORE_IF(threadIdx.x == 128, 5, clock64() - t_entry);
         if (!epi_ok) { atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_EPILOGUE); *abort_flag = 1; }
 #pragma unroll
         for (int m = 0; m < MMA_N; ++m) acc[m] = 0.0f;
@@ -177,9 +175,7 @@ __device__ __forceinline__ void decode_epilogue(const DecodeStreamParams& p, uin
             tmem_ld_wait();
             tc_fence_before_sync();
         }
-#ifdef BLZ_KERNEL_TIMING
-        if (threadIdx.x == 128) BLZ_T_STORE(1, clock64() - t_entry);
-#endif
+        BLZ_T_STORE_IF(threadIdx.x == 128, 1, clock64() - t_entry);
     }
     if (p_split > 1) {
         cluster_sync_all();                 // every CTA of the tile is past its main loop: the leader's stage buffers are free
@@ -208,26 +204,20 @@ __device__ __forceinline__ void decode_epilogue(const DecodeStreamParams& p, uin
         // possible straight-line code (this code runs once per CTA, so every instruction line is an
         // instruction-cache miss on the critical path); the epilogue arithmetic and the narrowing
         // happen in the compact row-store loop below.
-#ifdef BLZ_KERNEL_TIMING
-        if (threadIdx.x == 128) BLZ_T_STORE(2, clock64() - t_entry);
-#endif
+        BLZ_T_STORE_IF(threadIdx.x == 128, 2, clock64() - t_entry);
         griddep_wait();                      // bias / residual may come from the predecessor; C may be read by it
         named_barrier_sync(1, 128);          // all reads of the partial sums are done: the buffer can be reused
         float* stag = reinterpret_cast<float*>(gen_base);
 #pragma unroll
         for (int m = 0; m < MMA_N; ++m) stag[m * 128 + n_local] = acc[m];
         named_barrier_sync(1, 128);
-#ifdef BLZ_KERNEL_TIMING
-        if (threadIdx.x == 128) BLZ_T_STORE(6, clock64() - t_entry);
-#endif
+        BLZ_T_STORE_IF(threadIdx.x == 128, 6, clock64() - t_entry);
         if (epi_ok) {
             decode_store_rows(stag, p_M, p_N, n_tile, e_alpha, p.epi.alpha2, e_mode, e_out, e_vec, e_ldc, e_ldr, e_C, e_bias, e_res);
         }
     }
 
-#ifdef BLZ_KERNEL_TIMING
-    if (threadIdx.x == 128) BLZ_T_STORE(7, clock64() - t_entry);
-#endif
+    BLZ_T_STORE_IF(threadIdx.x == 128, 7, clock64() - t_entry);
 }
 
 // The same for wide activation tiles (MMA_N = 128): the sums do not fit a thread's registers, so
@@ -313,9 +303,7 @@ __device__ __forceinline__ void decode_teardown(uint32_t tmem_base, uint32_t tme
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, tmem_cols);
     }
-#ifdef BLZ_KERNEL_TIMING
-    if (threadIdx.x == 0) { BLZ_T_STORE(10, global_timer_ns()); }
-#endif
+    BLZ_T_STORE_IF(threadIdx.x == 0, 10, global_timer_ns());
 }
 
 template <int KIND, int MMA_N, int STAGES>
@@ -363,9 +351,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     [[maybe_unused]] const long long t_entry = BLZ_T_NOW();
-#ifdef BLZ_KERNEL_TIMING
-    if (threadIdx.x == 0) BLZ_T_STORE(9, global_timer_ns());
-#endif
+    BLZ_T_STORE_IF(threadIdx.x == 0, 9, global_timer_ns());
     const int n_tile = blockIdx.x / p.split;
     const int split_idx = blockIdx.x % p.split;             // = rank in the cluster
     const int ks_begin = split_idx * p.stages_per_split;
@@ -394,9 +380,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
     // successor may start its own set-up and weight prefetch now.
     griddep_launch_dependents();
 #endif
-#ifdef BLZ_KERNEL_TIMING
-    if (threadIdx.x == 0) BLZ_T_STORE(11, clock64() - t_entry);
-#endif
+    BLZ_T_STORE_IF(threadIdx.x == 0, 11, clock64() - t_entry);
 
     if (warp == 0) {
         if (elect_one()) {
@@ -426,9 +410,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
 #ifdef BLZ_DECODE_LATE_DEPENDENTS
             griddep_launch_dependents();     // at most one successor prefetches while this grid runs
 #endif
-#ifdef BLZ_KERNEL_TIMING
             BLZ_T_STORE(12, clock64() - t_entry); BLZ_T_STORE(14, global_timer_ns());
-#endif
             for (int ks = ks_begin; ks < ks_end; ++ks) {
                 const uint32_t sw = base + stage * Cfg::STAGE_BYTES;
                 const uint32_t sx = sw + Cfg::W_BYTES;
@@ -459,9 +441,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
                 if (!mbar_wait(Cfg::HAS_SF ? ready_bar(stage) : full_bar(stage), phase, abort_flag)) {
                     atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
                 }
-#ifdef BLZ_KERNEL_TIMING
-                if (ks == ks_begin) BLZ_T_STORE(13, clock64() - t_entry);
-#endif
+                BLZ_T_STORE_IF(ks == ks_begin, 13, clock64() - t_entry);
                 tc_fence_after_sync();
                 const uint32_t sw = base + stage * Cfg::STAGE_BYTES;
                 const uint32_t sx = sw + Cfg::W_BYTES;
@@ -787,30 +767,29 @@ decode_w4a16_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             if (!mbar_wait_warp(load_full(ls), lphase, abort_flag)) {
                 atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; break;
             }
+            BLZ_T_ADD(t_load, t0);
             [[maybe_unused]] const long long t1 = BLZ_T_NOW();
             uint32_t r[32];
             const uint32_t sf4 = *reinterpret_cast<const uint32_t*>(gen_base + Cfg::SF_OFF + ls * Cfg::SF_BYTES + j * 512 + lane * 16 + q * 4);
             expand_w4_row<BF16>(gen_base + Cfg::PK_OFF + ls * Cfg::PK_BYTES + row * 128, row, j, sf4, r);
+            BLZ_T_ADD(t_expand, t1);
             [[maybe_unused]] const long long t2 = BLZ_T_NOW();
             // the slot group is free once the MMAs of the load stage that used it last have completed
             if (!mbar_wait_warp(og_empty(og), ophase ^ 1u, abort_flag)) {
                 atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; break;
             }
             tc_fence_after_sync();
+            BLZ_T_ADD(t_slot, t2);
             [[maybe_unused]] const long long t3 = BLZ_T_NOW();
             tmem_st32(t_lane + os * Cfg::OP_COLS, r);
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(og_ready(og));
-#ifdef BLZ_KERNEL_TIMING
-            t_load += t1 - t0; t_expand += t2 - t1; t_slot += t3 - t2; t_sync += clock64() - t3;
-#endif
+            BLZ_T_ADD(t_sync, t3);
         }
-#ifdef BLZ_KERNEL_TIMING
-        if (lane == 0 && q == 0 && j == 0) { BLZ_T_STORE(0, t_load); BLZ_T_STORE(3, t_slot); BLZ_T_STORE(4, t_expand); BLZ_T_STORE(11, t_sync); }
-        if (lane == 0 && q == 0 && j == 1) { BLZ_T_STORE(12, t_load); BLZ_T_STORE(13, t_slot); BLZ_T_STORE(14, t_expand); BLZ_T_STORE(15, t_sync); }
-#endif
+        BLZ_T_STORE_IF(lane == 0 && q == 0 && j == 0, 0, t_load); BLZ_T_STORE_IF(lane == 0 && q == 0 && j == 0, 3, t_slot);
+        BLZ_T_STORE_IF(lane == 0 && q == 0 && j == 0, 4, t_expand); BLZ_T_STORE_IF(lane == 0 && q == 0 && j == 0, 11, t_sync);
     }
 
     // the epilogue warps sleep between polls: the expansion warps need every issue slot

@@ -241,7 +241,7 @@ blz_status blz_tile_scales(const uint8_t* sf, int64_t rows, int64_t K, int64_t r
 blz_status blz_wait_probe(uint64_t limit_ns, int32_t* d_status, uint64_t* d_waited_ns, void* stream);
 
 /* ---- several GPUs: fused GEMM + all-gather (no counterpart in the reference, which has no
- *      multi-GPU code; the sharded benchmark configuration of BASELINE.json gathers with NCCL after the GEMM) ----
+ *      multi-GPU code; the sharded benchmark configuration gathers the bf16 output with NCCL after the GEMM) ----
  *
  * Peer-visible buffers: blz_peer_buffer_create allocates device memory and returns a 64-byte
  * CUDA IPC handle; another process of the same box opens it with blz_peer_buffer_open (peer

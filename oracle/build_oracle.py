@@ -21,7 +21,9 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = os.environ.get("BLAZE_REFERENCE_ROOT", "/root/reference")
+# The Blaze source tree: BLAZE_REFERENCE_ROOT, else a directory named "reference" beside this repository.
+# Absent (e.g. on a GPU box) -> the steps that need it are skipped and the prebuilt files are used.
+REF_ROOT = os.environ.get("BLAZE_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 NVCC = os.environ.get("NVCC", shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc")
 
 

@@ -33,7 +33,7 @@ def main() -> None:
     B = O.ref_init_random_fp16(K * N, 123).reshape(K, N)
     C = O.ref_gemm_cpu_fp16(A, B)
     np.savez_compressed(os.path.join(HERE, "ref_gemm_cpu_fp16_48x80x96.npz"), A=A, B=B, C=C)
-    # BASELINE.json config 1 (256^3): operands are regenerated from the seeds; digests and sampled rows stored
+    # the 256^3 fp16 configuration: operands are regenerated from the seeds; digests and sampled rows stored
     M = N = K = 256
     A = O.ref_init_random_fp16(M * K, 42).reshape(M, K)
     B = O.ref_init_random_fp16(K * N, 123).reshape(K, N)

@@ -51,7 +51,7 @@ def _dense_inputs(oracle, kind, M, N, K, scale=1.0):
 @pytest.mark.parametrize("kind,out_dtype,variant,shape", [
     ("f16", "f32", "128x128", (128, 128, 64)),       # one tile, one K stage
     ("f16", "f32", "128x128", (128, 128, 256)),      # one tile, four K stages
-    ("f16", "f32", "128x128", (256, 256, 256)),      # BASELINE.json config 1 shape
+    ("f16", "f32", "128x128", (256, 256, 256)),      # the 256^3 fp16 configuration
     ("bf16", "bf16", "128x128", (256, 384, 512)),
     ("bf16", "bf16", "256x256", (256, 512, 192)),
     ("f16", "f16", "256x256", (384, 768, 1024)),
@@ -92,7 +92,7 @@ def test_dense16(oracle, cuda_device, kind, out_dtype, variant, shape):
 
 
 def test_fp16_config1_golden(oracle, cuda_device):
-    """BASELINE.json config 1: fp16 256^3, A row-major, B column-major, seeded fill 42 / 123, fp32 out,
+    """The 256^3 fp16 configuration: fp16 256^3, A row-major, B column-major, seeded fill 42 / 123, fp32 out,
     checked against the rows Blaze's own gemm_cpu_fp16 produced (tests/golden)."""
     from blaze_b200 import create_fp16_gemm_plan, destroy_fp16_gemm_plan, execute_fp16_gemm
     g = np.load(os.path.join(GOLDEN, "ref_gemm_cpu_fp16_256.npz"))
@@ -175,7 +175,7 @@ def test_fp8(oracle, cuda_device, variant, shape):
 
 
 def test_fp8_config2_sampled(oracle, cuda_device):
-    """BASELINE.json config 2 (4096^3, uniform[-1,1], per-tensor scales to 448, bf16 out): inputs are
+    """The FP8 configuration (4096^3, uniform[-1,1], per-tensor scales to 448, bf16 out): inputs are
     quantised on the GPU (bit-checked against the oracle on a slice), 48 output rows are checked."""
     torch = _torch()
     from blaze_b200 import GemmPlan, quantize_fp8
@@ -293,7 +293,7 @@ def test_nvfp4_position_coded(oracle, cuda_device, variant, M):
 
 @pytest.mark.parametrize("N,K", [(12288, 4096), (4096, 4096), (22016, 4096), (4096, 11008)])
 def test_nvfp4_config3_decode(oracle, cuda_device, N, K):
-    """BASELINE.json config 3: Llama-7B decode projections at M = 16, N(0,1) both sides, bf16 out."""
+    """The NVFP4 decode configuration: Llama-7B decode projections at M = 16, N(0,1) both sides, bf16 out."""
     from blaze_b200 import GemmPlan
     M = 16
     qa, qb = _nvfp4_inputs(oracle, M, N, K)
@@ -355,7 +355,7 @@ def test_nvfp4_nmajor_weights(oracle, cuda_device):
 
 
 def test_nvfp4_config5_sampled(oracle, cuda_device):
-    """BASELINE.json config 5 on one GPU (M=8192, N=28672, K=8192): operands quantised on the GPU,
+    """The sharded NVFP4 configuration on one GPU (M=8192, N=28672, K=8192): operands quantised on the GPU,
     24 rows of the output checked against the oracle, plus a linearity property at full size:
     doubling the activations' tensor scale doubles every output bit-exactly (bf16 keeps exponent)."""
     torch = _torch()

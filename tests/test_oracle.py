@@ -43,7 +43,7 @@ def test_golden_small_bit_exact(oracle):
 
 
 def test_golden_256_seeded(oracle):
-    """BASELINE.json config 1: operands from the seeded fill (42 / 123), result digests from the reference."""
+    """The 256^3 fp16 configuration: operands from the seeded fill (42 / 123), result digests from the reference."""
     g = np.load(os.path.join(GOLDEN, "ref_gemm_cpu_fp16_256.npz"))
     M = N = K = 256
     A = oracle.f32_to_f16(oracle.fill_uniform_rand(M * K, 42)).reshape(M, K)
