@@ -61,6 +61,7 @@ class PlanInfo(ctypes.Structure):
         ("variant", ctypes.c_int32), ("tile_m", ctypes.c_int32), ("tile_n", ctypes.c_int32), ("stages", ctypes.c_int32),
         ("split_k", ctypes.c_int32), ("grid", ctypes.c_int32), ("smem_bytes", ctypes.c_int32), ("tmem_cols", ctypes.c_int32),
         ("launches", ctypes.c_int32), ("scheduler", ctypes.c_int32), ("workspace_bytes", ctypes.c_int64),
+        ("tail_tiles", ctypes.c_int32), ("tail_split", ctypes.c_int32),
     ]
 
 

@@ -153,6 +153,9 @@ struct blz_gemm_plan {
     void* own_sfb = nullptr;
     void* own_w16 = nullptr;      // W4A16: weights expanded to 16 bit, refreshed by every execute -- or only at creation
     bool w16_static = false;      //   (BLZ_FLAG_STATIC_WEIGHTS)
+    float* own_tail = nullptr;    // split tail of the schedule: [units][tile rows][BN] fp32 partial sums
+    int tail_tiles = 0, tail_split = 1, tail_first = 0, tail_kps = 0;
+    CUtensorMap tm_tail{};
     float* own_partial = nullptr; // split-K of the tiled kernel: [splits][m_tiles*128][partial_pitch] fp32
     int split_k = 1;
     int64_t partial_pitch = 0, partial_rows = 0;
@@ -376,6 +379,39 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1, bool wide = fa
     }
     const int64_t groups = tiles < max_groups ? tiles : max_groups;
     p->grid = static_cast<int>(groups) * csize;
+    // The tail of the schedule: when the last wave holds at most half as many tiles as there are CTA groups, its
+    // tiles are cut along K so that every group works until the end (4096^3 FP8: 256 tiles on 74 pairs are
+    // 3 full waves + 34 tiles -> 68 half-K units; a 3584-column shard of the 8192 x 28672 x 8192 problem: 6 waves
+    // + 4 tiles -> 72 units of 1/18 K).  The units' fp32 partial sums go to a plan-owned scratch matrix and a
+    // second, small kernel adds them in order.  Not with the variants whose roles walk a fixed sequence, the
+    // fused gate / up epilogue, or the tiled kernel's own K split.  BLZ_TAIL_SPLIT=0 turns it off.
+    cp.tail_first = static_cast<int>(tiles); cp.tail_split = 1; cp.tail_kps = cp.k_stages; cp.total_units = static_cast<int>(tiles);
+    cp.partial_map = BLZ_MAX_DST - 1;
+    p->tail_tiles = 0; p->tail_split = 1;
+    if (share == 1 && !fused_w4 && !wide && cp.split_k == 1 && d.epilogue != BLZ_EPI_SWIGLU && tiles > groups && env_int("BLZ_TAIL_SPLIT", 1) != 0) {
+        const int64_t tail = tiles % groups;
+        int split = tail > 0 ? static_cast<int>(groups / tail) : 1;
+        if (split > 16) split = 16;
+        while (split > 1 && cp.k_stages / split < 4) --split;                      // at least four K stages per unit
+        if (split >= 2) {
+            const int kps = static_cast<int>(ceil_div(cp.k_stages, split));
+            split = static_cast<int>(ceil_div(cp.k_stages, kps));                  // no empty unit
+            const int64_t units = tail * split;
+            const int64_t tile_rows = tile_m * share;
+            void* mem = nullptr;
+            blz_status st = dev_alloc(p, &mem, units * tile_rows * bn * 4, false);
+            if (st) return st;
+            p->own_tail = static_cast<float*>(mem);
+            st = encode_map(&p->tm_tail, p->own_tail, static_cast<uint64_t>(bn) * 4, static_cast<uint64_t>(units * tile_rows), static_cast<uint64_t>(bn) * 4, 128, 128,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+            if (st) return st;
+            p->tail_tiles = static_cast<int>(tail); p->tail_split = split; p->tail_first = static_cast<int>(tiles - tail); p->tail_kps = kps;
+            cp.tail_first = p->tail_first; cp.tail_split = split; cp.tail_kps = kps; cp.total_units = static_cast<int>(tiles - tail + units);
+            p->launches += 1;
+        }
+    }
+    cp.epi_part = EpilogueParams{};
+    cp.epi_part.alpha = 1.0f; cp.epi_part.alpha2 = 1.0f; cp.epi_part.mode = EPI_NONE; cp.epi_part.out_type = OUT_F32; cp.epi_part.vec_ok = 1;
     // Dynamic scheduling: one cluster per tile in the grid; clusters that are running take over the tiles of
     // clusters that have not started (cluster launch control).  On request (desc.flags / BLZ_SCHEDULER=clc);
     // not for the variants whose roles walk a fixed tile sequence (B sharing, in-kernel W4A16 expansion).
@@ -383,6 +419,10 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1, bool wide = fa
     bool want_clc = (d.flags & BLZ_FLAG_CLC_SCHEDULER) != 0;
     if (sched_env && *sched_env) want_clc = strcmp(sched_env, "clc") == 0;
     cp.clc = (want_clc && share == 1 && !fused_w4 && tiles * csize <= 0x7FFFFFFF) ? 1 : 0;
+    if (cp.clc && p->tail_tiles) {           // the launch queue hands out whole tiles only
+        cp.tail_first = static_cast<int>(tiles); cp.tail_split = 1; cp.total_units = static_cast<int>(tiles);
+        p->tail_tiles = 0; p->tail_split = 1; p->launches -= 1;
+    }
     if (cp.clc) p->grid = static_cast<int>(tiles) * csize;
     p->clc = cp.clc;
     return BLZ_OK;
@@ -630,10 +670,24 @@ blz_status launch_cluster(blz_gemm_plan* p, int n_dst, void* const* dst, int64_t
     } else if (p->out_n == 0) {
         p->out.m[0] = p->tm_a;                  // a valid descriptor the kernel never stores through
     }
+    // the split tail: only with one destination (the reduce kernel writes C); several destinations run whole tiles
+    const bool tail = p->tail_tiles > 0 && n_dst == 1;
+    if (p->tail_tiles > 0 && !tail) {
+        const int tiles = cp.tail_first + p->tail_tiles;
+        cp.tail_first = tiles; cp.tail_split = 1; cp.total_units = tiles;
+    }
+    if (tail) p->out.m[BLZ_MAX_DST - 1] = p->tm_tail;
     cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[1];
     launch_config_cluster(p, cfg, attr, stream);
     void* cargs[4] = {&p->tm_a, &p->tm_b, &p->out, &cp};
     BLZ_CUDA(cudaLaunchKernelExC(&cfg, p->cc.fn, cargs));
+    if (tail) {
+        const int tile_rows = 128 * p->cc.cg * p->cc.share;
+        const int64_t items = static_cast<int64_t>(p->tail_tiles) * tile_rows * (p->cc.bn / 4);
+        tail_reduce_kernel<<<grid_for(items, 256), 256, 0, stream>>>(p->own_tail, p->tail_first, p->tail_tiles, p->tail_split, tile_rows, p->cc.bn,
+                                                                     cp.m_tiles, cp.n_tiles, cp.group_m, d.M, d.N, cp.epi);
+        BLZ_CUDA(cudaGetLastError());
+    }
     return BLZ_OK;
 }
 
@@ -641,7 +695,7 @@ blz_status launch_cluster(blz_gemm_plan* p, int n_dst, void* const* dst, int64_t
 
 extern "C" {
 
-int blz_version(void) { return 2; }
+int blz_version(void) { return 3; }
 
 const char* blz_status_string(blz_status s) {
     switch (s) {
@@ -820,6 +874,7 @@ blz_status blz_gemm_plan_info(const blz_gemm_plan* p, blz_plan_info* info) {
     }
     info->launches = p->launches;
     info->scheduler = p->clc ? 1 : 0;
+    info->tail_tiles = p->tail_tiles; info->tail_split = p->tail_tiles ? p->tail_split : 1;
     info->workspace_bytes = p->owned_bytes;
     return BLZ_OK;
 }
@@ -835,7 +890,7 @@ blz_status blz_gemm_plan_refresh_weights(blz_gemm_plan* p, void* stream_v) {
 
 blz_status blz_gemm_plan_destroy(blz_gemm_plan* p) {
     if (!p) return BLZ_OK;
-    cudaFree(p->own_b); cudaFree(p->own_sfa); cudaFree(p->own_sfb); cudaFree(p->own_w16); cudaFree(p->own_partial);
+    cudaFree(p->own_b); cudaFree(p->own_sfa); cudaFree(p->own_sfb); cudaFree(p->own_w16); cudaFree(p->own_partial); cudaFree(p->own_tail);
     cudaFree(p->status);
     (void)cudaGetLastError();
     delete p;

@@ -55,6 +55,16 @@ struct ClusterGemmParams {
     int sf_katoms;
     int use_tma_store;       // C (and its pitch) 16-byte aligned: epilogue stores through the output maps
     int n_dst;               // output maps in use: 1, or one per GPU for the fused all-gather
+    // The tail of the schedule.  When the tiles do not fill the last wave of CTA groups, the tiles of that
+    // partial wave are cut along K into `tail_split` units each, so that every group has work until the end:
+    // scheduled indices [0, tail_first) are whole tiles, index tail_first + u is split u % tail_split of tile
+    // tail_first + u / tail_split.  A unit stores raw fp32 partial sums of its tile to row block u of a scratch
+    // matrix (output map `partial_map`); tail_reduce_kernel adds a tile's units in order and applies the epilogue.
+    int tail_first;          // = total_units when nothing is split
+    int tail_split, tail_kps;   // units per tail tile; K stages per unit
+    int total_units;         // scheduled indices in all
+    int partial_map;         // index of the scratch matrix's map in OutputMaps
+    EpilogueParams epi_part; // what a unit's epilogue does: alpha 1, no bias / activation, fp32
     int clc;                 // tiles come from the hardware's launch queue (cluster launch control) instead of a fixed stride
     EpilogueParams epi;
     int* status;
@@ -81,6 +91,19 @@ __device__ __forceinline__ void tile_k_range(const P& p, int m_ext, int& m_tile,
     m_tile = m_ext - sidx * p.m_tiles_real;
     ks0 = sidx * p.k_per_split;
     ks1 = min(p.k_stages, ks0 + p.k_per_split);
+}
+
+// A scheduled index is a whole tile or, in the split tail, one K range of a tile: `unit` >= 0 names its row
+// block of the partial-sum scratch matrix.
+template <typename P>
+__device__ __forceinline__ void resolve_unit(const P& p, int index, int& tile, int& unit, int& ks0, int& ks1) {
+    if (index < p.tail_first) { tile = index; unit = -1; return; }
+    const int u = index - p.tail_first;
+    const int t = u / p.tail_split;
+    tile = p.tail_first + t;
+    unit = u;
+    ks0 = (u - t * p.tail_split) * p.tail_kps;
+    ks1 = min(p.k_stages, ks0 + p.tail_kps);
 }
 
 // Where the epilogue stores a tile.  Normally one map (C).  For the fused GEMM + all-gather every
@@ -253,7 +276,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int total_tiles = p.total_units;            // scheduled indices: whole tiles, then the K-split units of the tail
     const int group = blockIdx.x / Cfg::CLUSTER, num_groups = gridDim.x / Cfg::CLUSTER;   // a cluster walks tiles of (128*CG*SHARE) x BN
     const bool use_clc = Cfg::CLC_OK && p.clc != 0;
 
@@ -299,9 +322,11 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             TileFeed feed = make_feed(false);
             for (int tile = feed.take(); ok && tile >= 0; tile = feed.take()) {
                 int m_tile, n_tile;
-                int m_ext, ks0, ks1;
+                int m_ext, ks0, ks1, unit, u0 = 0, u1 = 0;
+                resolve_unit(p, tile, tile, unit, u0, u1);
                 tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_ext, n_tile);
                 tile_k_range(p, m_ext, m_tile, ks0, ks1);
+                if (unit >= 0) { ks0 = u0; ks1 = u1; }
                 const int a_row = ((m_tile * SHARE + static_cast<int>(pair)) * CG + static_cast<int>(prank)) * 128;
                 const int b_row = n_tile * BN + static_cast<int>(prank) * static_cast<int>(Cfg::B_ROWS) + static_cast<int>(pair) * static_cast<int>(Cfg::B_LOAD_ROWS);
                 for (int ks = ks0; ks < ks1; ++ks) {
@@ -400,7 +425,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (Cfg::OVERLAP ? static_cast<uint32_t>(it & 1) * Cfg::ACC_OVL_OFF : static_cast<uint32_t>(buf) * BN);
                 int ks0, ks1;
-                if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
+                if (tile >= p.tail_first) { int t_, u_; resolve_unit(p, tile, t_, u_, ks0, ks1); }     // a K-split unit of the tail
+                else if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
                 else { int m_e, n_e, m_r; tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_e, n_e); tile_k_range(p, m_e, m_r, ks0, ks1); }
                 for (int ks = ks0; ks < ks1; ++ks) {
                     [[maybe_unused]] const long long tr = BLZ_T_NOW();
@@ -531,8 +557,6 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const int eset = warp >= 12 ? 1 : 0;                       // which set of four epilogue warps
         const int epi_tid = threadIdx.x - (eset ? 384 : 128);
         const uint32_t bar_id = 1 + eset;
-        const int out_esize = p.epi.out_type == OUT_F32 ? 4 : 2;
-        const int chunk_cols = 128 / out_esize;                    // columns per 128-byte staging row
         int it = 0;
         int obuf = 0;
         bool ok = true;
@@ -540,8 +564,14 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         [[maybe_unused]] const long long t_begin = BLZ_T_NOW();
         TileFeed feed = make_feed(true);
         for (int tile = feed.take(); tile >= 0; tile = feed.take(), ++it) {
-            int m_tile, n_tile;
+            int m_tile, n_tile, unit, u0_, u1_;
+            resolve_unit(p, tile, tile, unit, u0_, u1_);
             tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_tile, n_tile);
+            // a unit of the split tail stores raw fp32 partial sums to its row block of the scratch matrix
+            const bool part = unit >= 0;
+            const EpilogueParams& epi = part ? p.epi_part : p.epi;
+            const int out_esize = epi.out_type == OUT_F32 ? 4 : 2;
+            const int chunk_cols = 128 / out_esize;                    // columns per 128-byte staging row
             const int buf = it % ACC_BUFS;
             const uint32_t use = static_cast<uint32_t>(it / ACC_BUFS);
             [[maybe_unused]] const long long tw = BLZ_T_NOW();
@@ -555,9 +585,13 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             // tensor memory or C) so that no epilogue warp is left waiting for another.
             tc_fence_after_sync();
             const int row0 = ((m_tile * SHARE + static_cast<int>(pair)) * CG + static_cast<int>(prank)) * 128;
+            // where the staged chunks go: C (column n_tile * BN + c, row row0) or the unit's block of the scratch matrix
+            const int st_col0 = part ? 0 : n_tile * BN;
+            const int st_row0 = part ? (unit * SHARE * CG + static_cast<int>(pair) * CG + static_cast<int>(prank)) * 128 : row0;
+            const int st_map0 = part ? p.partial_map : 0, st_maps = part ? 1 : p.n_dst;
             const int r_local = q * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (Cfg::OVERLAP ? static_cast<uint32_t>(it & 1) * Cfg::ACC_OVL_OFF : static_cast<uint32_t>(buf) * BN);
-            if (p.use_tma_store) {
+            if (p.use_tma_store || part) {
                 if constexpr (Cfg::EPI_SETS == 2) {
                 // (single accumulator barrier pair: the epilogue is on the tensor pipe's critical path until
                 // it hands the accumulator back)
@@ -586,9 +620,9 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         if constexpr (CG == 1) mbar_arrive(acc_empty_bar(buf)); else mbar_arrive_cluster(acc_empty_bar(buf), leader_rank);
                     }
                 };
-                const float alpha = p.epi.alpha;
-                const bool plain16 = p.epi.mode == EPI_NONE && out_esize == 2;   // scale and narrow only: no temporaries, a handful of instructions per column pair
-                const bool plain_bf16 = plain16 && p.epi.out_type == OUT_BF16;
+                const float alpha = epi.alpha;
+                const bool plain16 = epi.mode == EPI_NONE && out_esize == 2;   // scale and narrow only: no temporaries, a handful of instructions per column pair
+                const bool plain_bf16 = plain16 && epi.out_type == OUT_BF16;
                 auto stage32 = [&](const uint32_t (&a)[32], uint32_t sbuf, int c, int h) {
                     // 128-byte swizzle: 16-byte unit j of row r lives at unit (j ^ (r % 8))
                     const uint32_t srow = sbuf + r_local * 128;
@@ -609,7 +643,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         return;
                     }
                     float v[32];
-                    epilogue_math32(p.epi, a, v, row0 + r_local, n_tile * BN + c + h, p.M, p.N);
+                    epilogue_math32(epi, a, v, row0 + r_local, n_tile * BN + c + h, p.M, p.N);
                     if (out_esize == 4) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
@@ -621,7 +655,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                         for (int j = 0; j < 4; ++j) {
                             uint32_t w[4];
 #pragma unroll
-                            for (int t = 0; t < 4; ++t) w[t] = pack2_out(p.epi.out_type, v[8 * j + 2 * t], v[8 * j + 2 * t + 1]);
+                            for (int t = 0; t < 4; ++t) w[t] = pack2_out(epi.out_type, v[8 * j + 2 * t], v[8 * j + 2 * t + 1]);
                             const uint32_t dst = srow + (((h / 8 + j) ^ (r_local & 7)) << 4);
                             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
                         }
@@ -641,7 +675,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     named_barrier_sync(bar_id, 128);
                     if (epi_tid == 0) {
                         if (ok) {
-                            for (int d = 0; d < p.n_dst; ++d) tma_store_2d(&out.m[d], sbuf, (n_tile * BN + c0) * out_esize, row0);
+                            for (int d = 0; d < st_maps; ++d) tma_store_2d(&out.m[st_map0 + d], sbuf, (st_col0 + c0) * out_esize, st_row0);
                         }
                         tma_store_commit();
                     }
@@ -721,7 +755,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     if (epi_tid == 0 && eset == 0 && j == eset) BLZ_TRACE(2, 8 * it + 6);
                     if (epi_tid == 0) {
                         if (ok) {
-                            for (int d = 0; d < p.n_dst; ++d) tma_store_2d(&out.m[d], sbuf, (n_tile * BN + c0) * out_esize, row0);
+                            for (int d = 0; d < st_maps; ++d) tma_store_2d(&out.m[st_map0 + d], sbuf, (st_col0 + c0) * out_esize, st_row0);
                         }
                         tma_store_commit();
                     }
@@ -752,7 +786,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                             }
                             const int col = n_tile * BN + c0 + h;
                             float v[32];
-                            epilogue_math32(p.epi, acc, v, row0 + r_local, col, p.M, p.N);
+                            epilogue_math32(epi, acc, v, row0 + r_local, col, p.M, p.N);
                             // 128-byte swizzle: 16-byte unit j of row r lives at unit (j ^ (r % 8))
                             const uint32_t srow = sbuf + r_local * 128;
                             if (out_esize == 4) {
@@ -766,7 +800,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                                 for (int j = 0; j < 4; ++j) {
                                     uint32_t w[4];
 #pragma unroll
-                                    for (int t = 0; t < 4; ++t) w[t] = pack2_out(p.epi.out_type, v[8 * j + 2 * t], v[8 * j + 2 * t + 1]);
+                                    for (int t = 0; t < 4; ++t) w[t] = pack2_out(epi.out_type, v[8 * j + 2 * t], v[8 * j + 2 * t + 1]);
                                     const uint32_t dst = srow + (((h / 8 + j) ^ (r_local & 7)) << 4);
                                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
                                 }
@@ -777,7 +811,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     named_barrier_sync(bar_id, 128);
                     if (epi_tid == 0) {
                         if (ok) {
-                            for (int d = 0; d < p.n_dst; ++d) tma_store_2d(&out.m[d], sbuf, (n_tile * BN + c0) * out_esize, row0);
+                            for (int d = 0; d < st_maps; ++d) tma_store_2d(&out.m[st_map0 + d], sbuf, (st_col0 + c0) * out_esize, st_row0);
                         }
                         tma_store_commit();
                     }
@@ -790,12 +824,12 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     uint32_t acc[32];
                     tmem_ld32(t_row + c0, acc);
                     tmem_ld_wait();
-                    epilogue_store32_dyn(p.epi, acc, row0 + r_local, n_tile * BN + c0, p.M, p.N);
+                    epilogue_store32_dyn(epi, acc, row0 + r_local, n_tile * BN + c0, p.M, p.N);
                 }
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (ok && !p.use_tma_store && lane == 0) {       // the TMA-store path released the accumulator after its last read
+            if (ok && !(p.use_tma_store || part) && lane == 0) {       // the TMA-store path released the accumulator after its last read
                 if constexpr (CG == 1) mbar_arrive(acc_empty_bar(buf)); else mbar_arrive_cluster(acc_empty_bar(buf), leader_rank);
             }
             BLZ_T_ADD(t_work, tk);
@@ -815,7 +849,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             bool ok = true;
             for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
                 int ks0, ks1;
-                if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
+                if (tile >= p.tail_first) { int t_, u_; resolve_unit(p, tile, t_, u_, ks0, ks1); }     // a K-split unit of the tail
+                else if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
                 else { int m_e, n_e, m_r; tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_e, n_e); tile_k_range(p, m_e, m_r, ks0, ks1); }
                 for (int ks = ks0; ks < ks1; ++ks, ++n) {
                     if ((n & 1u) != static_cast<uint32_t>(eg)) continue;
@@ -847,7 +882,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             TileFeed feed = make_feed(true);
             for (int tile = feed.take(); ok && tile >= 0; tile = feed.take()) {
                 int ks0, ks1;
-                if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
+                if (tile >= p.tail_first) { int t_, u_; resolve_unit(p, tile, t_, u_, ks0, ks1); }     // a K-split unit of the tail
+                else if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
                 else { int m_e, n_e, m_r; tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_e, n_e); tile_k_range(p, m_e, m_r, ks0, ks1); }
                 for (int ks = ks0; ks < ks1; ++ks) {
                     // DIRECT: only this CTA's scale factors have to have landed, the operand tiles may still be in flight
@@ -938,6 +974,54 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     if (warp == 2) {
         tc_fence_after_sync();
         if constexpr (CG == 2) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS); else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// Finishes the tiles of the split tail: C = epilogue(alpha * sum over the tile's units, in unit order).
+// partial: [units][tile_rows][BN] fp32, unit = tile_in_tail * splits + split.  One thread per 4 columns;
+// the fixed summation order keeps results independent of timing.
+__global__ void tail_reduce_kernel(const float* __restrict__ partial, int tail_first, int tail_tiles, int splits, int tile_rows, int bn,
+                                   int m_tiles, int n_tiles, int group_m, int M, int N, EpilogueParams e) {
+    const int groups = bn / 4;
+    const long long per_tile = static_cast<long long>(tile_rows) * groups, total = per_tile * tail_tiles;
+    const int esize = e.out_type == OUT_F32 ? 4 : 2;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int t = static_cast<int>(i / per_tile);
+        const int r = static_cast<int>((i - t * per_tile) / groups), c = static_cast<int>(i % groups) * 4;
+        int m_tile, n_tile;
+        tile_coords(tail_first + t, m_tiles, n_tiles, group_m, m_tile, n_tile);
+        const long long m = static_cast<long long>(m_tile) * tile_rows + r;
+        const int n0 = n_tile * bn + c;
+        if (m >= M || n0 >= N) continue;
+        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int sp = 0; sp < splits; ++sp) {
+            const float4 x = *reinterpret_cast<const float4*>(partial + ((static_cast<long long>(t) * splits + sp) * tile_rows + r) * bn + c);
+            v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int n = n0 + k;
+            v[k] *= e.alpha;
+            if (n < N && e.mode != EPI_NONE) {
+                if ((e.mode == EPI_BIAS || e.mode == EPI_BIAS_SILU) && e.bias != nullptr)
+                    v[k] += e.out_type == OUT_BF16 ? load_out_elem<OUT_BF16>(e.bias, n) : e.out_type == OUT_F16 ? load_out_elem<OUT_F16>(e.bias, n) : load_out_elem<OUT_F32>(e.bias, n);
+                if (e.mode == EPI_SILU || e.mode == EPI_BIAS_SILU) v[k] = silu_f32(v[k]);
+                if (e.mode == EPI_RESIDUAL && e.residual != nullptr) {
+                    const long long roff = m * e.ldr + n;
+                    v[k] += e.out_type == OUT_BF16 ? load_out_elem<OUT_BF16>(e.residual, roff) : e.out_type == OUT_F16 ? load_out_elem<OUT_F16>(e.residual, roff) : load_out_elem<OUT_F32>(e.residual, roff);
+                }
+            }
+        }
+        uint8_t* dst = reinterpret_cast<uint8_t*>(e.C) + (m * e.ldc + n0) * esize;
+        const bool whole = n0 + 4 <= N && (reinterpret_cast<uintptr_t>(dst) & (esize == 4 ? 15u : 7u)) == 0;
+        if (e.out_type == OUT_F32) {
+            if (whole) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+            else for (int k = 0; k < 4 && n0 + k < N; ++k) reinterpret_cast<float*>(dst)[k] = v[k];
+        } else {
+            const uint32_t w0 = pack2_out(e.out_type, v[0], v[1]), w1 = pack2_out(e.out_type, v[2], v[3]);
+            if (whole) *reinterpret_cast<uint2*>(dst) = make_uint2(w0, w1);
+            else for (int k = 0; k < 4 && n0 + k < N; ++k) reinterpret_cast<uint16_t*>(dst)[k] = static_cast<uint16_t>((k < 2 ? w0 : w1) >> (16 * (k & 1)));
+        }
     }
 }
 

@@ -150,6 +150,8 @@ typedef struct blz_plan_info {
     int32_t launches;         /* kernels one blz_gemm_execute launches */
     int32_t scheduler;        /* 0 = static persistent schedule, 1 = cluster launch control */
     int64_t workspace_bytes;  /* device memory the plan owns */
+    int32_t tail_tiles;       /* tiles of the last, partial wave that are cut along K (0 = none), and */
+    int32_t tail_split;       /* ... into how many units each; a second small kernel adds the units */
 } blz_plan_info;
 
 typedef struct blz_gemm_plan blz_gemm_plan;

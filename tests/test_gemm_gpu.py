@@ -853,6 +853,58 @@ def test_sharded_plan_one_rank(oracle, cuda_device, exchange):
     sp.destroy()
 
 
+# ----------------------------------------------------------- the split tail of the tile schedule
+
+@pytest.mark.parametrize("kind,variant,shape,mode,out_dtype", [
+    ("nvfp4", "256x256", (2304, 2304, 4096), "none", "bf16"),       # 81 tiles on 74 pairs: 7 tail tiles, each cut along K
+    ("nvfp4", "128x128", (1300, 2000, 2048), "none", "bf16"),       # ragged M and N; 176 tiles on 148 CTAs
+    ("fp8", "128x128", (1280, 2048, 6144), "bias_silu", "f16"),     # the reduce kernel applies bias and SiLU
+    ("fp8", "256x256", (2304, 2304, 2048), "residual", "bf16"),
+    ("bf16", "256x256", (2300, 2300, 1096), "none", "f32"),         # ragged in M, N and the last K stage
+])
+def test_tail_split(oracle, cuda_device, kind, variant, shape, mode, out_dtype):
+    """When the last wave of the schedule is less than half full its tiles are cut along K (units with fp32
+    partial sums, a second kernel adds them in order): same result as the oracle, and the same bits run to run."""
+    from blaze_b200 import GemmPlan
+    torch = _torch()
+    M, N, K = shape
+    rng = np.random.default_rng(91)
+    bias_n = oracle.widen(oracle.narrow(rng.standard_normal(N).astype(np.float32), out_dtype), out_dtype)
+    res_n = oracle.widen(oracle.narrow(rng.standard_normal((M, N)).astype(np.float32), out_dtype), out_dtype)
+    if kind == "nvfp4":
+        qa, qb = _nvfp4_inputs(oracle, M, N, K)
+        (ad, asf, ga), (bd, bsf, gb) = qa, qb
+        acc, alpha = oracle.gemm_nvfp4(ad, asf, ga, bd, bsf, gb)
+        args = (_u8(ad, cuda_device), _u8(bd, cuda_device)); kw = dict(A_sf=_u8(asf, cuda_device), B_sf=_u8(bsf, cuda_device), a_scale=ga, b_scale=gb)
+    elif kind == "fp8":
+        qa, da, qb, db = _fp8_inputs(oracle, M, N, K)
+        acc = oracle.gemm_f32(oracle.e4m3_to_f32(qa), oracle.e4m3_to_f32(qb)); alpha = float(np.float32(da) * np.float32(db))
+        args = (_u8(qa, cuda_device), _u8(qb, cuda_device)); kw = dict(a_scale=da, b_scale=db)
+    else:
+        A, Bt = _dense_inputs(oracle, kind, M, N, K, scale=0.25)
+        acc = oracle.gemm_dense16(A, Bt, kind); alpha = 1.0
+        args = (bits16_to_torch(A, kind, cuda_device), bits16_to_torch(Bt, kind, cuda_device)); kw = {}
+    want32 = oracle.epilogue(acc, alpha, bias=bias_n if "bias" in mode else None, residual=res_n if mode == "residual" else None, mode=mode)
+    want = oracle.widen(oracle.narrow(want32, out_dtype), out_dtype)
+
+    def dev(x32):
+        if out_dtype == "f32":
+            return torch.from_numpy(np.ascontiguousarray(x32, np.float32)).to(cuda_device)
+        return bits16_to_torch(oracle.narrow(x32, out_dtype), out_dtype, cuda_device)
+    plan = GemmPlan(kind, M, N, K, *args, out_dtype=out_dtype, variant=variant, epilogue=mode, bias=dev(bias_n) if "bias" in mode else None,
+                    residual=dev(res_n) if mode == "residual" else None, **kw)
+    info = plan.info()
+    assert info["tail_tiles"] > 0 and info["tail_split"] >= 2 and info["launches"] == 2, info
+    outs = []
+    for _ in range(2):
+        C = _out_tensor(M, N, out_dtype, cuda_device)
+        _run(plan, C)
+        outs.append(C)
+    assert_close(torch_to_f32(outs[0], oracle, out_dtype), want, "tail split %s %s %s %s" % (kind, variant, shape, info))
+    assert torch.equal(outs[0], outs[1])
+    plan.destroy()
+
+
 # ------------------------------------------------------------ dynamic tile scheduler (cluster launch control)
 
 @pytest.mark.parametrize("kind,variant,shape", [
@@ -896,6 +948,7 @@ def test_clc_scheduler(oracle, cuda_device, kind, variant, shape):
         plan = GemmPlan(kind, M, N, K, *args, out_dtype="bf16", variant=variant, scheduler=sched, **kw)
         info = plan.info()
         assert info["scheduler"] == (1 if sched == "clc" else 0), info
+        assert info["tail_tiles"] == 0, info                  # whole tiles under both schedules: the sums are formed in the same order
         for _ in range(2):                                     # twice: the launch queue is consumed anew by every launch
             C.fill_(-7.0)
             _run(plan, C)
