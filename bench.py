@@ -712,33 +712,36 @@ def main() -> int:
 
     gather = None
     if world > 1:
-        # optional exchange step, timed beside the GEMM: NCCL all-gather of the bf16 output,
-        # result layout [world][M][N/world]
+        # optional exchange step, timed beside the GEMM, through the library's sharded plan (blz_sharded_plan_*):
+        # its own NCCL all-gather of the bf16 output, result layout [world][M][N/world]
+        from blaze_b200 import sharded
+        skw = dict(res["kw"]); skw["out_dtype"] = "bf16"
         full = torch.empty((world * M, n_local), dtype=res["C"].dtype, device=device)
+        sp_nccl = sharded.ShardedPlan(kind, M, N, K, res["A"], res["B"], exchange="nccl", **skw)
 
         def step_gather():
-            res["plan"].execute(res["C"])
-            dist.all_gather_into_tensor(full, res["C"])
+            sp_nccl.execute(full)
         g_ms, _ = time_steps(step_gather, max(5, args.steps // 3), 3, flusher, barrier)
+        sp_nccl.check()
         g_ms = max_over_ranks(g_ms)
         gather = {"ms_per_step_gemm_plus_allgather": g_ms, "tflops": 2.0 * M * N * K / (g_ms * 1e-3) / 1e12,
-                  "allgather_bytes_received_per_rank": (world - 1) * M * n_local * 2, "layout": "[world][M][N/world] bf16"}
+                  "allgather_bytes_received_per_rank": (world - 1) * M * n_local * 2, "layout": "[world][M][N/world] bf16",
+                  "through": "blz_sharded_plan, BLZ_EXCHANGE_NCCL (the library's own communicator)"}
         # the same exchange fused into the GEMM: every epilogue stores its tiles into every rank's
         # full-width output (TMA stores to peer memory over NVLink), then the ranks meet at a
         # one-element all-reduce; result layout [M][N] row-major on every rank
         try:
-            from blaze_b200 import sharded
-            out = sharded.PeerOutput(M, N, res["C"].dtype)
-            out.local.fill_(-7.0)                    # a block that never arrives stays visible
+            sp_peer = sharded.ShardedPlan(kind, M, N, K, res["A"], res["B"], exchange="peer_stores", **skw)
+            sp_peer.output.fill_(-7.0)                    # a block that never arrives stays visible
             torch.cuda.synchronize()
             barrier()
             flag = torch.zeros(1, dtype=torch.float32, device=device)
 
             def step_fused():
-                res["plan"].execute_gather(out.ptrs, N, rank * n_local)
+                sp_peer.execute()
                 dist.all_reduce(flag)
             f_ms, _ = time_steps(step_fused, max(5, args.steps // 3), 3, flusher, barrier)
-            res["plan"].check()
+            sp_peer.check()
             f_ms = max_over_ranks(f_ms)
             # Every block of the full-width output -- the one this rank wrote and the ones its peers stored over
             # NVLink -- must equal what the local GEMMs plus the NCCL all-gather give (the ranks hold
@@ -747,22 +750,28 @@ def main() -> int:
             torch.cuda.synchronize()
             barrier()
             want = sharded.gathered_to_full(full.view(world, M, n_local))
-            same_local = bool(torch.equal(out.local[:, rank * n_local:(rank + 1) * n_local], res["C"]))
-            same_all = bool(torch.equal(out.local, want))
+            res["plan"].execute(res["C"])
+            torch.cuda.synchronize()
+            same_local = bool(torch.equal(sp_peer.output[:, rank * n_local:(rank + 1) * n_local], res["C"]))
+            same_all = bool(torch.equal(sp_peer.output, want))
             del want
             t = torch.tensor([1.0 if same_all else 0.0], dtype=torch.float64, device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MIN)
             same_all_ranks = bool(t.item() == 1.0)
             gather["fused"] = {"ms_per_step_gemm_with_peer_stores": f_ms, "tflops": 2.0 * M * N * K / (f_ms * 1e-3) / 1e12,
                                "nvlink_bytes_sent_per_rank": (world - 1) * M * n_local * 2, "layout": "[M][N] row-major on every rank",
+                               "through": "blz_sharded_plan, BLZ_EXCHANGE_PEER_STORES",
                                "local_block_matches": same_local, "all_blocks_match": same_all_ranks}
-            out.close()
+            barrier()
+            sp_peer.destroy()
             if not same_all_ranks:
                 raise GatherMismatch("fused GEMM + all-gather: the full-width output differs from GEMM + NCCL all-gather on some rank")
         except GatherMismatch:
             raise
         except Exception as ex:   # an unavailable exchange variant is reported beside the headline, never instead of it
             gather["fused"] = {"error": str(ex)[:300]}
+        barrier()
+        sp_nccl.destroy()
         del full
     flops_total = 2.0 * M * N * K
     value = flops_total / (ms * 1e-3) / 1e12

@@ -19,7 +19,7 @@ F16, BF16, F32 = range(3)
 EPI_NONE, EPI_BIAS, EPI_SILU, EPI_BIAS_SILU, EPI_RESIDUAL_ADD, EPI_SWIGLU = range(6)
 B_KMAJOR, B_NMAJOR = range(2)
 SF_ROWMAJOR, SF_TILED = range(2)
-FLAG_CLC_SCHEDULER, FLAG_STATIC_WEIGHTS = 1, 2
+FLAG_CLC_SCHEDULER, FLAG_STATIC_WEIGHTS, FLAG_TAIL_SPLIT = 1, 2, 4
 VARIANT_AUTO, VARIANT_TILE_128x128, VARIANT_PAIR_256x256, VARIANT_DECODE, VARIANT_QUAD_512x256, VARIANT_PAIR_256x384 = range(6)
 
 KINDS = {"f16": GEMM_F16, "bf16": GEMM_BF16, "fp8": GEMM_FP8, "nvfp4": GEMM_NVFP4,

@@ -384,11 +384,15 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1, bool wide = fa
     // 3 full waves + 34 tiles -> 68 half-K units; a 3584-column shard of the 8192 x 28672 x 8192 problem: 6 waves
     // + 4 tiles -> 72 units of 1/18 K).  The units' fp32 partial sums go to a plan-owned scratch matrix and a
     // second, small kernel adds them in order.  Not with the variants whose roles walk a fixed sequence, the
-    // fused gate / up epilogue, or the tiled kernel's own K split.  BLZ_TAIL_SPLIT=0 turns it off.
+    // fused gate / up epilogue, or the tiled kernel's own K split.
+    // Measured on B200 the second launch costs more than the idle tail it removes (FP8 4096^3: 62.3 against
+    // 55.5 us; NVFP4 8192 x 3584 x 8192: 106 against 99.7 us), so it runs on request only:
+    // desc.flags & BLZ_FLAG_TAIL_SPLIT, or BLZ_TAIL_SPLIT=1.
     cp.tail_first = static_cast<int>(tiles); cp.tail_split = 1; cp.tail_kps = cp.k_stages; cp.total_units = static_cast<int>(tiles);
     cp.partial_map = BLZ_MAX_DST - 1;
     p->tail_tiles = 0; p->tail_split = 1;
-    if (share == 1 && !fused_w4 && !wide && cp.split_k == 1 && d.epilogue != BLZ_EPI_SWIGLU && tiles > groups && env_int("BLZ_TAIL_SPLIT", 1) != 0) {
+    if (share == 1 && !fused_w4 && !wide && cp.split_k == 1 && d.epilogue != BLZ_EPI_SWIGLU && tiles > groups &&
+        env_int("BLZ_TAIL_SPLIT", (d.flags & BLZ_FLAG_TAIL_SPLIT) ? 1 : 0) != 0) {
         const int64_t tail = tiles % groups;
         int split = tail > 0 ? static_cast<int>(groups / tail) : 1;
         if (split > 16) split = 16;

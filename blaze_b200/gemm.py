@@ -34,7 +34,7 @@ def _stream(stream=None):
 def make_desc(kind: str, M: int, N: int, K: int, A, B, *, A_sf=None, B_sf=None, a_scale: float = 1.0, b_scale: float = 1.0,
               out_dtype: str = "bf16", epilogue: str = "none", bias=None, residual=None, b_layout: str = "kmajor",
               a_sf_layout: str = "rowmajor", b_sf_layout: str = "rowmajor", variant: str = "auto", ldc: int = 0, b_scale2: float = 0.0,
-              scheduler: str = "static", static_weights: bool = False):
+              scheduler: str = "static", static_weights: bool = False, tail_split: bool = False):
     """blz_gemm_desc from keyword arguments (field meanings: include/blaze_b200.h)."""
     d = nv.GemmDesc()
     d.kind = nv.KINDS[kind]
@@ -50,7 +50,8 @@ def make_desc(kind: str, M: int, N: int, K: int, A, B, *, A_sf=None, B_sf=None, 
     d.bias, d.residual = _ptr(bias), _ptr(residual)
     d.ldc = int(ldc)
     d.b_scale2 = float(b_scale2)
-    d.flags = (nv.FLAG_CLC_SCHEDULER if scheduler == "clc" else 0) | (nv.FLAG_STATIC_WEIGHTS if static_weights else 0)
+    d.flags = ((nv.FLAG_CLC_SCHEDULER if scheduler == "clc" else 0) | (nv.FLAG_STATIC_WEIGHTS if static_weights else 0)
+               | (nv.FLAG_TAIL_SPLIT if tail_split else 0))
     return d
 
 
@@ -61,11 +62,11 @@ class GemmPlan:
                  b_scale: float = 1.0, out_dtype: str = "bf16", epilogue: str = "none", bias=None, residual=None,
                  b_layout: str = "kmajor", a_sf_layout: str = "rowmajor", b_sf_layout: str = "rowmajor",
                  variant: str = "auto", ldc: int = 0, b_scale2: float = 0.0, scheduler: str = "static",
-                 static_weights: bool = False):
+                 static_weights: bool = False, tail_split: bool = False):
         L = nv.lib()
         d = make_desc(kind, M, N, K, A, B, A_sf=A_sf, B_sf=B_sf, a_scale=a_scale, b_scale=b_scale, out_dtype=out_dtype, epilogue=epilogue,
                       bias=bias, residual=residual, b_layout=b_layout, a_sf_layout=a_sf_layout, b_sf_layout=b_sf_layout, variant=variant,
-                      ldc=ldc, b_scale2=b_scale2, scheduler=scheduler, static_weights=static_weights)
+                      ldc=ldc, b_scale2=b_scale2, scheduler=scheduler, static_weights=static_weights, tail_split=tail_split)
         self._keep = (A, B, A_sf, B_sf, bias, residual)   # operands must outlive the plan
         self._handle = ctypes.c_void_p()
         self.kind, self.M, self.N, self.K, self.out_dtype = kind, int(M), int(N), int(K), out_dtype

@@ -107,6 +107,10 @@ typedef enum blz_gemm_flags {
                                   include/gemm/tmem_utils.cuh:251-305 and never wires (its persistent kernel
                                   claims tiles with atomicAdd, src/kernels/gemm_fp4_blkscaled_sm100.cu:555-563).
                                   Ignored by the 512x256 variant and by in-kernel W4A16 expansion. */
+    BLZ_FLAG_TAIL_SPLIT = 4,    /* tiled variants: when the last wave of tiles is at most half full, cut its tiles along K
+                                  into units that keep every CTA group busy; a second small kernel adds the units'
+                                  fp32 partial sums in a fixed order (run-to-run identical).  Off by default: on B200
+                                  the second launch costs more than the idle tail it removes. */
     BLZ_FLAG_STATIC_WEIGHTS = 2 /* W4A16, M > 128: the caller promises that the packed weights and their scales
                                   do not change while the plan lives (or calls blz_gemm_plan_refresh_weights
                                   after changing them).  The plan then expands them ONCE, at creation, into a

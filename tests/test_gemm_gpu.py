@@ -863,8 +863,8 @@ def test_sharded_plan_one_rank(oracle, cuda_device, exchange):
     ("bf16", "256x256", (2300, 2300, 1096), "none", "f32"),         # ragged in M, N and the last K stage
 ])
 def test_tail_split(oracle, cuda_device, kind, variant, shape, mode, out_dtype):
-    """When the last wave of the schedule is less than half full its tiles are cut along K (units with fp32
-    partial sums, a second kernel adds them in order): same result as the oracle, and the same bits run to run."""
+    """On request, when the last wave of the schedule is at most half full, its tiles are cut along K (units with
+    fp32 partial sums, a second kernel adds them in order): same result as the oracle, and the same bits run to run."""
     from blaze_b200 import GemmPlan
     torch = _torch()
     M, N, K = shape
@@ -892,7 +892,7 @@ def test_tail_split(oracle, cuda_device, kind, variant, shape, mode, out_dtype):
             return torch.from_numpy(np.ascontiguousarray(x32, np.float32)).to(cuda_device)
         return bits16_to_torch(oracle.narrow(x32, out_dtype), out_dtype, cuda_device)
     plan = GemmPlan(kind, M, N, K, *args, out_dtype=out_dtype, variant=variant, epilogue=mode, bias=dev(bias_n) if "bias" in mode else None,
-                    residual=dev(res_n) if mode == "residual" else None, **kw)
+                    residual=dev(res_n) if mode == "residual" else None, tail_split=True, **kw)
     info = plan.info()
     assert info["tail_tiles"] > 0 and info["tail_split"] >= 2 and info["launches"] == 2, info
     outs = []
