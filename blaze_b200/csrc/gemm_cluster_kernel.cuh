@@ -416,6 +416,12 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             for (int tile = feed.take(); ok && tile >= 0; tile = feed.take(), ++it) {
                 const int buf = it % ACC_BUFS;
                 const uint32_t use = static_cast<uint32_t>(it / ACC_BUFS);
+                // The tile's first stage was loaded long ago (the producer runs ahead through the ring): its barrier
+                // is looked at BEFORE the accumulator's, so that this poll's round trip (about 200 cycles even on a
+                // completed phase) is spent while the epilogue still drains, not after it has handed the accumulator back.
+                if (!mbar_wait(Cfg::DIRECT ? full_bar(stage) : ready_bar(stage), phase, abort_flag)) {
+                    atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
+                }
                 [[maybe_unused]] const long long ta = BLZ_T_NOW();
                 if (!mbar_wait(acc_empty_bar(buf), (use & 1u) ^ 1u, abort_flag)) {
                     atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_ACC); *abort_flag = 1; ok = false; break;
@@ -430,7 +436,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 else { int m_e, n_e, m_r; tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_e, n_e); tile_k_range(p, m_e, m_r, ks0, ks1); }
                 for (int ks = ks0; ks < ks1; ++ks) {
                     [[maybe_unused]] const long long tr = BLZ_T_NOW();
-                    if (!mbar_wait(Cfg::DIRECT ? full_bar(stage) : ready_bar(stage), phase, abort_flag)) {
+                    if (ks != ks0 && !mbar_wait(Cfg::DIRECT ? full_bar(stage) : ready_bar(stage), phase, abort_flag)) {
                         atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_MMA_FULL); *abort_flag = 1; ok = false; break;
                     }
                     BLZ_T_ADD(t_wait_ready, tr);

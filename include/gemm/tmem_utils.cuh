@@ -106,6 +106,32 @@ __device__ __forceinline__ void blkscaled_mma_mxf4nvf4(tmem_addr_t d_tmem, uint6
         ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate ? 1u : 0u), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
 }
 
+// ---- cluster launch control (Blaze: tmem_utils.cuh:251-305 sketches these names and never calls them).
+// clc_try_cancel asks the hardware to cancel a cluster of this grid that has not started; the 16-byte answer lands in
+// shared memory and completes 16 bytes on the mbarrier (arm it with mbarrier_expect_tx(mbar, 16) first, then
+// mbarrier_wait).  The answer is opaque: it is decoded with the query instructions, not by reading bits.
+__device__ __forceinline__ void clc_try_cancel(void* smem_response, uint64_t* mbar_smem, uint32_t /*cta_mask*/ = 1u) {
+    asm volatile("clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.b128 [%0], [%1];"
+                 ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_response))), "r"(static_cast<uint32_t>(__cvta_generic_to_shared(mbar_smem))) : "memory");
+}
+struct ClcResponse { uint32_t data[4]; };
+// true when a cluster was cancelled, i.e. its tile now belongs to the caller
+__device__ __forceinline__ bool clc_is_valid(const ClcResponse* resp) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .b128 rr;\n\t.reg .pred p;\n\tld.shared.b128 rr, [%1];\n\t"
+                 "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 p, rr;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(resp))) : "memory");
+    return ok != 0;
+}
+// x index of the cancelled cluster's first CTA (the linear tile id of a one-dimensional grid); only after clc_is_valid
+__device__ __forceinline__ uint32_t clc_get_linear_id(const ClcResponse* resp) {
+    uint32_t x;
+    asm volatile("{\n\t.reg .b128 rr;\n\tld.shared.b128 rr, [%1];\n\t"
+                 "clusterlaunchcontrol.query_cancel.get_first_ctaid::x.b32.b128 %0, rr;\n\t}"
+                 : "=r"(x) : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(resp))) : "memory");
+    return x;
+}
+
 #endif  // __CUDACC__
 
 }  // namespace blaze
