@@ -634,6 +634,7 @@ def main() -> int:
     ap.add_argument("--decode-kind", default="nvfp4", choices=["nvfp4", "fp8", "w4a16_bf16", "w4a16_f16"],
                     help="operand kind of --workload decode (the reference's decode configuration is nvfp4)")
     ap.add_argument("--no-others", action="store_true", help="skip the secondary workloads (decode, comparator, others)")
+    ap.add_argument("--comparator", action="store_true", help="with --no-others: still time cuBLASLt's scaled matmul on the main workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--sustained-seconds", type=float, default=1.5, help="length of the back-to-back region (0 = skip)")
     args = ap.parse_args()
@@ -809,10 +810,12 @@ def main() -> int:
     if gather:
         line["gather"] = gather
 
+    if rank == 0 and world == 1 and args.no_others and args.comparator:
+        line["comparator"] = {name: run_comparator(kind, M, N, K, device, min(args.steps, 20), flusher)}
     if rank == 0 and world == 1 and not args.no_others:
         # the second half of the metric: decode HBM GB/s on the M = 16 projections (NVFP4), compact
         try:
-            dec = run_decode(device, 5, 3, peaks, kind="nvfp4")
+            dec = run_decode(device, 20, 50, peaks, kind="nvfp4")     # after the sustained leg: enough replays for the clocks to settle
             line["decode"] = compact_decode(dec)
             launches += sum(d["launches"] for d in dec)
         except Exception as ex:
