@@ -100,14 +100,14 @@ int grid_for(int64_t work_items, int threads) {
 
 struct ClusterChoice {
     const void* fn;
-    int cg, bn, stages, acc_bufs, smem, tmem_cols, threads, share;
+    int cg, bn, stages, acc_bufs, smem, tmem_cols, threads, share, epi_warps;
 };
 
 template <int KIND, int CG, int BN, int STAGES, int ACC, int SHARE = 1>
 ClusterChoice cluster_choice() {
     using Cfg = ClusterGemmConfig<KIND, CG, BN, STAGES, ACC, SHARE>;
     return ClusterChoice{reinterpret_cast<const void*>(&gemm_cluster_kernel<KIND, CG, BN, STAGES, ACC, SHARE>), CG, BN, STAGES, ACC,
-                         static_cast<int>(Cfg::SMEM_BYTES), static_cast<int>(Cfg::TMEM_COLS), Cfg::THREADS, SHARE};
+                         static_cast<int>(Cfg::SMEM_BYTES), static_cast<int>(Cfg::TMEM_COLS), Cfg::THREADS, SHARE, 4 * Cfg::EPI_SETS};
 }
 
 ClusterChoice pick_cluster_kernel(int mma_kind, int cg, int share, bool wide = false) {
@@ -153,9 +153,10 @@ struct blz_gemm_plan {
     void* own_sfb = nullptr;
     void* own_w16 = nullptr;      // W4A16: weights expanded to 16 bit, refreshed by every execute -- or only at creation
     bool w16_static = false;      //   (BLZ_FLAG_STATIC_WEIGHTS)
-    float* own_tail = nullptr;    // split tail of the schedule: [units][tile rows][BN] fp32 partial sums
+    float* own_tail = nullptr;    // split tail of the schedule: fp32 partial sums of the K-split units, [units][tile rows][BN] in all
+    uint32_t* tail_flags = nullptr;   //   and one arrival counter per tail tile and CTA of a group
+    uint32_t tail_seq = 0;        //   launches that ran the split tail so far (the counters only grow)
     int tail_tiles = 0, tail_split = 1, tail_first = 0, tail_kps = 0;
-    CUtensorMap tm_tail{};
     float* own_partial = nullptr; // split-K of the tiled kernel: [splits][m_tiles*128][partial_pitch] fp32
     int split_k = 1;
     int64_t partial_pitch = 0, partial_rows = 0;
@@ -380,42 +381,48 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1, bool wide = fa
     const int64_t groups = tiles < max_groups ? tiles : max_groups;
     p->grid = static_cast<int>(groups) * csize;
     // The tail of the schedule: when the last wave holds at most half as many tiles as there are CTA groups, its
-    // tiles are cut along K so that every group works until the end (4096^3 FP8: 256 tiles on 74 pairs are
-    // 3 full waves + 34 tiles -> 68 half-K units; a 3584-column shard of the 8192 x 28672 x 8192 problem: 6 waves
-    // + 4 tiles -> 72 units of 1/18 K).  The units' fp32 partial sums go to a plan-owned scratch matrix and a
-    // second, small kernel adds them in order.  Not with the variants whose roles walk a fixed sequence, the
-    // fused gate / up epilogue, or the tiled kernel's own K split.
-    // Measured on B200 the second launch costs more than the idle tail it removes (FP8 4096^3: 62.3 against
-    // 55.5 us; NVFP4 8192 x 3584 x 8192: 106 against 99.7 us), so it runs on request only:
-    // desc.flags & BLZ_FLAG_TAIL_SPLIT, or BLZ_TAIL_SPLIT=1.
+    // tiles can be cut along K so that every group works until the end (4096^3 FP8: 256 tiles on 74 pairs are
+    // 3 full waves + 34 tiles -> 68 half-K units; 512 x 12288 x 4096: 74 + 22 tiles -> 66 units of a third of K;
+    // 512 x 4096 x 11008: 32 tiles -> 64 units, no whole tile at all).  The units of a tile exchange fp32 partial
+    // sums through a plan-owned scratch array inside the same launch and each finishes a slice of the tile's
+    // columns (sums in unit order: results do not depend on timing).  Not with the variants whose roles walk a
+    // fixed sequence, the fused gate / up epilogue, the tiled kernel's own K split or the launch-queue scheduler.
+    // Measured on B200 (per-phase cycle stamps of the tuning build, FP8 4096^3): a unit's exchange -- accumulator
+    // to scratch 3.7 k cycles, fence and publish 2.2 k, wait for the other units 1.4 k, sum / finish / store 9 k --
+    // costs about as much as 32 K stages of a whole 256x256 tile, so cutting pays only for long K and three or
+    // more units (f16 512 x 12288 x 4096: 59.0 -> 55.1 us; FP8 4096^3: 56.0 -> 58.3 us; NVFP4 8192 x 3584 x 8192:
+    // 111.3 -> 115.5 us).  It therefore runs on request only: desc.flags & BLZ_FLAG_TAIL_SPLIT, or BLZ_TAIL_SPLIT=1.
     cp.tail_first = static_cast<int>(tiles); cp.tail_split = 1; cp.tail_kps = cp.k_stages; cp.total_units = static_cast<int>(tiles);
-    cp.partial_map = BLZ_MAX_DST - 1;
+    cp.tail_scratch = nullptr; cp.tail_flags = nullptr; cp.tail_target = 0;
     p->tail_tiles = 0; p->tail_split = 1;
-    if (share == 1 && !fused_w4 && !wide && cp.split_k == 1 && d.epilogue != BLZ_EPI_SWIGLU && tiles > groups &&
+    const int64_t tail = tiles % max_groups;
+    if (share == 1 && !fused_w4 && !wide && cp.split_k == 1 && d.epilogue != BLZ_EPI_SWIGLU && tail > 0 &&
         env_int("BLZ_TAIL_SPLIT", (d.flags & BLZ_FLAG_TAIL_SPLIT) ? 1 : 0) != 0) {
-        const int64_t tail = tiles % groups;
-        int split = tail > 0 ? static_cast<int>(groups / tail) : 1;
+        int split = static_cast<int>(max_groups / tail);
         if (split > 16) split = 16;
         while (split > 1 && cp.k_stages / split < 4) --split;                      // at least four K stages per unit
+        int kps = cp.k_stages;
         if (split >= 2) {
-            const int kps = static_cast<int>(ceil_div(cp.k_stages, split));
+            kps = static_cast<int>(ceil_div(cp.k_stages, split));
             split = static_cast<int>(ceil_div(cp.k_stages, kps));                  // no empty unit
+        }
+        if (split >= 2) {
             const int64_t units = tail * split;
             const int64_t tile_rows = tile_m * share;
             void* mem = nullptr;
             blz_status st = dev_alloc(p, &mem, units * tile_rows * bn * 4, false);
             if (st) return st;
             p->own_tail = static_cast<float*>(mem);
-            st = encode_map(&p->tm_tail, p->own_tail, static_cast<uint64_t>(bn) * 4, static_cast<uint64_t>(units * tile_rows), static_cast<uint64_t>(bn) * 4, 128, 128,
-                            CU_TENSOR_MAP_SWIZZLE_128B);
+            st = dev_alloc(p, &mem, tail * csize * 4, true);
             if (st) return st;
+            p->tail_flags = static_cast<uint32_t*>(mem);
+            p->tail_seq = 0;
             p->tail_tiles = static_cast<int>(tail); p->tail_split = split; p->tail_first = static_cast<int>(tiles - tail); p->tail_kps = kps;
             cp.tail_first = p->tail_first; cp.tail_split = split; cp.tail_kps = kps; cp.total_units = static_cast<int>(tiles - tail + units);
-            p->launches += 1;
+            cp.tail_scratch = reinterpret_cast<float4*>(p->own_tail); cp.tail_flags = p->tail_flags;
+            p->grid = static_cast<int>(cp.total_units < max_groups ? cp.total_units : max_groups) * csize;    // few tiles: one group per unit
         }
     }
-    cp.epi_part = EpilogueParams{};
-    cp.epi_part.alpha = 1.0f; cp.epi_part.alpha2 = 1.0f; cp.epi_part.mode = EPI_NONE; cp.epi_part.out_type = OUT_F32; cp.epi_part.vec_ok = 1;
     // Dynamic scheduling: one cluster per tile in the grid; clusters that are running take over the tiles of
     // clusters that have not started (cluster launch control).  On request (desc.flags / BLZ_SCHEDULER=clc);
     // not for the variants whose roles walk a fixed tile sequence (B sharing, in-kernel W4A16 expansion).
@@ -425,7 +432,8 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1, bool wide = fa
     cp.clc = (want_clc && share == 1 && !fused_w4 && tiles * csize <= 0x7FFFFFFF) ? 1 : 0;
     if (cp.clc && p->tail_tiles) {           // the launch queue hands out whole tiles only
         cp.tail_first = static_cast<int>(tiles); cp.tail_split = 1; cp.total_units = static_cast<int>(tiles);
-        p->tail_tiles = 0; p->tail_split = 1; p->launches -= 1;
+        p->tail_tiles = 0; p->tail_split = 1;
+        p->grid = static_cast<int>(groups) * csize;
     }
     if (cp.clc) p->grid = static_cast<int>(tiles) * csize;
     p->clc = cp.clc;
@@ -674,24 +682,18 @@ blz_status launch_cluster(blz_gemm_plan* p, int n_dst, void* const* dst, int64_t
     } else if (p->out_n == 0) {
         p->out.m[0] = p->tm_a;                  // a valid descriptor the kernel never stores through
     }
-    // the split tail: only with one destination (the reduce kernel writes C); several destinations run whole tiles
+    // the split tail: only with one destination (its units finish their tiles with plain stores to C); several
+    // destinations run whole tiles
     const bool tail = p->tail_tiles > 0 && n_dst == 1;
     if (p->tail_tiles > 0 && !tail) {
         const int tiles = cp.tail_first + p->tail_tiles;
         cp.tail_first = tiles; cp.tail_split = 1; cp.total_units = tiles;
     }
-    if (tail) p->out.m[BLZ_MAX_DST - 1] = p->tm_tail;
+    if (tail) cp.tail_target = ++p->tail_seq * static_cast<uint32_t>(p->cc.epi_warps * p->tail_split);
     cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[1];
     launch_config_cluster(p, cfg, attr, stream);
     void* cargs[4] = {&p->tm_a, &p->tm_b, &p->out, &cp};
     BLZ_CUDA(cudaLaunchKernelExC(&cfg, p->cc.fn, cargs));
-    if (tail) {
-        const int tile_rows = 128 * p->cc.cg * p->cc.share;
-        const int64_t items = static_cast<int64_t>(p->tail_tiles) * tile_rows * (p->cc.bn / 4);
-        tail_reduce_kernel<<<grid_for(items, 256), 256, 0, stream>>>(p->own_tail, p->tail_first, p->tail_tiles, p->tail_split, tile_rows, p->cc.bn,
-                                                                     cp.m_tiles, cp.n_tiles, cp.group_m, d.M, d.N, cp.epi);
-        BLZ_CUDA(cudaGetLastError());
-    }
     return BLZ_OK;
 }
 
@@ -858,6 +860,10 @@ blz_status blz_gemm_plan_check(blz_gemm_plan* p, void* stream_v) {
         g_last_cuda_error = word;
         snprintf(g_last_cuda_error_text, sizeof(g_last_cuda_error_text), "device error word 0x%x", word);
         BLZ_CUDA(cudaMemset(p->status, 0, sizeof(int)));
+        if (p->tail_flags) {      // a launch that gave up may have left the units' arrival counters short: start them over
+            BLZ_CUDA(cudaMemset(p->tail_flags, 0, static_cast<size_t>(p->tail_tiles) * p->cc.cg * p->cc.share * sizeof(uint32_t)));
+            p->tail_seq = 0;
+        }
         return BLZ_ERR_DEVICE_TIMEOUT;
     }
     return BLZ_OK;
@@ -894,7 +900,7 @@ blz_status blz_gemm_plan_refresh_weights(blz_gemm_plan* p, void* stream_v) {
 
 blz_status blz_gemm_plan_destroy(blz_gemm_plan* p) {
     if (!p) return BLZ_OK;
-    cudaFree(p->own_b); cudaFree(p->own_sfa); cudaFree(p->own_sfb); cudaFree(p->own_w16); cudaFree(p->own_partial); cudaFree(p->own_tail);
+    cudaFree(p->own_b); cudaFree(p->own_sfa); cudaFree(p->own_sfb); cudaFree(p->own_w16); cudaFree(p->own_partial); cudaFree(p->own_tail); cudaFree(p->tail_flags);
     cudaFree(p->status);
     (void)cudaGetLastError();
     delete p;

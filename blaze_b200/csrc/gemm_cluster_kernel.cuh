@@ -58,13 +58,17 @@ struct ClusterGemmParams {
     // The tail of the schedule.  When the tiles do not fill the last wave of CTA groups, the tiles of that
     // partial wave are cut along K into `tail_split` units each, so that every group has work until the end:
     // scheduled indices [0, tail_first) are whole tiles, index tail_first + u is split u % tail_split of tile
-    // tail_first + u / tail_split.  A unit stores raw fp32 partial sums of its tile to row block u of a scratch
-    // matrix (output map `partial_map`); tail_reduce_kernel adds a tile's units in order and applies the epilogue.
+    // tail_first + u / tail_split (tail_first = 0: every tile is cut -- few tiles and a long K).  All units run
+    // in the same, last wave on different CTA groups.  A unit's CTAs store raw fp32 partial sums to their block
+    // of a scratch array, publish them (one release per epilogue warp on the tile's counter), wait -- bounded --
+    // until the counter shows every unit of the tile, and then each finishes its own slice of the tile's
+    // columns: the sum over the units in unit order (results do not depend on timing), epilogue, store to C.
     int tail_first;          // = total_units when nothing is split
     int tail_split, tail_kps;   // units per tail tile; K stages per unit
     int total_units;         // scheduled indices in all
-    int partial_map;         // index of the scratch matrix's map in OutputMaps
-    EpilogueParams epi_part; // what a unit's epilogue does: alpha 1, no bias / activation, fp32
+    float4* tail_scratch;    // [unit][CTA of the group][BN / 4 column groups][128 rows] of four fp32 sums
+    uint32_t* tail_flags;    // [tail tile][CTA of the group]: releases so far, over all launches of the plan
+    uint32_t tail_target;    // the counter value that says "all units of this launch have published"
     int clc;                 // tiles come from the hardware's launch queue (cluster launch control) instead of a fixed stride
     EpilogueParams epi;
     int* status;
@@ -104,6 +108,140 @@ __device__ __forceinline__ void resolve_unit(const P& p, int index, int& tile, i
     unit = u;
     ks0 = (u - t * p.tail_split) * p.tail_kps;
     ks1 = min(p.k_stages, ks0 + p.tail_kps);
+}
+
+// Epilogue of one K-split unit of the tail, for one epilogue warp (all 32 lanes call it): raw sums to the unit's
+// scratch block, accumulator handed back, partial sums published, then -- once every unit of the tile has
+// published -- this unit's slice of the tile's column groups summed over the units in unit order, finished and
+// stored to C.  False: the bounded wait for the other units ran out.
+template <int CG, int BN, int SETS, int CSIZE>
+__device__ __noinline__ bool tail_unit_epilogue(float4* scratch, uint32_t* flags, uint32_t target, int split, int unit, int cta_in_group,
+                                                uint32_t t_row, int eset, int r_local, uint32_t acc_empty, uint32_t leader_rank,
+                                                const volatile int* abort_flag, EpilogueParams epi, int row0, int col0, int M, int N, uint32_t warp_smem) {
+    constexpr int GROUPS4 = BN / 4;
+    const int lane = threadIdx.x & 31;
+    const int t_tail = unit / split, s_unit = unit - t_tail * split;
+    const int e_out = epi.out_type;
+    const long long e_ldc = epi.ldc;
+    uint8_t* const e_c = reinterpret_cast<uint8_t*>(epi.C);
+    // lanes are rows, so a warp's store of one column group is 512 contiguous bytes
+    float4* dst = scratch + (static_cast<size_t>(unit) * CSIZE + cta_in_group) * (GROUPS4 * 128) + r_local;
+    [[maybe_unused]] const long long ts0 = BLZ_T_NOW();
+    // two 32-column groups per step: the second tensor-memory load is in flight while the first one's stores issue
+    constexpr int STEP = 32 * SETS;
+#pragma unroll 1
+    for (int c0 = eset * 32; c0 < BN; c0 += 2 * STEP) {
+        uint32_t acc[32], acc_b[32];
+        const bool second = c0 + STEP < BN;
+        tmem_ld32(t_row + c0, acc);
+        if (second) tmem_ld32(t_row + c0 + STEP, acc_b);
+        tmem_ld_wait();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            dst[(c0 / 4 + k) * 128] = make_float4(__uint_as_float(acc[4 * k]), __uint_as_float(acc[4 * k + 1]), __uint_as_float(acc[4 * k + 2]), __uint_as_float(acc[4 * k + 3]));
+        if (second) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                dst[((c0 + STEP) / 4 + k) * 128] = make_float4(__uint_as_float(acc_b[4 * k]), __uint_as_float(acc_b[4 * k + 1]), __uint_as_float(acc_b[4 * k + 2]), __uint_as_float(acc_b[4 * k + 3]));
+        }
+    }
+    // nothing follows a unit, but the barrier protocol stays whole
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) {
+        if constexpr (CG == 1) mbar_arrive(acc_empty); else mbar_arrive_cluster(acc_empty, leader_rank);
+    }
+    uint32_t* flag = flags + t_tail * CSIZE + cta_in_group;
+    [[maybe_unused]] const long long ts1 = BLZ_T_NOW();
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) red_release_gpu_add_u32(flag, 1u);
+    [[maybe_unused]] const long long ts2 = BLZ_T_NOW();
+    if (!flag_wait_warp(flag, target, abort_flag)) return false;
+    [[maybe_unused]] const long long ts3 = BLZ_T_NOW();
+    // This unit's slice: whole pairs of column groups (16 bytes of a 16-bit row), the last units may get none.
+    const int per = (((GROUPS4 + split - 1) / split) + 1) & ~1;
+    const int g_begin = min(GROUPS4, s_unit * per), g_end = min(GROUPS4, g_begin + per);
+    const float4* src = scratch + (static_cast<size_t>(t_tail) * split * CSIZE + cta_in_group) * (GROUPS4 * 128) + r_local;
+    constexpr size_t UNIT_STRIDE = static_cast<size_t>(CSIZE) * (GROUPS4 * 128);
+    // Eight column groups (32 columns) at a time: eight independent loads per unit are in flight, and the warp's
+    // 32 rows x 32 finished columns turn through its 4 KB of the staging memory so that the stores to C are whole
+    // row segments.  (Lanes are rows in the scratch layout; storing C that way -- 32 lanes, 32 rows, 8 bytes each --
+    // was measured at 34 k cycles for a 128 x 128 slice, the loads at 7 k.)
+    constexpr int BATCH = 8;
+    const int esize = e_out == OUT_F32 ? 4 : 2;
+    const int units_row = esize == 4 ? 8 : 4;              // 16-byte units of one row of a batch
+    const int rows_pass = 32 / units_row;
+    const int warp_row0 = row0 + (r_local & ~31);
+#pragma unroll 1
+    for (int g0 = g_begin + eset * BATCH; g0 < g_end; g0 += BATCH * SETS) {
+        float4 a[BATCH];
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j) a[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 2
+        for (int sp = 0; sp < split; ++sp) {
+            float4 x[BATCH];
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j) x[j] = (g0 + j < g_end) ? __ldcg(src + sp * UNIT_STRIDE + (g0 + j) * 128) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j) { a[j].x += x[j].x; a[j].y += x[j].y; a[j].z += x[j].z; a[j].w += x[j].w; }
+        }
+        // finished values (the whole-tile epilogue's arithmetic on 32 consecutive columns: uniform branches per
+        // batch -- the same steps written per element compiled to predicated code that cost 200 cycles an element)
+        // -> this lane's row of the warp's block, 16-byte unit u at slot u ^ (row % 8)
+        const uint32_t srow = warp_smem + static_cast<uint32_t>(lane) * 128u;
+        uint32_t bits[32];
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j) {
+            bits[4 * j] = __float_as_uint(a[j].x); bits[4 * j + 1] = __float_as_uint(a[j].y);
+            bits[4 * j + 2] = __float_as_uint(a[j].z); bits[4 * j + 3] = __float_as_uint(a[j].w);
+        }
+        float v[32];
+        epilogue_math32(epi, bits, v, row0 + r_local, col0 + 4 * g0, M, N);
+        if (esize == 4) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(srow + ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4)), "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3]) : "memory");
+        } else {
+            uint32_t w[16];
+            if (e_out == OUT_BF16) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) w[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) w[i] = pack2_out(OUT_F16, v[2 * i], v[2 * i + 1]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4)), "r"(w[4 * j]), "r"(w[4 * j + 1]), "r"(w[4 * j + 2]), "r"(w[4 * j + 3]) : "memory");
+        }
+        __syncwarp();
+        // out again with lanes along the row: `units_row` lanes per row, `rows_pass` rows per pass
+        const int u = lane % units_row;
+        const int elems_unit = 16 / esize;
+        const int n_u = col0 + 4 * g0 + u * elems_unit;             // first column of this lane's unit
+        const bool unit_live = 4 * g0 + u * elems_unit < 4 * g_end;  // the batch may reach past the slice
+        const bool vec = unit_live && n_u + elems_unit <= N && ((reinterpret_cast<uintptr_t>(e_c) | static_cast<uintptr_t>(e_ldc * esize) | static_cast<uintptr_t>(n_u * esize)) & 15u) == 0;
+        uint8_t* dst_row = e_c + ((static_cast<long long>(warp_row0) + lane / units_row) * e_ldc + n_u) * esize;
+        const long long dst_step = static_cast<long long>(rows_pass) * e_ldc * esize;
+#pragma unroll 4
+        for (int r = lane / units_row; r < 32; r += rows_pass, dst_row += dst_step) {
+            if (!unit_live || warp_row0 + r >= M || n_u >= N) continue;
+            uint32_t w[4];
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                         : "r"(warp_smem + static_cast<uint32_t>(r) * 128u + ((static_cast<uint32_t>(u) ^ (static_cast<uint32_t>(r) & 7u)) << 4)) : "memory");
+            if (vec) {
+                *reinterpret_cast<uint4*>(dst_row) = make_uint4(w[0], w[1], w[2], w[3]);
+            } else if (esize == 4) {
+                for (int k = 0; k < 4 && n_u + k < N; ++k) reinterpret_cast<uint32_t*>(dst_row)[k] = w[k];
+            } else {
+                for (int k = 0; k < 8 && n_u + k < N; ++k) reinterpret_cast<uint16_t*>(dst_row)[k] = static_cast<uint16_t>(w[k >> 1] >> (16 * (k & 1)));
+            }
+        }
+        __syncwarp();
+    }
+    if (r_local == 0 && eset == 0) { BLZ_T_STORE(9, ts1 - ts0); BLZ_T_STORE(10, ts2 - ts1); BLZ_T_STORE(11, ts3 - ts2); BLZ_T_STORE(12, BLZ_T_NOW() - ts3); }
+    return true;
 }
 
 // Where the epilogue stores a tile.  Normally one map (C).  For the fused GEMM + all-gather every
@@ -575,7 +713,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_tile, n_tile);
             // a unit of the split tail stores raw fp32 partial sums to its row block of the scratch matrix
             const bool part = unit >= 0;
-            const EpilogueParams& epi = part ? p.epi_part : p.epi;
+            const EpilogueParams& epi = p.epi;
             const int out_esize = epi.out_type == OUT_F32 ? 4 : 2;
             const int chunk_cols = 128 / out_esize;                    // columns per 128-byte staging row
             const int buf = it % ACC_BUFS;
@@ -592,12 +730,24 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             tc_fence_after_sync();
             const int row0 = ((m_tile * SHARE + static_cast<int>(pair)) * CG + static_cast<int>(prank)) * 128;
             // where the staged chunks go: C (column n_tile * BN + c, row row0) or the unit's block of the scratch matrix
-            const int st_col0 = part ? 0 : n_tile * BN;
-            const int st_row0 = part ? (unit * SHARE * CG + static_cast<int>(pair) * CG + static_cast<int>(prank)) * 128 : row0;
-            const int st_map0 = part ? p.partial_map : 0, st_maps = part ? 1 : p.n_dst;
+            const int st_col0 = n_tile * BN;
+            const int st_row0 = row0;
+            const int st_map0 = 0, st_maps = p.n_dst;
             const int r_local = q * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (Cfg::OVERLAP ? static_cast<uint32_t>(it & 1) * Cfg::ACC_OVL_OFF : static_cast<uint32_t>(buf) * BN);
-            if (p.use_tma_store || part) {
+            if (part) {
+                // ---- a K-split unit of the tail (always this group's last piece of work); out of line, so that its
+                // registers do not weigh on the whole-tile paths
+                // the staging memory (free once the earlier TMA stores have read it) becomes each warp's 4 KB transposition block
+                if (epi_tid == 0) tma_store_wait_read<0>();
+                named_barrier_sync(bar_id, 128);
+                const uint32_t warp_smem = out_base + (Cfg::EPI_SETS == 2 ? eset : 0) * Cfg::OUT_BUF_BYTES + static_cast<uint32_t>(q) * 4096u;
+                if (ok && !tail_unit_epilogue<CG, BN, Cfg::EPI_SETS, CG * SHARE>(p.tail_scratch, p.tail_flags, p.tail_target, p.tail_split, unit,
+                                                                                static_cast<int>(pair) * CG + static_cast<int>(prank), t_row, eset, r_local,
+                                                                                acc_empty_bar(buf), leader_rank, abort_flag, epi, row0, n_tile * BN, p.M, p.N, warp_smem)) {
+                    atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_SPLITK); *abort_flag = 1; ok = false;
+                }
+            } else if (p.use_tma_store) {
                 if constexpr (Cfg::EPI_SETS == 2) {
                 // (single accumulator barrier pair: the epilogue is on the tensor pipe's critical path until
                 // it hands the accumulator back)
@@ -835,7 +985,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (ok && !(p.use_tma_store || part) && lane == 0) {       // the TMA-store path released the accumulator after its last read
+            if (ok && !(p.use_tma_store || part) && lane == 0) {       // the other paths released the accumulator after their last read
                 if constexpr (CG == 1) mbar_arrive(acc_empty_bar(buf)); else mbar_arrive_cluster(acc_empty_bar(buf), leader_rank);
             }
             BLZ_T_ADD(t_work, tk);
@@ -980,54 +1130,6 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     if (warp == 2) {
         tc_fence_after_sync();
         if constexpr (CG == 2) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS); else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
-    }
-}
-
-// Finishes the tiles of the split tail: C = epilogue(alpha * sum over the tile's units, in unit order).
-// partial: [units][tile_rows][BN] fp32, unit = tile_in_tail * splits + split.  One thread per 4 columns;
-// the fixed summation order keeps results independent of timing.
-__global__ void tail_reduce_kernel(const float* __restrict__ partial, int tail_first, int tail_tiles, int splits, int tile_rows, int bn,
-                                   int m_tiles, int n_tiles, int group_m, int M, int N, EpilogueParams e) {
-    const int groups = bn / 4;
-    const long long per_tile = static_cast<long long>(tile_rows) * groups, total = per_tile * tail_tiles;
-    const int esize = e.out_type == OUT_F32 ? 4 : 2;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int t = static_cast<int>(i / per_tile);
-        const int r = static_cast<int>((i - t * per_tile) / groups), c = static_cast<int>(i % groups) * 4;
-        int m_tile, n_tile;
-        tile_coords(tail_first + t, m_tiles, n_tiles, group_m, m_tile, n_tile);
-        const long long m = static_cast<long long>(m_tile) * tile_rows + r;
-        const int n0 = n_tile * bn + c;
-        if (m >= M || n0 >= N) continue;
-        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        for (int sp = 0; sp < splits; ++sp) {
-            const float4 x = *reinterpret_cast<const float4*>(partial + ((static_cast<long long>(t) * splits + sp) * tile_rows + r) * bn + c);
-            v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int n = n0 + k;
-            v[k] *= e.alpha;
-            if (n < N && e.mode != EPI_NONE) {
-                if ((e.mode == EPI_BIAS || e.mode == EPI_BIAS_SILU) && e.bias != nullptr)
-                    v[k] += e.out_type == OUT_BF16 ? load_out_elem<OUT_BF16>(e.bias, n) : e.out_type == OUT_F16 ? load_out_elem<OUT_F16>(e.bias, n) : load_out_elem<OUT_F32>(e.bias, n);
-                if (e.mode == EPI_SILU || e.mode == EPI_BIAS_SILU) v[k] = silu_f32(v[k]);
-                if (e.mode == EPI_RESIDUAL && e.residual != nullptr) {
-                    const long long roff = m * e.ldr + n;
-                    v[k] += e.out_type == OUT_BF16 ? load_out_elem<OUT_BF16>(e.residual, roff) : e.out_type == OUT_F16 ? load_out_elem<OUT_F16>(e.residual, roff) : load_out_elem<OUT_F32>(e.residual, roff);
-                }
-            }
-        }
-        uint8_t* dst = reinterpret_cast<uint8_t*>(e.C) + (m * e.ldc + n0) * esize;
-        const bool whole = n0 + 4 <= N && (reinterpret_cast<uintptr_t>(dst) & (esize == 4 ? 15u : 7u)) == 0;
-        if (e.out_type == OUT_F32) {
-            if (whole) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-            else for (int k = 0; k < 4 && n0 + k < N; ++k) reinterpret_cast<float*>(dst)[k] = v[k];
-        } else {
-            const uint32_t w0 = pack2_out(e.out_type, v[0], v[1]), w1 = pack2_out(e.out_type, v[2], v[3]);
-            if (whole) *reinterpret_cast<uint2*>(dst) = make_uint2(w0, w1);
-            else for (int k = 0; k < 4 && n0 + k < N; ++k) reinterpret_cast<uint16_t*>(dst)[k] = static_cast<uint16_t>((k < 2 ? w0 : w1) >> (16 * (k & 1)));
-        }
     }
 }
 

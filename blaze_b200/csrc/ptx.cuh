@@ -145,6 +145,31 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, co
     }
     return __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
 }
+// A counter in global memory that CTAs of one grid publish to and wait on (all of them resident, and no CTA
+// waits before it has published): release-add, and the bounded wait of a whole warp for the counter to reach
+// `target` (wrap-safe; lane 0 polls with an acquire load, the warp barrier passes the ordering on).
+__device__ __forceinline__ void red_release_gpu_add_u32(uint32_t* p, uint32_t v) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ bool flag_wait_warp(const uint32_t* flag, uint32_t target, const volatile int* abort_flag) {
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0) {
+        const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+        for (int i = 0; static_cast<int32_t>(ld_acquire_gpu_u32(flag) - target) < 0; ++i) {
+            __nanosleep(20);
+            if ((i & 255) == 255 && (*abort_flag != 0 || global_timer_ns() - t0 > BLZ_WAIT_LIMIT_NS)) { ok = false; break; }
+        }
+    }
+    ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
+    __syncwarp();
+    return ok;
+}
 // The same bounded wait for warps that wait long while other warps of the SM need the issue slots:
 // sleeps between polls (the wake-up may come up to ~0.2 us late).
 __device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {

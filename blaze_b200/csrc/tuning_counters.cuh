@@ -4,7 +4,8 @@
 //
 // Counter slots per CTA (16 x u64), tiled kernel: 0 producer wait-empty, 1 producer total, 2 MMA wait for a
 // loaded stage, 3 MMA wait for the accumulator, 4 MMA total, 5 epilogue wait-full, 6 epilogue work, 7 epilogue
-// total, 8 tiles.  The skinny-M kernels use the slots as stamps along their dependent chain (see the kernels).
+// total, 8 tiles; a K-split unit of the tail (first epilogue warp): 9 accumulator -> scratch, 10 fence and publish,
+// 11 wait for the tile's other units, 12 sum / finish / store.  The skinny-M kernels use the slots as stamps along their dependent chain (see the kernels).
 #pragma once
 
 namespace blz {

@@ -7,6 +7,7 @@
 The tuning build is the same sources compiled with -DBLZ_KERNEL_TIMING into
 blaze_b200/libblaze_b200_tuning.so (built here on first use; the shipped library carries no counters).
 KIND: nvfp4 | fp8 | bf16 | f16; VARIANT as in GemmPlan (default auto).  Needs a B200.
+The library's environment switches apply (BLZ_TAIL_SPLIT=1: `roles` then also prints the phases of a K-split unit).
 """
 from __future__ import annotations
 
@@ -35,7 +36,7 @@ def build_tuning_library(force: bool = False) -> str:
     return TUNING_LIB
 
 
-def _plan(kind, M, N, K, variant):
+def _plan(kind, M, N, K, variant, tail_split=False):
     import torch
     from . import GemmPlan, quantize_fp8, quantize_nvfp4
     dev = torch.device("cuda:0")
@@ -52,7 +53,7 @@ def _plan(kind, M, N, K, variant):
         dt = torch.bfloat16 if kind == "bf16" else torch.float16
         A, B, kw = xa.to(dt), xb.to(dt), {}
     C = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
-    plan = GemmPlan(kind, M, N, K, A, B, out_dtype="bf16", variant=variant, **kw)
+    plan = GemmPlan(kind, M, N, K, A, B, out_dtype="bf16", variant=variant, tail_split=tail_split, **kw)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     for _ in range(3):
         flush.fill_(1); plan.execute(C)
@@ -79,6 +80,12 @@ def roles(kind, M, N, K, variant="auto"):
     for i, nm in enumerate(["producer: wait for a free stage", "producer: total", "MMA thread: wait for a loaded stage", "MMA thread: wait for the accumulator",
                             "MMA thread: total", "epilogue: wait for a full accumulator", "epilogue: work", "epilogue: total"]):
         print("   %-40s %9.0f cycles per tile" % (nm, t[:, i].mean() / max(tiles, 1)))
+    if info["tail_tiles"]:
+        print("   %d tiles cut along K into %d units each; per unit (CTAs that ran one):" % (info["tail_tiles"], info["tail_split"]))
+        for i, nm in ((9, "accumulator -> scratch"), (10, "fence and publish"), (11, "wait for the tile's other units"), (12, "sum, finish, store")):
+            col = t[:, i][t[:, i] > 0]
+            if len(col):
+                print("   %-40s %9.0f cycles (max %.0f)" % (nm, col.mean(), col.max()))
     plan.destroy()
 
 

@@ -107,10 +107,19 @@ typedef enum blz_gemm_flags {
                                   include/gemm/tmem_utils.cuh:251-305 and never wires (its persistent kernel
                                   claims tiles with atomicAdd, src/kernels/gemm_fp4_blkscaled_sm100.cu:555-563).
                                   Ignored by the 512x256 variant and by in-kernel W4A16 expansion. */
-    BLZ_FLAG_TAIL_SPLIT = 4,    /* tiled variants: when the last wave of tiles is at most half full, cut its tiles along K
-                                  into units that keep every CTA group busy; a second small kernel adds the units'
-                                  fp32 partial sums in a fixed order (run-to-run identical).  Off by default: on B200
-                                  the second launch costs more than the idle tail it removes. */
+    BLZ_FLAG_TAIL_SPLIT = 4,    /* tiled variants: when the last wave of tiles is at most half full (or the whole problem has
+                                  at most half as many tiles as the device has CTA groups), cut those tiles along K into
+                                  units that keep every CTA group busy.  Inside the same launch the units of a tile
+                                  exchange fp32 partial sums through plan-owned scratch memory and each finishes a slice
+                                  of the tile, summing in unit order (run-to-run identical; not bit-identical to the
+                                  whole-tile schedule).  The units of a tile wait for one another (bounded: a wait that
+                                  runs out sets the plan's status), so the plan must be able to have its whole grid
+                                  resident -- do not run it beside kernels that hold SMs for long.  Off by default:
+                                  measured on B200 a unit's exchange costs about what 32 K stages of a 256x256 tile cost,
+                                  so it pays only when k_stages * (1 - 1/units) is well above that (f16 512 x 12288 x 4096:
+                                  59.0 -> 55.1 us; FP8 4096^3: 56.0 -> 58.3 us).  Ignored with several outputs
+                                  (blz_gemm_execute_gather), the 512x256 and 256x384 variants, in-kernel W4A16 expansion,
+                                  the fused gate / up epilogue and BLZ_FLAG_CLC_SCHEDULER. */
     BLZ_FLAG_STATIC_WEIGHTS = 2 /* W4A16, M > 128: the caller promises that the packed weights and their scales
                                   do not change while the plan lives (or calls blz_gemm_plan_refresh_weights
                                   after changing them).  The plan then expands them ONCE, at creation, into a
@@ -154,8 +163,8 @@ typedef struct blz_plan_info {
     int32_t launches;         /* kernels one blz_gemm_execute launches */
     int32_t scheduler;        /* 0 = static persistent schedule, 1 = cluster launch control */
     int64_t workspace_bytes;  /* device memory the plan owns */
-    int32_t tail_tiles;       /* tiles of the last, partial wave that are cut along K (0 = none), and */
-    int32_t tail_split;       /* ... into how many units each; a second small kernel adds the units */
+    int32_t tail_tiles;       /* tiles that are cut along K (BLZ_FLAG_TAIL_SPLIT; 0 = none), and */
+    int32_t tail_split;       /* ... into how many units each */
 } blz_plan_info;
 
 typedef struct blz_gemm_plan blz_gemm_plan;

@@ -861,10 +861,14 @@ def test_sharded_plan_one_rank(oracle, cuda_device, exchange):
     ("fp8", "128x128", (1280, 2048, 6144), "bias_silu", "f16"),     # the reduce kernel applies bias and SiLU
     ("fp8", "256x256", (2304, 2304, 2048), "residual", "bf16"),
     ("bf16", "256x256", (2300, 2300, 1096), "none", "f32"),         # ragged in M, N and the last K stage
+    ("f16", "256x256", (512, 2048, 4096), "none", "bf16"),          # 16 tiles for 74 pairs: every tile is cut (four units each)
+    ("fp8", "256x256", (500, 1000, 11008), "bias", "bf16"),         # 8 ragged tiles, nine units each
+    ("nvfp4", "256x256", (8192, 3584, 2048), "none", "bf16"),       # 448 tiles = 6 waves + 4 tiles of 8 units (one rank's shard shape, shorter K)
 ])
 def test_tail_split(oracle, cuda_device, kind, variant, shape, mode, out_dtype):
-    """On request, when the last wave of the schedule is at most half full, its tiles are cut along K (units with
-    fp32 partial sums, a second kernel adds them in order): same result as the oracle, and the same bits run to run."""
+    """When the last wave of the schedule is at most half full, its tiles are cut along K; the units of a tile
+    exchange fp32 partial sums inside the launch and each finishes a slice of the tile in unit order: same result
+    as the oracle, and the same bits run to run."""
     from blaze_b200 import GemmPlan
     torch = _torch()
     M, N, K = shape
@@ -894,14 +898,14 @@ def test_tail_split(oracle, cuda_device, kind, variant, shape, mode, out_dtype):
     plan = GemmPlan(kind, M, N, K, *args, out_dtype=out_dtype, variant=variant, epilogue=mode, bias=dev(bias_n) if "bias" in mode else None,
                     residual=dev(res_n) if mode == "residual" else None, tail_split=True, **kw)
     info = plan.info()
-    assert info["tail_tiles"] > 0 and info["tail_split"] >= 2 and info["launches"] == 2, info
+    assert info["tail_tiles"] > 0 and info["tail_split"] >= 2 and info["launches"] == 1, info
     outs = []
-    for _ in range(2):
+    for _ in range(3):
         C = _out_tensor(M, N, out_dtype, cuda_device)
         _run(plan, C)
         outs.append(C)
     assert_close(torch_to_f32(outs[0], oracle, out_dtype), want, "tail split %s %s %s %s" % (kind, variant, shape, info))
-    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     plan.destroy()
 
 
