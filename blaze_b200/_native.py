@@ -20,13 +20,14 @@ EPI_NONE, EPI_BIAS, EPI_SILU, EPI_BIAS_SILU, EPI_RESIDUAL_ADD, EPI_SWIGLU = rang
 B_KMAJOR, B_NMAJOR = range(2)
 SF_ROWMAJOR, SF_TILED = range(2)
 FLAG_CLC_SCHEDULER, FLAG_STATIC_WEIGHTS, FLAG_TAIL_SPLIT = 1, 2, 4
-VARIANT_AUTO, VARIANT_TILE_128x128, VARIANT_PAIR_256x256, VARIANT_DECODE, VARIANT_QUAD_512x256, VARIANT_PAIR_256x384 = range(6)
+VARIANT_AUTO, VARIANT_TILE_128x128, VARIANT_PAIR_256x256, VARIANT_DECODE, VARIANT_QUAD_512x256, VARIANT_PAIR_256x384, VARIANT_PAIR_256x128 = range(7)
 
 KINDS = {"f16": GEMM_F16, "bf16": GEMM_BF16, "fp8": GEMM_FP8, "nvfp4": GEMM_NVFP4,
          "w4a16_f16": GEMM_W4A16_F16, "w4a16_bf16": GEMM_W4A16_BF16}
 DTYPES = {"f16": F16, "bf16": BF16, "f32": F32}
 EPILOGUES = {"none": EPI_NONE, "bias": EPI_BIAS, "silu": EPI_SILU, "bias_silu": EPI_BIAS_SILU, "residual": EPI_RESIDUAL_ADD, "swiglu": EPI_SWIGLU}
-VARIANTS = {"auto": VARIANT_AUTO, "128x128": VARIANT_TILE_128x128, "256x256": VARIANT_PAIR_256x256, "decode": VARIANT_DECODE, "512x256": VARIANT_QUAD_512x256, "256x384": VARIANT_PAIR_256x384}
+VARIANTS = {"auto": VARIANT_AUTO, "128x128": VARIANT_TILE_128x128, "256x256": VARIANT_PAIR_256x256, "decode": VARIANT_DECODE, "512x256": VARIANT_QUAD_512x256, "256x384": VARIANT_PAIR_256x384,
+            "256x128": VARIANT_PAIR_256x128}
 
 # every symbol include/blaze_b200.h declares
 EXPORTS = (

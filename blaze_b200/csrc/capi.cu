@@ -110,8 +110,15 @@ ClusterChoice cluster_choice() {
                          static_cast<int>(Cfg::SMEM_BYTES), static_cast<int>(Cfg::TMEM_COLS), Cfg::THREADS, SHARE, 4 * Cfg::EPI_SETS};
 }
 
-ClusterChoice pick_cluster_kernel(int mma_kind, int cg, int share, bool wide = false) {
+ClusterChoice pick_cluster_kernel(int mma_kind, int cg, int share, bool wide = false, bool narrow = false) {
     if (wide) return cluster_choice<MMA_NVF4, 2, 384, 4, 1>();
+    if (narrow) {       // CTA pairs on 256x128 tiles: 24 KB per stage, eight stages, two accumulators
+        switch (mma_kind) {
+            case MMA_F16: return cluster_choice<MMA_F16, 2, 128, 8, 2>();
+            case MMA_F8: return cluster_choice<MMA_F8, 2, 128, 8, 2>();
+            default: return cluster_choice<MMA_NVF4, 2, 128, 6, 2>();
+        }
+    }
     if (cg == 2 && share == 2) {
         switch (mma_kind) {
             case MMA_F16: return cluster_choice<MMA_F16, 2, 256, 6, 2, 2>();
@@ -301,15 +308,15 @@ blz_status launch_config_cluster(const blz_gemm_plan* p, cudaLaunchConfig_t& cfg
     return BLZ_OK;
 }
 
-blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1, bool wide = false) {
+blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1, bool wide = false, bool narrow = false) {
     const blz_gemm_desc& d = p->desc;
     const int64_t rb = row_bytes(p->mma_kind, d.K);
     if (wide && p->mma_kind != MMA_NVF4) return BLZ_ERR_UNSUPPORTED;
     // W4A16 without a 16-bit copy of the weights: the kernel expands the packed weights itself
     const bool fused_w4 = (d.kind == BLZ_GEMM_W4A16_F16 || d.kind == BLZ_GEMM_W4A16_BF16) && p->own_w16 == nullptr;
-    if (fused_w4 && share != 1) return BLZ_ERR_UNSUPPORTED;
-    p->cc = pick_cluster_kernel(fused_w4 ? static_cast<int>(MMA_W4A16) : p->mma_kind, cg, share, wide);
-    p->variant = wide ? BLZ_VARIANT_PAIR_256x384 : share == 2 ? BLZ_VARIANT_QUAD_512x256 : cg == 2 ? BLZ_VARIANT_PAIR_256x256 : BLZ_VARIANT_TILE_128x128;
+    if (fused_w4 && (share != 1 || narrow)) return BLZ_ERR_UNSUPPORTED;
+    p->cc = pick_cluster_kernel(fused_w4 ? static_cast<int>(MMA_W4A16) : p->mma_kind, cg, share, wide, narrow);
+    p->variant = wide ? BLZ_VARIANT_PAIR_256x384 : narrow ? BLZ_VARIANT_PAIR_256x128 : share == 2 ? BLZ_VARIANT_QUAD_512x256 : cg == 2 ? BLZ_VARIANT_PAIR_256x256 : BLZ_VARIANT_TILE_128x128;
     BLZ_CUDA(cudaFuncSetAttribute(p->cc.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, p->cc.smem));
     const int bn = p->cc.bn, tile_m = 128 * cg;
     blz_status s = encode_map(&p->tm_a, p->a_used, static_cast<uint64_t>(rb), static_cast<uint64_t>(d.M), static_cast<uint64_t>(rb), 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -803,6 +810,7 @@ blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_p
         if (v == BLZ_VARIANT_PAIR_256x384) s = setup_cluster(p, 2, 1, true);
         else if (v == BLZ_VARIANT_QUAD_512x256) s = setup_cluster(p, 2, 2);
         else if (v == BLZ_VARIANT_PAIR_256x256) s = setup_cluster(p, 2);
+        else if (v == BLZ_VARIANT_PAIR_256x128) s = setup_cluster(p, 2, 1, false, true);
         else if (v == BLZ_VARIANT_TILE_128x128) s = setup_cluster(p, 1);
         else s = BLZ_ERR_INVALID_ARGUMENT;
         p->b_used = keep;

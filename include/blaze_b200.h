@@ -95,8 +95,10 @@ typedef enum blz_variant {
                                      kernel); on request also M <= 128 for FP8 and 16-bit, not NVFP4 */
     BLZ_VARIANT_QUAD_512x256 = 4, /* two CTA pairs per 512x256 tile; the pairs pass each other their
                                      halves of the B tile through distributed shared memory */
-    BLZ_VARIANT_PAIR_256x384 = 5  /* NVFP4 only: CTA pairs, 256x384 tiles (a 256-wide and a 128-wide
+    BLZ_VARIANT_PAIR_256x384 = 5, /* NVFP4 only: CTA pairs, 256x384 tiles (a 256-wide and a 128-wide
                                      instruction per K step), fewer L2 bytes per FLOP */
+    BLZ_VARIANT_PAIR_256x128 = 6  /* CTA pairs, 256x128 tiles: twice as many tiles as 256x256 for problems whose
+                                     256x256 tiles fill the last wave of CTA pairs badly */
 } blz_variant;
 
 typedef enum blz_gemm_flags {

@@ -67,6 +67,9 @@ def _dense_inputs(oracle, kind, M, N, K, scale=1.0):
     ("bf16", "bf16", "512x256", (512, 256, 64)),     # two pairs sharing B, one tile, one K stage
     ("bf16", "f32", "512x256", (700, 520, 392)),     # ragged; the second pair partly outside M
     ("f16", "f16", "512x256", (2048, 2304, 1024)),
+    ("bf16", "bf16", "256x128", (256, 128, 64)),     # CTA pair on a 256x128 tile: one tile, one K stage
+    ("f16", "f32", "256x128", (300, 200, 136)),      # ... ragged in M, N and K
+    ("f16", "f16", "256x128", (2048, 2304, 1024)),   # ... several tiles per pair, the eight-stage ring wraps
     ("f16", "f32", "decode", (1, 128, 64)),          # skinny-M weight stream: one tile, one K stage
     ("bf16", "bf16", "decode", (16, 384, 520)),      # ragged K stage
     ("f16", "f16", "decode", (33, 1000, 1032)),      # 64-row instruction, ragged N
@@ -151,6 +154,9 @@ def _fp8_inputs(oracle, M, N, K):
     ("512x256", (512, 256, 128)),
     ("512x256", (1024, 2048, 2048)),
     ("512x256", (300, 328, 144)),
+    ("256x128", (256, 128, 128)),
+    ("256x128", (300, 328, 144)),
+    ("256x128", (1024, 2048, 2048)),
     ("decode", (1, 256, 128)),
     ("decode", (32, 4096, 1024)),
     ("decode", (48, 1000, 1136)),
@@ -241,6 +247,9 @@ def _nvfp4_ref(oracle, qa, qb, out_dtype="bf16", **epi):
     ("512x256", (1024, 768, 1536)),
     ("512x256", (700, 328, 160)),      # ragged
     ("512x256", (2048, 2304, 1024)),
+    ("256x128", (256, 128, 256)),      # CTA pair on a 256x128 tile: one tile, one K stage
+    ("256x128", (200, 328, 160)),      # ... ragged
+    ("256x128", (2048, 2304, 2048)),   # ... several tiles per pair
     ("decode", (16, 512, 1024)),
     ("decode", (1, 128, 256)),
     ("decode", (7, 200, 160)),
@@ -262,7 +271,7 @@ def test_nvfp4(oracle, cuda_device, variant, shape):
     plan.destroy()
 
 
-@pytest.mark.parametrize("variant,M", [("128x128", 128), ("256x256", 256), ("256x256", 128), ("256x384", 256), ("decode", 16)])
+@pytest.mark.parametrize("variant,M", [("128x128", 128), ("256x256", 256), ("256x256", 128), ("256x384", 256), ("256x128", 256), ("decode", 16)])
 def test_nvfp4_position_coded(oracle, cuda_device, variant, M):
     """Catches transposition, nibble order and scale-layout errors that constant fills hide:
     row m of A is one-hot at k = (37*m + 5) % K with its own block scale, every weight and every
