@@ -103,11 +103,28 @@ struct ClusterChoice {
     int cg, bn, stages, acc_bufs, smem, tmem_cols, threads, share, epi_warps;
 };
 
-template <int KIND, int CG, int BN, int STAGES, int ACC, int SHARE = 1>
+template <int KIND, int CG, int BN, int STAGES, int ACC, int SHARE = 1, bool TAIL = false>
 ClusterChoice cluster_choice() {
     using Cfg = ClusterGemmConfig<KIND, CG, BN, STAGES, ACC, SHARE>;
-    return ClusterChoice{reinterpret_cast<const void*>(&gemm_cluster_kernel<KIND, CG, BN, STAGES, ACC, SHARE>), CG, BN, STAGES, ACC,
+    return ClusterChoice{reinterpret_cast<const void*>(&gemm_cluster_kernel<KIND, CG, BN, STAGES, ACC, SHARE, TAIL>), CG, BN, STAGES, ACC,
                          static_cast<int>(Cfg::SMEM_BYTES), static_cast<int>(Cfg::TMEM_COLS), Cfg::THREADS, SHARE, 4 * Cfg::EPI_SETS};
+}
+
+// the instances that can run K-split units of the tail (BLZ_FLAG_TAIL_SPLIT): 128x128 and 256x256 tiles of the three
+// tensor-core kinds
+ClusterChoice pick_tail_kernel(int mma_kind, int cg) {
+    if (cg == 2) {
+        switch (mma_kind) {
+            case MMA_F16: return cluster_choice<MMA_F16, 2, 256, 6, 2, 1, true>();
+            case MMA_F8: return cluster_choice<MMA_F8, 2, 256, 6, 2, 1, true>();
+            default: return cluster_choice<MMA_NVF4, 2, 256, 5, 1, 1, true>();
+        }
+    }
+    switch (mma_kind) {
+        case MMA_F16: return cluster_choice<MMA_F16, 1, 128, 6, 2, 1, true>();
+        case MMA_F8: return cluster_choice<MMA_F8, 1, 128, 6, 2, 1, true>();
+        default: return cluster_choice<MMA_NVF4, 1, 128, 5, 2, 1, true>();
+    }
 }
 
 ClusterChoice pick_cluster_kernel(int mma_kind, int cg, int share, bool wide = false, bool narrow = false) {
@@ -403,7 +420,7 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1, bool wide = fa
     cp.tail_scratch = nullptr; cp.tail_flags = nullptr; cp.tail_target = 0;
     p->tail_tiles = 0; p->tail_split = 1;
     const int64_t tail = tiles % max_groups;
-    if (share == 1 && !fused_w4 && !wide && cp.split_k == 1 && d.epilogue != BLZ_EPI_SWIGLU && tail > 0 &&
+    if (share == 1 && !fused_w4 && !wide && !narrow && cp.split_k == 1 && d.epilogue != BLZ_EPI_SWIGLU && tail > 0 &&
         env_int("BLZ_TAIL_SPLIT", (d.flags & BLZ_FLAG_TAIL_SPLIT) ? 1 : 0) != 0) {
         int split = static_cast<int>(max_groups / tail);
         if (split > 16) split = 16;
@@ -428,6 +445,8 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1, bool wide = fa
             cp.tail_first = p->tail_first; cp.tail_split = split; cp.tail_kps = kps; cp.total_units = static_cast<int>(tiles - tail + units);
             cp.tail_scratch = reinterpret_cast<float4*>(p->own_tail); cp.tail_flags = p->tail_flags;
             p->grid = static_cast<int>(cp.total_units < max_groups ? cp.total_units : max_groups) * csize;    // few tiles: one group per unit
+            p->cc = pick_tail_kernel(p->mma_kind, cg);             // same configuration, the instance that knows units
+            BLZ_CUDA(cudaFuncSetAttribute(p->cc.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, p->cc.smem));
         }
     }
     // Dynamic scheduling: one cluster per tile in the grid; clusters that are running take over the tiles of
@@ -445,6 +464,36 @@ blz_status setup_cluster(blz_gemm_plan* p, int cg, int share = 1, bool wide = fa
     if (cp.clc) p->grid = static_cast<int>(tiles) * csize;
     p->clc = cp.clc;
     return BLZ_OK;
+}
+
+// Tile shape for BLZ_VARIANT_AUTO (M > 128; below that the decode kernels or 128-row tiles).  Large problems take
+// 256x256 pair tiles: fewest L2 bytes per FLOP.  Up to three waves of those, the quantisation of the last wave and
+// the drain of the last tile decide, and a small model picks among 256x256, 256x128 (pairs) and 128x128 (single
+// CTAs): cost = waves x K stages x the variant's time per stage + its drain, in units of one K stage of a 256x256
+// tile.  The per-stage factors and drains are fitted to measurements on B200 (18 shapes with M = 256 ... 1024, three
+// kinds): a 256x128 tile takes 0.58 of a 256x256 tile's time (0.50 for NVFP4), a wave of 128x128 tiles 0.68 (0.52);
+// the model ranks the variants correctly on all of them, e.g. f16 1024 x 4096 x 11008: 70 us (256x256) against 94
+// (128x128, the former choice); f16 512 x 4096 x 11008: 52 (256x128) against 56 / 66.  The larger tile wins ties
+// (within 7 %).
+int choose_tile_variant(const blz_gemm_plan* p, bool fused_w4) {
+    const blz_gemm_desc& d = p->desc;
+    const int64_t pairs = p->num_sms / 2;
+    const int64_t t256 = ceil_div(d.M, 256) * ceil_div(d.N, 256);
+    if (d.M <= 128) return BLZ_VARIANT_TILE_128x128;
+    if (fused_w4 || d.epilogue == BLZ_EPI_SWIGLU)      // no 256x128 instance of these: pairs when every pair gets a tile
+        return t256 >= pairs ? BLZ_VARIANT_PAIR_256x256 : BLZ_VARIANT_TILE_128x128;
+    const int64_t w256 = ceil_div(t256, pairs);
+    if (w256 > 3) return BLZ_VARIANT_PAIR_256x256;
+    const bool nvf4 = p->mma_kind == MMA_NVF4;
+    const double ks = static_cast<double>(ceil_div(row_bytes(p->mma_kind, d.K), 128));
+    const double r_narrow = nvf4 ? 0.50 : 0.58, r_single = nvf4 ? 0.52 : 0.68;
+    const double c256 = static_cast<double>(w256) * ks + 6.0;
+    const double c_narrow = static_cast<double>(ceil_div(ceil_div(d.M, 256) * ceil_div(d.N, 128), pairs)) * ks * r_narrow + 3.0;
+    const double c_single = static_cast<double>(ceil_div(ceil_div(d.M, 128) * ceil_div(d.N, 128), static_cast<int64_t>(p->num_sms))) * ks * r_single + 3.0;
+    const double best = c256 < c_narrow ? (c256 < c_single ? c256 : c_single) : (c_narrow < c_single ? c_narrow : c_single);
+    if (c256 <= 1.07 * best) return BLZ_VARIANT_PAIR_256x256;
+    if (c_narrow <= 1.07 * best) return BLZ_VARIANT_PAIR_256x128;
+    return BLZ_VARIANT_TILE_128x128;
 }
 
 void fill_epilogue(const blz_gemm_plan* p, void* C, EpilogueParams& e) {
@@ -802,11 +851,7 @@ blz_status blz_gemm_plan_create(const blz_gemm_desc* desc, blz_gemm_plan** out_p
         const void* keep = p->b_used;
         p->b_used = b_tc;
         int v = desc->variant;
-        if (v == BLZ_VARIANT_AUTO) {
-            // CTA pairs when there is at least one 256x256 tile per pair of SMs, else single CTAs
-            const int64_t tiles256 = ceil_div(desc->M, 256) * ceil_div(desc->N, 256);
-            v = (desc->M > 128 && tiles256 >= p->num_sms / 2) ? BLZ_VARIANT_PAIR_256x256 : BLZ_VARIANT_TILE_128x128;
-        }
+        if (v == BLZ_VARIANT_AUTO) v = choose_tile_variant(p, w4a16 && p->own_w16 == nullptr);
         if (v == BLZ_VARIANT_PAIR_256x384) s = setup_cluster(p, 2, 1, true);
         else if (v == BLZ_VARIANT_QUAD_512x256) s = setup_cluster(p, 2, 2);
         else if (v == BLZ_VARIANT_PAIR_256x256) s = setup_cluster(p, 2);

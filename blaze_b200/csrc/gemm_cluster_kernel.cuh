@@ -115,7 +115,7 @@ __device__ __forceinline__ void resolve_unit(const P& p, int index, int& tile, i
 // published -- this unit's slice of the tile's column groups summed over the units in unit order, finished and
 // stored to C.  False: the bounded wait for the other units ran out.
 template <int CG, int BN, int SETS, int CSIZE>
-__device__ __noinline__ bool tail_unit_epilogue(float4* scratch, uint32_t* flags, uint32_t target, int split, int unit, int cta_in_group,
+__device__ __forceinline__ bool tail_unit_epilogue(float4* scratch, uint32_t* flags, uint32_t target, int split, int unit, int cta_in_group,
                                                 uint32_t t_row, int eset, int r_local, uint32_t acc_empty, uint32_t leader_rank,
                                                 const volatile int* abort_flag, EpilogueParams epi, int row0, int col0, int M, int N, uint32_t warp_smem) {
     constexpr int GROUPS4 = BN / 4;
@@ -347,7 +347,10 @@ struct ClusterGemmConfig {
     static_assert(!WIDE || (KIND == MMA_NVF4 && CG == 2 && SHARE == 1 && ACC_BUFS == 1 && STAGES % 2 == 0), "384-wide tiles: NVFP4 CTA pairs only");
 };
 
-template <int KIND, int CG, int BN, int STAGES, int ACC_BUFS, int SHARE = 1>
+// TAIL: the instance that can run K-split units of the tail (plans that asked for them); the plain instance
+// carries none of that code -- in the NVFP4 pair kernel the extra epilogue path cost the whole-tile path its
+// registers (11.6 k -> 14.5 k cycles per 256x256 tile at K = 4096).
+template <int KIND, int CG, int BN, int STAGES, int ACC_BUFS, int SHARE = 1, bool TAIL = false>
 __global__ void __launch_bounds__(ClusterGemmConfig<KIND, CG, BN, STAGES, ACC_BUFS, SHARE>::THREADS, 1)
 gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const __grid_constant__ OutputMaps out, const ClusterGemmParams p) {
@@ -461,7 +464,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             for (int tile = feed.take(); ok && tile >= 0; tile = feed.take()) {
                 int m_tile, n_tile;
                 int m_ext, ks0, ks1, unit, u0 = 0, u1 = 0;
-                resolve_unit(p, tile, tile, unit, u0, u1);
+                if constexpr (TAIL) resolve_unit(p, tile, tile, unit, u0, u1); else unit = -1;
                 tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_ext, n_tile);
                 tile_k_range(p, m_ext, m_tile, ks0, ks1);
                 if (unit >= 0) { ks0 = u0; ks1 = u1; }
@@ -569,7 +572,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (Cfg::OVERLAP ? static_cast<uint32_t>(it & 1) * Cfg::ACC_OVL_OFF : static_cast<uint32_t>(buf) * BN);
                 int ks0, ks1;
-                if (tile >= p.tail_first) { int t_, u_; resolve_unit(p, tile, t_, u_, ks0, ks1); }     // a K-split unit of the tail
+                if (TAIL && tile >= p.tail_first) { int t_, u_; resolve_unit(p, tile, t_, u_, ks0, ks1); }     // a K-split unit of the tail
                 else if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
                 else { int m_e, n_e, m_r; tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_e, n_e); tile_k_range(p, m_e, m_r, ks0, ks1); }
                 for (int ks = ks0; ks < ks1; ++ks) {
@@ -709,10 +712,10 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         TileFeed feed = make_feed(true);
         for (int tile = feed.take(); tile >= 0; tile = feed.take(), ++it) {
             int m_tile, n_tile, unit, u0_, u1_;
-            resolve_unit(p, tile, tile, unit, u0_, u1_);
+            if constexpr (TAIL) resolve_unit(p, tile, tile, unit, u0_, u1_); else unit = -1;
             tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_tile, n_tile);
             // a unit of the split tail stores raw fp32 partial sums to its row block of the scratch matrix
-            const bool part = unit >= 0;
+            const bool part = TAIL && unit >= 0;
             const EpilogueParams& epi = p.epi;
             const int out_esize = epi.out_type == OUT_F32 ? 4 : 2;
             const int chunk_cols = 128 / out_esize;                    // columns per 128-byte staging row
@@ -736,8 +739,8 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             const int r_local = q * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (Cfg::OVERLAP ? static_cast<uint32_t>(it & 1) * Cfg::ACC_OVL_OFF : static_cast<uint32_t>(buf) * BN);
             if (part) {
-                // ---- a K-split unit of the tail (always this group's last piece of work); out of line, so that its
-                // registers do not weigh on the whole-tile paths
+              if constexpr (TAIL) {
+                // ---- a K-split unit of the tail (always this group's last piece of work)
                 // the staging memory (free once the earlier TMA stores have read it) becomes each warp's 4 KB transposition block
                 if (epi_tid == 0) tma_store_wait_read<0>();
                 named_barrier_sync(bar_id, 128);
@@ -747,6 +750,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                                                                                 acc_empty_bar(buf), leader_rank, abort_flag, epi, row0, n_tile * BN, p.M, p.N, warp_smem)) {
                     atomicCAS(p.status, 0, BLZ_DEV_TIMEOUT_SPLITK); *abort_flag = 1; ok = false;
                 }
+              }
             } else if (p.use_tma_store) {
                 if constexpr (Cfg::EPI_SETS == 2) {
                 // (single accumulator barrier pair: the epilogue is on the tensor pipe's critical path until
@@ -1005,7 +1009,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             bool ok = true;
             for (int tile = group; ok && tile < total_tiles; tile += num_groups) {
                 int ks0, ks1;
-                if (tile >= p.tail_first) { int t_, u_; resolve_unit(p, tile, t_, u_, ks0, ks1); }     // a K-split unit of the tail
+                if (TAIL && tile >= p.tail_first) { int t_, u_; resolve_unit(p, tile, t_, u_, ks0, ks1); }     // a K-split unit of the tail
                 else if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
                 else { int m_e, n_e, m_r; tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_e, n_e); tile_k_range(p, m_e, m_r, ks0, ks1); }
                 for (int ks = ks0; ks < ks1; ++ks, ++n) {
@@ -1038,7 +1042,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             TileFeed feed = make_feed(true);
             for (int tile = feed.take(); ok && tile >= 0; tile = feed.take()) {
                 int ks0, ks1;
-                if (tile >= p.tail_first) { int t_, u_; resolve_unit(p, tile, t_, u_, ks0, ks1); }     // a K-split unit of the tail
+                if (TAIL && tile >= p.tail_first) { int t_, u_; resolve_unit(p, tile, t_, u_, ks0, ks1); }     // a K-split unit of the tail
                 else if (p.split_k == 1) { ks0 = 0; ks1 = p.k_stages; }      // no K split: nothing to look up (the divisions below would sit on the tile's critical path)
                 else { int m_e, n_e, m_r; tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, m_e, n_e); tile_k_range(p, m_e, m_r, ks0, ks1); }
                 for (int ks = ks0; ks < ks1; ++ks) {
