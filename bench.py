@@ -631,6 +631,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="nvfp4_8192x28672x8192", choices=list(WORKLOADS) + ["decode"])
     ap.add_argument("--variant", default="auto")
+    ap.add_argument("--shape", default=None, metavar="KIND,M,N,K",
+                    help="time this shape instead of a named workload (kind: nvfp4, fp8, f16, bf16, w4a16_bf16, w4a16_f16), e.g. f16,512,12288,4096")
     ap.add_argument("--decode-kind", default="nvfp4", choices=["nvfp4", "fp8", "w4a16_bf16", "w4a16_f16"],
                     help="operand kind of --workload decode (the reference's decode configuration is nvfp4)")
     ap.add_argument("--no-others", action="store_true", help="skip the secondary workloads (decode, comparator, others)")
@@ -641,6 +643,11 @@ def main() -> int:
     args.warmup = max(args.warmup, 3)
 
     name = args.workload
+    if args.shape:
+        k_, m_, n_, kk_ = args.shape.split(",")
+        name = "%s_%sx%sx%s" % (k_, m_, n_, kk_)
+        WORKLOADS[name] = (k_, int(m_), int(n_), int(kk_))
+        args.workload = name
     if name == "decode":
         kind, M, N, K = "nvfp4", 16, 22016, 4096
     else:
