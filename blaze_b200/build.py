@@ -34,19 +34,26 @@ def _stale() -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return OUT
-    objs = []
+    # the translation units compile side by side (the tiled-kernel instances in capi.cu take most of the time)
+    jobs = []
     for src in SOURCES:
         obj = os.path.join(CSRC, src.replace(".cu", ".o"))
         cmd = [NVCC, *FLAGS, "-c", "-o", obj, os.path.join(CSRC, src)]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
-        r = subprocess.run(cmd, capture_output=True, text=True)
+        jobs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
+    objs = []
+    failed = None
+    for src, obj, proc in jobs:
+        out, err = proc.communicate()
         if verbose:
-            sys.stderr.write(r.stderr)
-        if r.returncode != 0:
-            raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, r.stdout, r.stderr))
+            sys.stderr.write(err)
+        if proc.returncode != 0 and failed is None:
+            failed = "nvcc failed for %s:\n%s\n%s" % (src, out, err)
         objs.append(obj)
+    if failed:
+        raise RuntimeError(failed)
     r = subprocess.run([NVCC, "-shared", "-o", OUT, *objs, "-ldl"], capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
